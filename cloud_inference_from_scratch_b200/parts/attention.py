@@ -1,0 +1,103 @@
+"""Grouped-query causal attention over the paged cache.
+
+Reference formulas: projections with bias, head-major split (src/cloud_engine/model.py:132-137);
+rotary on q and k (attention.py:83-85); keys and values written to the pages before
+attention so that a portion attends to itself through the cache (attention.py:193,225;
+cache.py:398-425); per q head h the kv head h // (Hq/Hkv), keys 0..pos inclusive,
+scale 1/sqrt(head_dim), float32 softmax (kernel.py:356-405; attention.py:88-112,129);
+output projection without bias (model.py:128-130).
+
+Here q, k and v come from ONE matrix product with the three weights stacked, the
+rotation is fused with the write of k and v into the pages, and attention reads the
+pages directly through the block table.  ``window`` > 0 limits a query at position p
+to keys p-window+1..p.
+"""
+
+from __future__ import annotations
+
+import math
+
+from ..config.spec import PartSpec
+from .base import CacheSpec, Mixer, TensorSpec, build_part, register_part
+
+
+class Attention(Mixer):
+    def __init__(
+        self,
+        hidden_size: int,
+        num_heads: int,
+        num_kv_heads: int,
+        head_dim: int,
+        qkv_bias: bool,
+        position: PartSpec | None,
+        window: int = 0,
+        scale: float | None = None,
+    ) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.hidden_size = int(hidden_size)
+        self.num_heads = int(num_heads)
+        self.num_kv_heads = int(num_kv_heads)
+        self.head_dim = int(head_dim)
+        self.qkv_bias = bool(qkv_bias)
+        self.window = int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.position = build_part("position", position) if position is not None else None
+        self.q_width = self.num_heads * self.head_dim
+        self.kv_width = self.num_kv_heads * self.head_dim
+        self.qkv_width = self.q_width + 2 * self.kv_width
+
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        specs = {
+            "q_proj.weight": TensorSpec((self.q_width, self.hidden_size)),
+            "k_proj.weight": TensorSpec((self.kv_width, self.hidden_size)),
+            "v_proj.weight": TensorSpec((self.kv_width, self.hidden_size)),
+            "o_proj.weight": TensorSpec((self.hidden_size, self.q_width)),
+        }
+        if self.qkv_bias:
+            specs["q_proj.bias"] = TensorSpec((self.q_width,), role="vector")
+            specs["k_proj.bias"] = TensorSpec((self.kv_width,), role="vector")
+            specs["v_proj.bias"] = TensorSpec((self.kv_width,), role="vector")
+        return specs
+
+    def bind(self, tensors, runtime) -> None:
+        import torch
+
+        self.runtime = runtime
+        self.w_qkv = runtime.ops.prepare_weight(
+            torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]])
+        )
+        self.b_qkv = (
+            torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]).contiguous()
+            if self.qkv_bias
+            else None
+        )
+        self.w_o = runtime.ops.prepare_weight(tensors["o_proj.weight"])
+        if self.position is not None:
+            self.position.bind({}, runtime)
+        runtime.ops.require_attention(self.head_dim)
+
+    def forward(self, x, ctx, binding):
+        rt = self.runtime
+        tokens = x.shape[0]
+        qkv = rt.workspace.get("attention.qkv", tokens, self.qkv_width, rt.dtype)
+        rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        kv = binding.kv
+        rt.ops.rope_kv_write(
+            qkv, ctx, kv, self.position, self.num_heads, self.num_kv_heads, self.head_dim,
+            write_cache=binding.owns_cache,
+        )
+        mixed = rt.workspace.get("attention.out", tokens, self.q_width, rt.dtype)
+        rt.ops.attention(
+            qkv, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
+            self.scale, self.window,
+        )
+        update = rt.workspace.get("mixer.update", tokens, self.hidden_size, rt.dtype)
+        rt.ops.linear(mixed, self.w_o, None, update)
+        return update
+
+
+register_part("mixer", "attention", Attention, replace=True)

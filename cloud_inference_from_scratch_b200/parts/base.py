@@ -1,0 +1,166 @@
+"""Interfaces of the parts a layer is put together from, and the registries they are chosen from.
+
+A part is built from constants only (its ``PartSpec.params``); it never sees a model
+configuration.  Each part says which tensors it needs (``tensor_specs``), takes them
+(``bind``) and runs on a flat batch of tokens (``forward``).  Five kinds exist:
+
+* ``Norm``              normalises the residual stream (after adding a pending update to it)
+* ``PositionEncoding``  owned by a mixer; gives the constants its kernels rotate with
+* ``Mixer``             mixes information between the tokens of a request; may own pages of
+                        a cache (``cache_spec``) and/or per-request state of fixed size
+                        (``state_spec``)
+* ``FeedForward``       acts on each token alone
+* ``Block``             the arrangement of the above inside one layer
+
+Registering a new kind is ``register_part("mixer", "name", cls)``; a model description
+then names it in a ``PartSpec``.  The reference builds the same parts as fixed
+``nn.Module`` classes taking the whole ``ModelDims`` (src/cloud_engine/model.py:86-160).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import TYPE_CHECKING, Any
+
+from ..config.spec import PartSpec
+
+if TYPE_CHECKING:  # pragma: no cover
+    import torch
+
+    from ..engine.context import LayerBinding, StepContext
+    from ..engine.runtime import Runtime
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """A tensor a part reads from the weight files.
+
+    ``init`` is how the random-weights mode fills it: "normal" N(0, std), "gain"
+    1 + N(0, std), "zeros".  ``role`` "matrix" tensors are held in the compute dtype
+    (bfloat16 unless the whole run is 32-bit); "vector" tensors (norm gains, biases)
+    are held in float32, which keeps a 32-bit stored tensor as it is and widens a
+    bfloat16 one without loss; "table" tensors are integer tables held as int32.
+    """
+
+    shape: tuple[int, ...]
+    init: str = "normal"
+    role: str = "matrix"
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """What a mixer needs of the page manager: keys and values for ``kv_heads`` heads of
+    ``head_dim`` per token, for all earlier tokens (``window == 0``) or the last ``window``."""
+
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+    @property
+    def group_key(self) -> tuple[int, int, int]:
+        return (self.window, self.kv_heads, self.head_dim)
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size, one tensor of ``shape`` per live request."""
+
+    shape: tuple[int, ...]
+    dtype: str = "float32"
+
+
+class Part:
+    """Common protocol: declare tensors, take them, run."""
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {}
+
+    def bind(self, tensors: dict[str, "torch.Tensor"], runtime: "Runtime") -> None:
+        self.runtime = runtime
+
+
+class Norm(Part):
+    def forward(
+        self,
+        residual: "torch.Tensor",
+        update: "torch.Tensor | None",
+        ctx: "StepContext",
+        rows: "torch.Tensor | None" = None,
+    ) -> "torch.Tensor":
+        """``residual`` is the float32 stream [T, H].  Adds ``update`` to it in place (32-bit
+        sum) when given, and returns the normalised rows in the compute dtype.  With ``rows``
+        only those rows are normalised and returned, and ``residual`` is left as it was."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Constants of a position encoding; the mixer's kernels consume them."""
+
+
+class Mixer(Part):
+    def cache_spec(self) -> CacheSpec | None:
+        return None
+
+    def state_spec(self) -> StateSpec | None:
+        return None
+
+    def forward(
+        self, x: "torch.Tensor", ctx: "StepContext", binding: "LayerBinding"
+    ) -> "torch.Tensor":
+        """x: normalised input [T, H] in the compute dtype; returns the update [T, H]."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: "torch.Tensor", ctx: "StepContext") -> "torch.Tensor":
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of the parts of one layer around the residual stream."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
+                 feed_forward_norm: Norm, **params: Any) -> None:
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(
+        self,
+        residual: "torch.Tensor",
+        pending: "torch.Tensor | None",
+        ctx: "StepContext",
+        binding: "LayerBinding",
+    ) -> "torch.Tensor | None":
+        """Runs the layer.  ``pending`` is an update not yet added to ``residual``; the
+        returned tensor is this layer's last update, again pending."""
+        raise NotImplementedError
+
+
+_KINDS = ("norm", "position", "mixer", "feed_forward", "block")
+_REGISTRY: dict[str, dict[str, type]] = {kind: {} for kind in _KINDS}
+
+
+def register_part(kind: str, name: str, cls: type, *, replace: bool = False) -> None:
+    if kind not in _REGISTRY:
+        raise ValueError(f"unknown part kind {kind!r}; expected one of {_KINDS}")
+    if name in _REGISTRY[kind] and not replace:
+        raise ValueError(f"{kind} {name!r} is already registered")
+    _REGISTRY[kind][name] = cls
+
+
+def part_class(kind: str, name: str) -> type:
+    try:
+        return _REGISTRY[kind][name]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRY.get(kind, {}))) or "none"
+        raise KeyError(f"no {kind} registered under {name!r} (known: {known})") from None
+
+
+def build_part(kind: str, spec: PartSpec) -> Any:
+    return part_class(kind, spec.kind)(**spec.params)
+
+
+def registered_parts(kind: str) -> tuple[str, ...]:
+    return tuple(sorted(_REGISTRY[kind]))

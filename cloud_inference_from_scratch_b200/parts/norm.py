@@ -1,0 +1,35 @@
+"""RMSNorm over the float32 residual stream, fused with the pending residual add.
+
+Formula (src/cloud_engine/attention.py:52-57): ``w * (x * rsqrt(mean(x^2) + eps))`` with
+the statistics in float32.  The reference keeps the residual in float16 and adds in
+float16 (model.py:217-220); here the stream is float32, the add is a 32-bit sum inside
+the same kernel, and the result is rounded once to the compute dtype.
+"""
+
+from __future__ import annotations
+
+from .base import Norm, TensorSpec, register_part
+
+
+class RMSNorm(Norm):
+    def __init__(self, hidden_size: int, eps: float) -> None:
+        self.hidden_size = int(hidden_size)
+        self.eps = float(eps)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.hidden_size,), init="gain", role="vector")}
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        self.weight = tensors["weight"]
+
+    def forward(self, residual, update, ctx, rows=None):
+        rt = self.runtime
+        count = residual.shape[0] if rows is None else rows.shape[0]
+        out = rt.workspace.get("norm.out" if rows is None else "norm.rows", count,
+                               self.hidden_size, rt.dtype)
+        rt.ops.add_rmsnorm(residual, update, self.weight, self.eps, out, rows)
+        return out
+
+
+register_part("norm", "rmsnorm", RMSNorm, replace=True)
