@@ -1,0 +1,84 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions, error reporting.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+
+namespace cie {
+
+// Element type codes passed through the C interface.
+constexpr int kFloat32 = 0;
+constexpr int kBFloat16 = 1;
+
+// Bits of the device error word that kernels set instead of trapping.
+constexpr int kErrBadPage = 1;      // a block-table entry needed by a token was < 0 or too large
+constexpr int kErrBadToken = 2;     // a token id outside the vocabulary
+constexpr int kErrBadRequest = 4;   // a request index outside the batch
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; every thread gets the result.
+// The order of additions depends only on blockDim, never on the data.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int warps = (blockDim.x + 31) >> 5;
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  const float total = scratch[32];
+  __syncthreads();
+  return total;
+}
+
+}  // namespace cie
+
+// Every library keeps the text of its last failure for the Python side to raise.
+#define CIE_DEFINE_LAST_ERROR()                                                       \
+  static thread_local char cie_error_text[512] = "";                                  \
+  extern "C" const char* cie_last_error() { return cie_error_text; }
+
+#define CIE_FAIL(...)                                                                 \
+  do {                                                                                \
+    snprintf(cie_error_text, sizeof(cie_error_text), __VA_ARGS__);                    \
+    return 1;                                                                         \
+  } while (0)
+
+#define CIE_CHECK_LAUNCH(name)                                                        \
+  do {                                                                                \
+    cudaError_t cie_status = cudaGetLastError();                                      \
+    if (cie_status != cudaSuccess)                                                    \
+      CIE_FAIL("%s: launch failed: %s", name, cudaGetErrorString(cie_status));        \
+  } while (0)

@@ -1,0 +1,205 @@
+// Memory-bound kernels of the forward pass, for float32 and bfloat16 activations:
+// embedding gather into the float32 residual stream, residual-add + RMSNorm, rotary position
+// encoding fused with the write of keys and values into the paged cache, SiLU * up.
+// Statistics, angles and sums are float32; results are rounded once to the activation type.
+//
+// Reference formulas: zeeshan8281/cloud-inference-from-scratch src/cloud_engine/attention.py:52-85
+// (rms_norm, rope), src/cloud_engine/cache.py:398-425 (slot = table[pos/page]*page + pos%page),
+// src/cloud_engine/model.py:100 (SwiGLU), :210 (embedding).
+#include "common.cuh"
+
+CIE_DEFINE_LAST_ERROR()
+
+namespace cie {
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ residual, int hidden, int vocab, int* err) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, kErrBadToken);
+    id = 0;
+  }
+  const T* row = table + (size_t)id * hidden;
+  float* out = residual + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+}
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+// One block per output row.  rows == nullptr: row r is residual row r and residual is updated
+// in place with `update`.  rows != nullptr: row r reads residual row rows[r]; residual is not
+// written.  out = gain * ((x) * rsqrt(mean(x^2) + eps)), x = residual (+ update), all float32.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ update,
+                                   const float* __restrict__ gain, T* __restrict__ out,
+                                   const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  const T* upd = update ? update + (size_t)src * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && (upd != nullptr);
+  float sumsq = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float x = res[i];
+    if (upd) x += to_float(upd[i]);
+    if (write_back) res[i] = x;
+    sumsq += x * x;
+  }
+  const float total = block_sum(sumsq, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  T* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float x = res[i];
+    if (upd && !write_back) x += to_float(upd[i]);
+    dst[i] = from_float<T>(gain[i] * (x * inv));
+  }
+}
+
+// ---------------------------------------------------------------- rotary + paged KV write
+// qkv: [T, (Hq + 2 Hkv) * D], q heads first, then k heads, then v heads.  q is rotated in place.
+// k is rotated and written, v is copied, to pool[page][kv_head][pos % page][D] with
+// page = table[request][pos / page].  Element j < rot/2 pairs with j + rot/2 (rotate-half).
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ request_of_token,
+                                     const int* __restrict__ table, int table_width, int num_pages,
+                                     T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                     const float* __restrict__ inv_freq, int q_heads, int kv_heads,
+                                     int dim, int rot, int page_size, int write_cache, int* err) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int width = (q_heads + 2 * kv_heads) * dim;
+  T* row = qkv + (size_t)t * width;
+  const int half = rot / 2;
+
+  size_t slot_base = 0;
+  bool slot_ok = false;
+  if (write_cache) {
+    const int request = request_of_token[t];
+    const int index = pos / page_size;
+    int page = index < table_width ? table[(size_t)request * table_width + index] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, kErrBadPage);
+    } else {
+      slot_ok = true;
+      slot_base = ((size_t)page * kv_heads) * page_size * dim + (size_t)(pos % page_size) * dim;
+    }
+  }
+  const size_t head_stride = (size_t)page_size * dim;
+
+  // rotated pairs of q and k heads
+  const int rot_heads = q_heads + kv_heads;
+  for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
+    const int h = i / half, j = i % half;
+    const float angle = (float)pos * inv_freq[j];
+    float s, c;
+    sincosf(angle, &s, &c);
+    T* x = row + (size_t)h * dim;
+    const float a = to_float(x[j]), b = to_float(x[j + half]);
+    const T ra = from_float<T>(a * c - b * s), rb = from_float<T>(b * c + a * s);
+    if (h < q_heads) {
+      x[j] = ra;
+      x[j + half] = rb;
+    } else if (slot_ok) {
+      T* dst = k_pool + slot_base + (size_t)(h - q_heads) * head_stride;
+      dst[j] = ra;
+      dst[j + half] = rb;
+    }
+  }
+  if (!slot_ok) return;
+  // the part of k beyond the rotary dims passes through
+  const int tail = dim - rot;
+  for (int i = threadIdx.x; i < kv_heads * tail; i += blockDim.x) {
+    const int h = i / tail, d = rot + i % tail;
+    k_pool[slot_base + (size_t)h * head_stride + d] = row[(size_t)(q_heads + h) * dim + d];
+  }
+  for (int i = threadIdx.x; i < kv_heads * dim; i += blockDim.x) {
+    const int h = i / dim, d = i % dim;
+    v_pool[slot_base + (size_t)h * head_stride + d] = row[(size_t)(q_heads + kv_heads + h) * dim + d];
+  }
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens,
+                                int inter) {
+  const size_t total = (size_t)tokens * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter, c = i % inter;
+    const float g = to_float(gate_up[t * 2 * inter + c]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+    out[i] = from_float<T>((g / (1.f + expf(-g))) * u);
+  }
+}
+
+}  // namespace cie
+
+using namespace cie;
+
+#define DISPATCH_DTYPE(dtype, name, ...)                                  \
+  if (dtype == kFloat32) { using T = float; __VA_ARGS__ }                 \
+  else if (dtype == kBFloat16) { using T = __nv_bfloat16; __VA_ARGS__ }   \
+  else CIE_FAIL("%s: unknown element type code %d", name, dtype);
+
+static int threads_for(int n) {
+  int t = 32;
+  while (t < n && t < 1024) t <<= 1;
+  return t;
+}
+
+extern "C" int cie_embedding(const int* ids, const void* table, float* residual, int tokens,
+                             int hidden, int vocab, int dtype, int* err, void* stream) {
+  if (tokens <= 0) return 0;
+  DISPATCH_DTYPE(dtype, "embedding", {
+    embedding_kernel<T><<<tokens, threads_for(hidden / 4), 0, (cudaStream_t)stream>>>(
+        ids, (const T*)table, residual, hidden, vocab, err);
+  })
+  CIE_CHECK_LAUNCH("embedding");
+  return 0;
+}
+
+extern "C" int cie_add_rmsnorm(float* residual, const void* update, const float* gain, void* out,
+                               const int* rows, int count, int hidden, float eps, int dtype,
+                               void* stream) {
+  if (count <= 0) return 0;
+  DISPATCH_DTYPE(dtype, "add_rmsnorm", {
+    add_rmsnorm_kernel<T><<<count, threads_for(hidden / 4), 0, (cudaStream_t)stream>>>(
+        residual, (const T*)update, gain, (T*)out, rows, hidden, eps);
+  })
+  CIE_CHECK_LAUNCH("add_rmsnorm");
+  return 0;
+}
+
+extern "C" int cie_rope_kv_write(void* qkv, const int* positions, const int* request_of_token,
+                                 const int* table, int table_width, int num_pages, void* k_pool,
+                                 void* v_pool, const float* inv_freq, int tokens, int q_heads,
+                                 int kv_heads, int dim, int rot, int page_size, int write_cache,
+                                 int dtype, int* err, void* stream) {
+  if (tokens <= 0) return 0;
+  if (rot % 2 || rot > dim || rot < 0) CIE_FAIL("rope_kv_write: rotary size %d does not fit head size %d", rot, dim);
+  DISPATCH_DTYPE(dtype, "rope_kv_write", {
+    const int work = (q_heads + kv_heads) * (rot / 2) > kv_heads * dim ? (q_heads + kv_heads) * (rot / 2) : kv_heads * dim;
+    rope_kv_write_kernel<T><<<tokens, threads_for(work), 0, (cudaStream_t)stream>>>(
+        (T*)qkv, positions, request_of_token, table, table_width, num_pages, (T*)k_pool, (T*)v_pool,
+        inv_freq, q_heads, kv_heads, dim, rot, page_size, write_cache, err);
+  })
+  CIE_CHECK_LAUNCH("rope_kv_write");
+  return 0;
+}
+
+extern "C" int cie_silu_mul(const void* gate_up, void* out, int tokens, int inter, int dtype,
+                            void* stream) {
+  if (tokens <= 0) return 0;
+  const size_t total = (size_t)tokens * inter;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  DISPATCH_DTYPE(dtype, "silu_mul", {
+    silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, tokens, inter);
+  })
+  CIE_CHECK_LAUNCH("silu_mul");
+  return 0;
+}

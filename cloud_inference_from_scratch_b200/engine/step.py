@@ -1,0 +1,288 @@
+"""The step function: one flat batch of (request, its next tokens) through the model, from the cache.
+
+Contract (the reference's ``RaggedRunner._pack`` + ``execute_batch``,
+src/cloud_engine/engine.py:231-301, 439-488): a step holds any mix of prompt portions and
+single decoded tokens, no request twice; the cache tables of all its requests grow in one
+all-or-nothing transaction BEFORE anything is launched, so running out of pages is a host
+exception and nothing has changed; keys and values of every token are written; lengths are
+committed after the launch sequence was issued; float32 logits come back only for the rows
+that were asked for.
+
+Differences: all integer metadata of the step is laid out in one pinned buffer and copied to
+the device once (the reference makes seven tensors plus one copy per request row,
+engine.py:264-300); positions and request indices are built with vectorised numpy, not
+per-token Python loops; a step made only of single tokens can be replayed from a CUDA graph
+(``GraphedDecode``), padded to a power-of-two batch by repeating its last row, as the reference
+pads (engine.py:320-356).
+"""
+
+from __future__ import annotations
+
+from collections.abc import Hashable, Sequence
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+
+from ..cache.manager import CacheManager
+from .context import StepContext
+
+
+@dataclass
+class StepEntry:
+    request_id: Hashable
+    token_ids: Sequence[int]
+    want: Sequence[int] = ()          # places among token_ids whose logits are wanted
+    start_pos: int | None = None      # default: the request's committed length
+
+
+@dataclass
+class HostBatch:
+    """The integer arrays of one step on the host (numpy int32)."""
+
+    token_ids: np.ndarray
+    positions: np.ndarray
+    request_of_token: np.ndarray
+    query_start: np.ndarray
+    context_lens: np.ndarray
+    query_lens: np.ndarray
+    slots: np.ndarray
+    logit_rows: np.ndarray
+    tables: list[np.ndarray]
+    extras: dict[Any, dict[str, np.ndarray]] = field(default_factory=dict)
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.token_ids.shape[0])
+
+    @property
+    def num_requests(self) -> int:
+        return int(self.query_lens.shape[0])
+
+
+@dataclass
+class StepResult:
+    logits: Any                                   # float32 [R, vocab] on the device, or None
+    rows: list[tuple[Hashable, int]]              # (request id, place in its entry) per logits row
+
+
+def _align(n: int, to: int = 4) -> int:
+    return (n + to - 1) // to * to
+
+
+class MetadataBuffer:
+    """A pinned host buffer and its device twin; ``upload`` lays the arrays out and copies once."""
+
+    def __init__(self, device: Any, words: int = 1 << 16) -> None:
+        import torch
+
+        self.torch = torch
+        self.device = device
+        self.capacity = 0
+        self.host = None
+        self.dev = None
+        self.event = torch.cuda.Event()
+        self.pending = False
+        self.reserve(words)
+
+    def reserve(self, words: int) -> None:
+        if words <= self.capacity:
+            return
+        torch = self.torch
+        if self.pending:
+            self.event.synchronize()
+            self.pending = False
+        self.capacity = max(words, 2 * self.capacity)
+        self.host = torch.empty(self.capacity, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty(self.capacity, dtype=torch.int32, device=self.device)
+
+    def upload(self, arrays: list[np.ndarray]) -> list[Any]:
+        """Copies the arrays (any shape, int32) and returns device views of the same shapes."""
+        offsets = []
+        total = 0
+        for array in arrays:
+            offsets.append(total)
+            total += _align(array.size)
+        self.reserve(max(total, 4))
+        if self.pending:
+            self.event.synchronize()  # the previous copy must have left the pinned buffer
+        for array, offset in zip(arrays, offsets, strict=True):
+            if array.size:
+                self.host_np[offset:offset + array.size] = array.reshape(-1)
+        if total:
+            self.dev[:total].copy_(self.host[:total], non_blocking=True)
+            self.event.record()
+            self.pending = True
+        return [
+            self.dev[offset:offset + array.size].view(array.shape)
+            for array, offset in zip(arrays, offsets, strict=True)
+        ]
+
+
+class StepFunction:
+    def __init__(self, model: Any, runtime: Any, cache: CacheManager, pools: Any) -> None:
+        self.model = model
+        self.runtime = runtime
+        self.cache = cache
+        self.pools = pools
+        self.vocab_size = model.spec.vocab_size
+        self.num_groups = len(cache.groups)
+        self.meta = MetadataBuffer(runtime.device)
+        self.planners = self._collect_planners()
+        self.steps_run = 0
+        self.tokens_run = 0
+        self.h2d_bytes = 0
+
+    def _collect_planners(self) -> dict[Any, Any]:
+        """Mixers may add integer work lists of their own to a step's metadata: a mixer with
+        ``plan_key`` and ``plan(host, cache)`` is asked once per distinct key."""
+        planners: dict[Any, Any] = {}
+        for layer in self.model.layers:
+            key = getattr(layer.mixer, "plan_key", None)
+            if key is not None and key not in planners:
+                planners[key] = layer.mixer
+        return planners
+
+    # ------------------------------------------------------------------ admission
+    def admit(self, request_id: Hashable) -> int:
+        return self.cache.admit(request_id)
+
+    def release(self, request_id: Hashable) -> None:
+        self.cache.release(request_id)
+
+    # ------------------------------------------------------------------ packing
+    def build_host_batch(self, entries: Sequence[StepEntry], table_width: int | None = None
+                         ) -> tuple[HostBatch, list[tuple[Hashable, int]], dict[Hashable, tuple[int, int]]]:
+        cache = self.cache
+        seen: set[Hashable] = set()
+        starts: list[int] = []
+        lens: list[int] = []
+        for entry in entries:
+            if entry.request_id in seen:
+                raise ValueError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            if not cache.is_admitted(entry.request_id):
+                raise KeyError(f"request {entry.request_id!r} is not admitted")
+            committed = cache.committed_length(entry.request_id)
+            start = committed if entry.start_pos is None else int(entry.start_pos)
+            if start != committed:
+                raise ValueError(
+                    f"request {entry.request_id!r}: tokens start at position {start} but the "
+                    f"cache holds {committed}"
+                )
+            if len(entry.token_ids) == 0:
+                raise ValueError(f"request {entry.request_id!r} brings no tokens")
+            starts.append(start)
+            lens.append(len(entry.token_ids))
+        query_lens = np.asarray(lens, dtype=np.int32)
+        context_lens = np.asarray(starts, dtype=np.int32)
+        query_start = np.zeros(len(entries) + 1, dtype=np.int32)
+        np.cumsum(query_lens, out=query_start[1:])
+        total = int(query_start[-1])
+        token_ids = np.fromiter(
+            (t for entry in entries for t in entry.token_ids), dtype=np.int64, count=total
+        )
+        if total and (token_ids.min() < 0 or token_ids.max() >= self.vocab_size):
+            raise ValueError(f"token id outside the vocabulary of {self.vocab_size}")
+        request_of_token = np.repeat(np.arange(len(entries), dtype=np.int32), query_lens)
+        positions = (
+            np.arange(total, dtype=np.int32)
+            - np.repeat(query_start[:-1] - context_lens, query_lens)
+        ).astype(np.int32)
+        rows: list[tuple[Hashable, int]] = []
+        logit_rows: list[int] = []
+        for index, entry in enumerate(entries):
+            for place in entry.want:
+                if not 0 <= place < lens[index]:
+                    raise ValueError(
+                        f"request {entry.request_id!r}: wanted place {place} is outside its "
+                        f"{lens[index]} tokens"
+                    )
+                rows.append((entry.request_id, int(place)))
+                logit_rows.append(int(query_start[index]) + int(place))
+        spans = {
+            entry.request_id: (starts[i], starts[i] + lens[i]) for i, entry in enumerate(entries)
+        }
+        slots = np.asarray([cache.slot(entry.request_id) for entry in entries], dtype=np.int32)
+        host = HostBatch(
+            token_ids=token_ids.astype(np.int32),
+            positions=positions,
+            request_of_token=request_of_token,
+            query_start=query_start,
+            context_lens=context_lens,
+            query_lens=query_lens,
+            slots=slots,
+            logit_rows=np.asarray(logit_rows, dtype=np.int32),
+            tables=[],
+        )
+        host._table_width = table_width  # type: ignore[attr-defined]
+        return host, rows, spans
+
+    def _fill_tables(self, host: HostBatch, spans: dict[Hashable, tuple[int, int]]) -> None:
+        width = getattr(host, "_table_width", None)
+        if width is None:
+            width = self.cache.width_for(max(end for _, end in spans.values()))
+        host.tables = [
+            np.ascontiguousarray(self.cache.table_rows(group, host.slots, width))
+            for group in range(self.num_groups)
+        ]
+        for key, mixer in self.planners.items():
+            host.extras[key] = mixer.plan(host, self.cache)
+
+    def upload(self, host: HostBatch, meta: MetadataBuffer | None = None) -> StepContext:
+        meta = meta or self.meta
+        extra_items = [(key, name, array) for key, arrays in host.extras.items()
+                       for name, array in arrays.items()]
+        arrays = [
+            host.token_ids, host.positions, host.request_of_token, host.query_start,
+            host.context_lens, host.query_lens, host.slots, host.logit_rows, *host.tables,
+            *[array for _, _, array in extra_items],
+        ]
+        views = meta.upload(arrays)
+        self.h2d_bytes = sum(_align(a.size) for a in arrays) * 4
+        extras: dict[Any, dict[str, Any]] = {}
+        for (key, name, _), view in zip(extra_items, views[8 + len(host.tables):], strict=True):
+            extras.setdefault(key, {})[name] = view
+        return StepContext(
+            num_tokens=host.num_tokens,
+            num_requests=host.num_requests,
+            num_logit_rows=int(host.logit_rows.shape[0]),
+            token_ids=views[0],
+            positions=views[1],
+            request_of_token=views[2],
+            query_start=views[3],
+            context_lens=views[4],
+            query_lens=views[5],
+            slots=views[6],
+            logit_rows=views[7],
+            block_tables=list(views[8:8 + len(host.tables)]),
+            host=host,
+            bindings=self.pools.bindings,
+            all_decode=bool((host.query_lens == 1).all()),
+            extras=extras,
+        )
+
+    # ------------------------------------------------------------------ the step
+    def prepare(self, entries: Sequence[StepEntry], table_width: int | None = None
+                ) -> tuple[HostBatch, list[tuple[Hashable, int]], dict[Hashable, tuple[int, int]]]:
+        """Everything that can fail on the host: checks the entries, grows the tables
+        (``CacheCapacityFull`` leaves the cache untouched) and builds the host arrays."""
+        host, rows, spans = self.build_host_batch(entries, table_width)
+        self.cache.ensure_capacity_batch(spans)
+        dirty = self.cache.take_dirty_slots()
+        if dirty:
+            self.pools.zero_slots(dirty)
+        self._fill_tables(host, spans)
+        return host, rows, spans
+
+    def run(self, entries: Sequence[StepEntry]) -> StepResult:
+        if not entries:
+            return StepResult(None, [])
+        host, rows, spans = self.prepare(entries)
+        ctx = self.upload(host)
+        logits = self.model.forward(ctx)
+        self.cache.commit_lengths({request_id: end for request_id, (_, end) in spans.items()})
+        self.steps_run += 1
+        self.tokens_run += host.num_tokens
+        return StepResult(logits, rows)
