@@ -1,0 +1,208 @@
+"""The scheduler's runner: turns a batch plan into one step, samples on the device, returns ids.
+
+Interface towards the scheduler (duck-typed, as in the reference, src/cloud_engine/scheduler.py:287-290,
+449, 523, 531): ``admit``, ``release``, ``allocated_tokens``, ``execute_batch(plan) -> {request id:
+token id}``.  Counterpart of ``RaggedRunner`` (src/cloud_engine/engine.py:193-488).
+
+A plan made only of single decoded tokens is replayed from a CUDA graph captured per
+power-of-two batch size (engine.py:320-408): the step's metadata goes into the graph's fixed
+buffers with one copy, rows beyond the real batch repeat the last real row (they rewrite the
+same cache slot with the same values and their tokens are dropped).  Graphs are not used when
+a mixer keeps per-request state, because a repeated row would advance that state twice.
+Sampling parameters (temperature and draw key per row) ride in the same metadata copy; only
+the sampled token ids and the device error word come back to the host.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import numpy as np
+
+from ..sampling.keys import as_signed, draw_key
+from .profiling import nvtx_range
+from .step import MetadataBuffer, StepEntry
+
+
+class _DecodeGraph:
+    def __init__(self, bucket: int, meta: MetadataBuffer, graph: Any, result_dev: Any) -> None:
+        self.bucket = bucket
+        self.meta = meta
+        self.graph = graph
+        self.result_dev = result_dev
+
+
+class EngineRunner:
+    def __init__(self, core: Any, config: Any) -> None:
+        import torch
+
+        self.torch = torch
+        self.core = core
+        self.config = config
+        self.step = core.step
+        self.ops = core.runtime.ops
+        self.max_rows = max(1, config.max_active_sequences)
+        self.result_dev = torch.zeros(1 + self.max_rows, dtype=torch.int32, device=core.runtime.device)
+        self.result_host = torch.zeros(1 + self.max_rows, dtype=torch.int32, pin_memory=True)
+        self.ops.error_word = self.result_dev[0:1]
+        has_state = any(need.state is not None for need in core.model.cache_needs())
+        self.use_graphs = bool(config.cuda_graph_decode) and not has_state
+        self.table_width = -(-config.max_model_len // core.page_size)
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.forward_invocations = 0
+        self.max_forward_request_count = 0
+        self.cuda_graph_captures = 0
+        self.cuda_graph_replays = 0
+        self.forward_plans: list[tuple[tuple[str, int, int, bool], ...]] = []
+        self.d2h_bytes = 0
+
+    # ------------------------------------------------------------------ scheduler interface
+    def admit(self, request: Any) -> None:
+        self.step.admit(request.request_id)
+
+    def release(self, request: Any) -> None:
+        self.step.release(request.request_id)
+
+    def allocated_tokens(self, request: Any) -> int:
+        return self.core.cache.allocated_tokens(request.request_id)
+
+    def execute_batch(self, plan: Any) -> dict[str, int]:
+        items = plan.items
+        entries = [
+            StepEntry(item.request.request_id, item.token_ids,
+                      want=(len(item.token_ids) - 1,) if item.sample else (), start_pos=item.start_pos)
+            for item in items
+        ]
+        sampled = [item for item in items if item.sample]
+        self.forward_invocations += 1
+        self.max_forward_request_count = max(self.max_forward_request_count, len(items))
+        self.forward_plans.append(
+            tuple((i.request.request_id, i.start_pos, i.query_length, i.sample) for i in items)
+        )
+        if len(self.forward_plans) > 256:
+            del self.forward_plans[:128]
+        decode_only = all(item.query_length == 1 and item.sample for item in items)
+        phase = "decode" if decode_only else "mixed"
+        with nvtx_range(f"ragged.forward.{phase}.requests_{len(items)}.tokens_{plan.token_count}"):
+            if decode_only and self.use_graphs and len(items) <= self.max_rows:
+                tokens = self._graphed_decode(entries, sampled)
+            else:
+                tokens = self._eager(entries, sampled)
+        return {item.request.request_id: int(tokens[i]) for i, item in enumerate(sampled)}
+
+    # ------------------------------------------------------------------ sampling parameters
+    @staticmethod
+    def _sampling_arrays(sampled: list[Any], rows: int) -> dict[str, np.ndarray]:
+        temperature = np.zeros(rows, dtype=np.float32)
+        keys = np.zeros(rows, dtype=np.int64)
+        for index, item in enumerate(sampled):
+            request = item.request
+            temperature[index] = request.config.temperature
+            if request.config.temperature > 0:
+                keys[index] = as_signed(
+                    draw_key(request.config.seed, request.sequence_number, request.generated_count)
+                )
+        return {"temperature": temperature.view(np.int32), "keys": keys.view(np.int32)}
+
+    def _launch_sampling(self, logits: Any, ctx: Any, result_dev: Any, rows: int) -> None:
+        torch = self.torch
+        params = ctx.extras["sampling"]
+        self.ops.sample(logits, params["temperature"].view(torch.float32),
+                        params["keys"].view(torch.int64), result_dev[1:1 + rows])
+
+    def _read_back(self, result_dev: Any, rows: int) -> np.ndarray:
+        with nvtx_range("ragged.sample.readback"):
+            self.result_host[:1 + rows].copy_(result_dev[:1 + rows], non_blocking=True)
+            self.torch.cuda.current_stream().synchronize()
+        self.d2h_bytes = 4 * (1 + rows)
+        values = self.result_host[:1 + rows].numpy()
+        if values[0]:
+            self.ops.error_word = result_dev[0:1]
+            self.ops.check_errors()
+        return values[1:].copy()
+
+    # ------------------------------------------------------------------ eager (mixed) step
+    def _eager(self, entries: list[StepEntry], sampled: list[Any]) -> np.ndarray:
+        step = self.step
+        with nvtx_range("ragged.kv.ensure_capacity"):
+            host, _, spans = step.prepare(entries)
+        rows = len(sampled)
+        host.extras["sampling"] = self._sampling_arrays(sampled, rows)
+        ctx = step.upload(host)
+        self.ops.error_word = self.result_dev[0:1]
+        logits = self.core.model.forward(ctx)
+        with nvtx_range("ragged.kv.commit"):
+            self.core.cache.commit_lengths({rid: end for rid, (_, end) in spans.items()})
+        step.steps_run += 1
+        step.tokens_run += host.num_tokens
+        if rows:
+            self._launch_sampling(logits, ctx, self.result_dev, rows)
+        return self._read_back(self.result_dev, rows)
+
+    # ------------------------------------------------------------------ graphed decode
+    @staticmethod
+    def _bucket(batch: int) -> int:
+        return 1 << (batch - 1).bit_length()
+
+    def _pad(self, host: Any, bucket: int) -> None:
+        """Repeats the last row until the batch has ``bucket`` requests of one token each."""
+        real = host.num_requests
+        extra = bucket - real
+        if extra <= 0:
+            return
+
+        def grow(array: np.ndarray) -> np.ndarray:
+            return np.concatenate([array, np.repeat(array[-1:], extra, axis=0)])
+
+        host.token_ids = grow(host.token_ids)
+        host.positions = grow(host.positions)
+        host.context_lens = grow(host.context_lens)
+        host.query_lens = grow(host.query_lens)
+        host.slots = grow(host.slots)
+        host.request_of_token = np.arange(bucket, dtype=np.int32)
+        host.query_start = np.arange(bucket + 1, dtype=np.int32)
+        host.logit_rows = np.arange(bucket, dtype=np.int32)
+        host.tables = [grow(table) for table in host.tables]
+
+    def _graphed_decode(self, entries: list[StepEntry], sampled: list[Any]) -> np.ndarray:
+        torch = self.torch
+        step = self.step
+        real = len(entries)
+        bucket = self._bucket(real)
+        with nvtx_range("ragged.kv.ensure_capacity"):
+            host, _, spans = step.prepare(entries, table_width=self.table_width)
+        self._pad(host, bucket)
+        host.extras["sampling"] = self._sampling_arrays(sampled, bucket)
+        for key, mixer in step.planners.items():
+            host.extras[key] = mixer.plan(host, self.core.cache)
+        cached = self._graphs.get(bucket)
+        if cached is None:
+            meta = MetadataBuffer(self.core.runtime.device, words=1 << 12)
+            result_dev = torch.zeros(1 + bucket, dtype=torch.int32, device=self.core.runtime.device)
+            ctx = step.upload(host, meta)
+            self.ops.error_word = result_dev[0:1]
+            # once eagerly (allocates workspace, loads kernels), then capture the same launches
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                logits = self.core.model.forward(ctx)
+                self._launch_sampling(logits, ctx, result_dev, bucket)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            self.core.runtime.workspace.frozen = True
+            with torch.cuda.graph(graph):
+                logits = self.core.model.forward(ctx)
+                self._launch_sampling(logits, ctx, result_dev, bucket)
+            cached = _DecodeGraph(bucket, meta, graph, result_dev)
+            self._graphs[bucket] = cached
+            self.cuda_graph_captures += 1
+        else:
+            step.upload(host, cached.meta)
+        cached.graph.replay()
+        self.cuda_graph_replays += 1
+        with nvtx_range("ragged.kv.commit"):
+            self.core.cache.commit_lengths({rid: end for rid, (_, end) in spans.items()})
+        step.steps_run += 1
+        step.tokens_run += real
+        return self._read_back(cached.result_dev, bucket)[:real]
