@@ -56,6 +56,7 @@ class PageAllocator:
         self.page_size = int(page_size)
         self._free: list[int] = list(range(num_pages - 1, -1, -1))
         self._owner: dict[int, Hashable] = {}
+        self.allocations_total = 0  # pages handed out since the start (reuse shows as > total)
 
     @property
     def free_count(self) -> int:
@@ -80,6 +81,7 @@ class PageAllocator:
         if count > len(self._free):
             raise CacheCapacityFull(f"requested {count} pages, only {len(self._free)} free")
         pages = [self._free.pop() for _ in range(count)]
+        self.allocations_total += count
         for page in pages:
             self._owner[page] = owner
         return pages

@@ -1,0 +1,319 @@
+"""Each kernel alone against a plain float32 reference, at sizes other than the models' own."""
+
+import math
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from cloud_inference_from_scratch_b200.sampling import as_signed, draw_key, uniform_from_key
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cloud_inference_from_scratch_b200.native import Ops
+
+    made = {dtype: Ops("cuda:0", dtype) for dtype in DTYPES}
+    yield made
+    for item in made.values():
+        item.check_errors()
+
+
+def rand(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    generator = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=generator) * scale).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    table = rand(1000, 200, dtype=dtype)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32).cuda()
+    out = torch.empty(5, 200, dtype=torch.float32).cuda()
+    ops[dtype].embedding(ids, table, out)
+    torch.testing.assert_close(out, plain_model.embedding(table.float().cpu(), ids.cpu().tolist()).cuda())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [96, 200, 2048, 5000])
+def test_add_rmsnorm(ops, dtype, hidden):
+    residual = rand(7, hidden, seed=1)
+    update = rand(7, hidden, dtype=dtype, seed=2)
+    gain = 1 + rand(hidden, scale=0.1, seed=3)
+    eps = 1e-5
+    expect_res = residual + update.float()
+    expect = plain_model.rms_norm(expect_res.cpu(), gain.cpu(), eps).cuda()
+    out = torch.empty(7, hidden, dtype=dtype).cuda()
+    work = residual.clone()
+    ops[dtype].add_rmsnorm(work, update, gain, eps, out)
+    torch.testing.assert_close(work, expect_res)                 # 32-bit sum, written back
+    torch.testing.assert_close(out.float(), expect, **tol(dtype))
+    out2 = torch.empty(7, hidden, dtype=dtype).cuda()            # no update: residual untouched
+    work = residual.clone()
+    ops[dtype].add_rmsnorm(work, None, gain, eps, out2)
+    assert torch.equal(work, residual)
+    torch.testing.assert_close(out2.float(), plain_model.rms_norm(residual.cpu(), gain.cpu(), eps).cuda(), **tol(dtype))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32).cuda()     # selected rows: nothing written back
+    out3 = torch.empty(3, hidden, dtype=dtype).cuda()
+    work = residual.clone()
+    ops[dtype].add_rmsnorm(work, update, gain, eps, out3, rows)
+    assert torch.equal(work, residual)
+    torch.testing.assert_close(out3.float(), expect[rows.long()], **tol(dtype))
+
+
+def paged_setup(lengths, page, heads, dim, dtype, seed=0, extra_pages=3):
+    """Random keys/values scattered over a shuffled page pool; returns pools, tables, dense copies."""
+    generator = torch.Generator().manual_seed(seed)
+    pages_per = [-(-n // page) for n in lengths]
+    total = sum(pages_per) + extra_pages
+    order = torch.randperm(total, generator=generator).tolist()
+    width = max(pages_per) + 1
+    table = torch.full((len(lengths), width), -1, dtype=torch.int32)
+    k_pool = torch.zeros(total, heads, page, dim)
+    v_pool = torch.zeros(total, heads, page, dim)
+    dense = []
+    cursor = 0
+    for r, n in enumerate(lengths):
+        k = torch.randn(n, heads, dim, generator=generator)
+        v = torch.randn(n, heads, dim, generator=generator)
+        dense.append((k, v))
+        for p in range(pages_per[r]):
+            page_id = order[cursor]
+            cursor += 1
+            table[r, p] = page_id
+            count = min(page, n - p * page)
+            k_pool[page_id, :, :count] = k[p * page:p * page + count].transpose(0, 1)
+            v_pool[page_id, :, :count] = v[p * page:p * page + count].transpose(0, 1)
+    return k_pool.to(dtype).cuda(), v_pool.to(dtype).cuda(), table.cuda(), dense, total
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("page,dim,rot", [(4, 48, 32), (16, 128, 128), (32, 16, 16)])
+def test_rope_kv_write(ops, dtype, page, dim, rot):
+    q_heads, kv_heads = 6, 3
+    starts, lens = [0, 37, 5], [9, 2, 20]
+    width = (q_heads + 2 * kv_heads) * dim
+    tokens = sum(lens)
+    qkv = rand(tokens, width, dtype=dtype, seed=4)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).int().cuda()
+    request = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().cuda()
+    k_pool, v_pool, table, _, total = paged_setup([s + n for s, n in zip(starts, lens)], page, kv_heads, dim, dtype)
+    before_k, before_v = k_pool.clone(), v_pool.clone()
+    theta = 50000.0
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).cuda()
+    position = SimpleNamespace(rotary_dim=rot, inv_freq=inv_freq)
+    ctx = SimpleNamespace(positions=positions, request_of_token=request, block_tables=[table])
+    kv = SimpleNamespace(group=0, k=k_pool, v=v_pool, num_pages=total, page_size=page)
+    original = qkv.clone()
+    ops[dtype].rope_kv_write(qkv, ctx, kv, position, q_heads, kv_heads, dim, write_cache=True)
+    torch.cuda.synchronize()
+    src = original.float().cpu().view(tokens, q_heads + 2 * kv_heads, dim)
+    cos, sin = plain_model.rope_tables(rot, positions.cpu().tolist(), theta)
+    want_q = plain_model.apply_rope(src[:, :q_heads], cos, sin)
+    want_k = plain_model.apply_rope(src[:, q_heads:q_heads + kv_heads], cos, sin)
+    want_v = src[:, q_heads + kv_heads:]
+    got = qkv.float().cpu().view(tokens, q_heads + 2 * kv_heads, dim)
+    torch.testing.assert_close(got[:, :q_heads], want_q, **tol(dtype))
+    assert torch.equal(got[:, q_heads:], src[:, q_heads:])      # k and v stay as they were in qkv
+    touched = torch.zeros_like(k_pool, dtype=torch.bool)
+    for t in range(tokens):
+        r, pos = int(request[t]), int(positions[t])
+        page_id = int(table[r, pos // page])
+        torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], **tol(dtype))
+        assert torch.equal(v_pool[page_id, :, pos % page].float().cpu(), want_v[t])
+        touched[page_id, :, pos % page] = True
+    assert torch.equal(k_pool[~touched], before_k[~touched])   # nothing else was written
+    assert torch.equal(v_pool[~touched], before_v[~touched])
+    k2, v2 = before_k.clone(), before_v.clone()                 # a run that reads another's cache
+    kv2 = SimpleNamespace(group=0, k=k2, v=v2, num_pages=total, page_size=page)
+    again = original.clone()
+    ops[dtype].rope_kv_write(again, ctx, kv2, position, q_heads, kv_heads, dim, write_cache=False)
+    assert torch.equal(k2, before_k) and torch.equal(v2, before_v)
+    assert torch.equal(again, qkv)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 64, 65, 130])
+def test_gemm_simt_any_shape(ops, dtype, m):
+    n, k = 331, 100
+    x, w = rand(m, k, dtype=dtype, seed=5), rand(n, k, dtype=dtype, scale=0.1, seed=6)
+    bias = rand(n, seed=7)
+    want = plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).cuda()
+    item = ops[dtype]
+    out = torch.empty(m, n, dtype=dtype).cuda()
+    item._gemm_simt(x.data_ptr(), w.data_ptr(), bias.data_ptr(), out.data_ptr(), m, n, k,
+                    item._code_of(x), item._code_of(out), 1, item.stream)
+    torch.testing.assert_close(out.float(), want, **tol(dtype))
+    wide = torch.empty(m, n, dtype=torch.float32).cuda()        # float32 output (logits)
+    item._gemm_simt(x.data_ptr(), w.data_ptr(), None, wide.data_ptr(), m, n, k, item._code_of(x), 0, 0,
+                    item.stream)
+    torch.testing.assert_close(wide, plain_model.linear(x.float().cpu(), w.float().cpu()).cuda(),
+                               rtol=2e-5, atol=2e-5)
+
+
+def test_gemm_float32_rows_do_not_depend_on_the_batch(ops):
+    item = ops[torch.float32]
+    x, w = rand(70, 300, seed=8), rand(200, 300, scale=0.1, seed=9)
+    full = torch.empty(70, 200).cuda()
+    item.linear(x, w, None, full)
+    for rows in (1, 2, 33):
+        part = torch.empty(rows, 200).cuda()
+        item.linear(x[:rows].contiguous(), w, None, part)
+        assert torch.equal(part, full[:rows])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_of_the_engine(ops, dtype):
+    """Whatever kernel ``linear`` picks for the dtype: bias, float32 output, odd sizes."""
+    item = ops[dtype]
+    for m, n, k in [(1, 331, 96), (5, 64, 200), (130, 1000, 128), (64, 2048, 2048)]:
+        x, w = rand(m, k, dtype=dtype, seed=m), item.prepare_weight(rand(n, k, scale=0.05, seed=n))
+        bias = rand(n, seed=k)
+        out = torch.empty(m, n, dtype=dtype).cuda()
+        item.linear(x, w, bias, out)
+        want = plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).cuda()
+        torch.testing.assert_close(out.float(), want, **tol(dtype))
+        logits = torch.empty(m, n, dtype=torch.float32).cuda()
+        item.linear(x, w, None, logits)
+        torch.testing.assert_close(logits, plain_model.linear(x.float().cpu(), w.float().cpu()).cuda(),
+                                   rtol=1e-3 if dtype == torch.bfloat16 else 2e-5, atol=1e-3 if dtype == torch.bfloat16 else 2e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    gate_up = rand(9, 2 * 208, dtype=dtype, scale=3.0, seed=10)
+    out = torch.empty(9, 208, dtype=dtype).cuda()
+    ops[dtype].silu_mul(gate_up, out)
+    g, u = gate_up.float()[:, :208], gate_up.float()[:, 208:]
+    torch.testing.assert_close(out.float(), torch.nn.functional.silu(g) * u, **tol(dtype))
+
+
+def attention_case(ops, dtype, contexts, query_lens, q_heads, kv_heads, dim, page, window=0, seed=0,
+                   plant=None, fn="attention_generic"):
+    lengths = [c + q for c, q in zip(contexts, query_lens)]
+    k_pool, v_pool, table, dense, total = paged_setup(lengths, page, kv_heads, dim, dtype, seed=seed)
+    tokens = sum(query_lens)
+    q = rand(tokens, q_heads * dim, dtype=dtype, seed=seed + 1)
+    if plant is not None:   # make one far key the only one that matters for the last query
+        request, key_pos, strength = plant
+        row = sum(query_lens[:request + 1]) - 1
+        key = dense[request][0][key_pos, 0]
+        q[row, :dim] = (key * strength).to(dtype).cuda()
+    positions = torch.cat([torch.arange(c, c + n) for c, n in zip(contexts, query_lens)]).int().cuda()
+    request_of = torch.cat([torch.full((n,), i) for i, n in enumerate(query_lens)]).int().cuda()
+    host = SimpleNamespace(query_lens=np.asarray(query_lens, dtype=np.int32),
+                           context_lens=np.asarray(contexts, dtype=np.int32),
+                           query_start=np.concatenate([[0], np.cumsum(query_lens)]).astype(np.int32))
+    ctx = SimpleNamespace(positions=positions, request_of_token=request_of, block_tables=[table],
+                          host=host, all_decode=all(n == 1 for n in query_lens), extras={},
+                          num_tokens=tokens, num_requests=len(query_lens),
+                          context_lens=torch.tensor(contexts, dtype=torch.int32).cuda(),
+                          query_lens=torch.tensor(query_lens, dtype=torch.int32).cuda(),
+                          query_start=torch.tensor(host.query_start).cuda())
+    kv = SimpleNamespace(group=0, k=k_pool, v=v_pool, num_pages=total, page_size=page)
+    out = torch.zeros(tokens, q_heads * dim, dtype=dtype).cuda()
+    scale = 1.0 / math.sqrt(dim)
+    getattr(ops[dtype], fn)(q, out, ctx, kv, q_heads, kv_heads, dim, scale, window)
+    torch.cuda.synchronize()
+    ops[dtype].check_errors()
+    start = 0
+    worst = 0.0
+    for r, (context, n) in enumerate(zip(contexts, query_lens)):
+        k = k_pool_dense(dense[r][0], dtype)
+        v = k_pool_dense(dense[r][1], dtype)
+        full_q = torch.zeros(context + n, q_heads, dim)
+        full_q[context:] = q[start:start + n].float().cpu().view(n, q_heads, dim)
+        want = plain_model.attention(full_q, k, v, scale, window=window)[context:]
+        got = out[start:start + n].float().cpu()
+        worst = max(worst, float((got - want).abs().max()))
+        torch.testing.assert_close(got, want, **tol(dtype))
+        start += n
+    return worst
+
+
+def k_pool_dense(values, dtype):
+    return values.to(dtype).float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("query_len", [1, 2, 7, 16])
+def test_attention_generic_context_matrix(ops, dtype, query_len):
+    contexts = [0, 15, 16, 17, 127, 128, 511, 1024]
+    attention_case(ops, dtype, contexts, [query_len] * len(contexts), q_heads=4, kv_heads=2, dim=64, page=16)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim,page,q_heads,kv_heads", [(16, 4, 6, 3), (48, 8, 5, 5), (128, 32, 8, 1), (256, 16, 2, 1), (80, 5, 3, 1)])
+def test_attention_generic_sizes(ops, dtype, dim, page, q_heads, kv_heads):
+    attention_case(ops, dtype, [3, 0, 200, 61], [5, 1, 1, 40], q_heads, kv_heads, dim, page, seed=3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 100])
+def test_attention_generic_window(ops, dtype, window):
+    attention_case(ops, dtype, [0, 33, 150], [20, 9, 1], 4, 2, 32, 8, window=window, seed=5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_generic_far_key(ops, dtype):
+    """The last query is aligned with key 3 of 900: its output must be that key's value."""
+    attention_case(ops, dtype, [899, 10], [1, 4], 2, 1, 64, 16, seed=6, plant=(0, 3, 4.0))
+
+
+def test_sampling_greedy_ties_take_the_lowest_index(ops):
+    item = ops[torch.float32]
+    logits = torch.full((3, 5003), -1.0).cuda()
+    logits[0, 4000] = 2.0
+    logits[0, 77] = 2.0
+    logits[1, 5002] = 0.5
+    logits[2, 0] = -0.5
+    out = torch.zeros(3, dtype=torch.int32).cuda()
+    item.sample(logits, None, None, out)
+    assert out.tolist() == [77, 5002, 0]
+    temperature = torch.zeros(3).cuda()
+    keys = torch.zeros(3, dtype=torch.int64).cuda()
+    item.sample(logits, temperature, keys, out)      # temperature 0 rows are greedy too
+    assert out.tolist() == [77, 5002, 0]
+
+
+@pytest.mark.parametrize("vocab", [331, 1000, 151936])
+def test_sampling_temperature_is_the_inverse_cdf_of_the_keyed_draw(ops, vocab):
+    item = ops[torch.float32]
+    rows = 24
+    logits = rand(rows, vocab, scale=2.0, seed=11)
+    temps = torch.tensor([0.8 if r % 3 else 1.7 for r in range(rows)]).cuda()
+    keys_int = [draw_key(5, r // 2, r) for r in range(rows)]
+    keys = torch.tensor([as_signed(k) for k in keys_int], dtype=torch.int64).cuda()
+    out = torch.zeros(rows, dtype=torch.int32).cuda()
+    item.sample(logits, temps, keys, out)
+    again = torch.zeros(rows, dtype=torch.int32).cuda()
+    item.sample(logits, temps, keys, again)
+    assert torch.equal(out, again)
+    for r in range(rows):
+        probs = plain_model.temperature_probs(logits[r].cpu().double(), float(temps[r])).double()
+        cdf = torch.cumsum(probs, 0)
+        u = uniform_from_key(keys_int[r])
+        token = int(out[r])
+        low = float(cdf[token - 1]) if token else 0.0
+        assert low - 1e-5 <= u <= float(cdf[token]) + 1e-5, (r, token, low, u, float(cdf[token]))
+    picks = {int(t) for t in out}
+    assert len(picks) > rows // 2
+
+
+def test_sampling_draws_follow_the_distribution(ops):
+    item = ops[torch.float32]
+    logits = torch.tensor([[0.0, math.log(2.0), math.log(5.0), -30.0]]).repeat(4000, 1).cuda()
+    temps = torch.ones(4000).cuda()
+    keys = torch.tensor([as_signed(draw_key(9, 1, i)) for i in range(4000)], dtype=torch.int64).cuda()
+    out = torch.zeros(4000, dtype=torch.int32).cuda()
+    item.sample(logits, temps, keys, out)
+    counts = torch.bincount(out.long().cpu(), minlength=4).float() / 4000
+    torch.testing.assert_close(counts, torch.tensor([0.125, 0.25, 0.625, 0.0]), atol=0.03, rtol=0)
