@@ -54,6 +54,7 @@ class EngineRunner:
         self.cuda_graph_captures = 0
         self.cuda_graph_replays = 0
         self.forward_plans: list[tuple[tuple[str, int, int, bool], ...]] = []
+        self.launches_per_graph: dict[int, int] = {}  # kernels of ours inside each captured graph
         self.d2h_bytes = 0
 
     # ------------------------------------------------------------------ scheduler interface
@@ -191,9 +192,11 @@ class EngineRunner:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             self.core.runtime.workspace.frozen = True
+            launches_before = self.ops.launches
             with torch.cuda.graph(graph):
                 logits = self.core.model.forward(ctx)
                 self._launch_sampling(logits, ctx, result_dev, bucket)
+            self.launches_per_graph[bucket] = self.ops.launches - launches_before
             cached = _DecodeGraph(bucket, meta, graph, result_dev)
             self._graphs[bucket] = cached
             self.cuda_graph_captures += 1
