@@ -1,0 +1,578 @@
+// Tensor-core attention over the paged cache for bfloat16, one head size per build (-DHEAD_DIM).
+//
+//  * prefill_kernel: ragged causal attention of prompt portions (cached prefix + the portion
+//    itself).  One CTA takes a tile of query rows of ONE request and ONE kv head; a row is a
+//    (token, query head of the group) pair, so the heads of a group share every K/V load.
+//    K/V tiles of 64 keys are gathered row by row from the pages with cp.async (any page
+//    size), double buffered; QK^T and PV run on mma.sync m16n8k16 with float32 accumulators
+//    and a float32 running-maximum softmax.
+//  * decode_kernel + combine_kernel: one query token per request.  The keys of a request are
+//    split over CTAs (grid.x) and, inside a CTA, over 4 warps that each stream 16-key tiles
+//    through a private double buffer; partial (max, sum, output) triples are merged in shared
+//    memory, then across CTAs by combine_kernel through a float32 scratch buffer.
+//
+// Formula: zeeshan8281/cloud-inference-from-scratch src/cloud_engine/kernel.py:324-405 (one
+// program per query token and head, CUDA-core reductions, page size fixed at 16, head size
+// 64 or 128).  Here head sizes are the multiples of 16 up to 256, any page size and grouping.
+#include "common.cuh"
+
+#include <cfloat>
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+
+CIE_DEFINE_LAST_ERROR()
+
+namespace cie {
+
+using bf16 = __nv_bfloat16;
+constexpr int D = HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int ROW = D + 8;          // shared-memory row in elements: odd number of 16-byte units
+constexpr int CHUNKS = D / 8;       // 16-byte pieces of a row
+constexpr int KSTEPS = D / 16;
+constexpr int NTILES_D = D / 8;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+struct Pools {
+  const bf16* k;
+  const bf16* v;
+  const int* table;   // [requests][table_width]
+  int table_width;
+  int num_pages;
+  int kv_heads;
+  int page_size;
+};
+
+// Address of key `key` of request row `row` for kv head `kvh`, or nullptr (and an error bit) if
+// the block table has no page there.
+__device__ __forceinline__ long long kv_offset(const Pools& pools, const int* row, int key, int kvh, int* err) {
+  const int index = key / pools.page_size;
+  const int page = index < pools.table_width ? row[index] : -1;
+  if (page < 0 || page >= pools.num_pages) {
+    atomicOr(err, kErrBadPage);
+    return -1;
+  }
+  return (((long long)page * pools.kv_heads + kvh) * pools.page_size + key % pools.page_size) * D;
+}
+
+// One 16-row block against NB*16 keys held in shared memory (rows of ROW elements).
+// q_frag: A fragments of the 16 query rows.  s: NB*2 score tiles of 16 x 8.
+template <int NB>
+__device__ __forceinline__ void scores(const uint32_t (&q_frag)[KSTEPS][4], const bf16* k_tile,
+                                       float (&s)[NB * 2][4], int lane) {
+#pragma unroll
+  for (int i = 0; i < NB * 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+  const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      uint32_t b[4];
+      ldsm_x4(b, k_tile + (nb * 16 + (mi >> 1) * 8 + r) * ROW + kk * 16 + (mi & 1) * 8);
+      mma_bf16(s[2 * nb], q_frag[kk], b[0], b[1]);
+      mma_bf16(s[2 * nb + 1], q_frag[kk], b[2], b[3]);
+    }
+  }
+}
+
+// o += P V for NB*16 keys; p: probabilities in the score-tile layout.
+template <int NB>
+__device__ __forceinline__ void accumulate(const float (&p)[NB * 2][4], const bf16* v_tile,
+                                           float (&o)[NTILES_D][4], int lane) {
+  const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kb = 0; kb < NB; ++kb) {
+    uint32_t a[4];
+    a[0] = pack_bf16(p[2 * kb][0], p[2 * kb][1]);
+    a[1] = pack_bf16(p[2 * kb][2], p[2 * kb][3]);
+    a[2] = pack_bf16(p[2 * kb + 1][0], p[2 * kb + 1][1]);
+    a[3] = pack_bf16(p[2 * kb + 1][2], p[2 * kb + 1][3]);
+#pragma unroll
+    for (int db = 0; db < KSTEPS; ++db) {
+      uint32_t b[4];
+      ldsm_x4_trans(b, v_tile + (kb * 16 + (mi & 1) * 8 + r) * ROW + db * 16 + (mi >> 1) * 8);
+      mma_bf16(o[2 * db], a, b[0], b[1]);
+      mma_bf16(o[2 * db + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Running-maximum softmax update for the two rows (g, g + 8) a thread holds.
+// s holds scores already multiplied by scale * log2(e); masked entries are -inf.
+template <int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2],
+                                               float (&o)[NTILES_D][4]) {
+  float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    tile_max[0] = fmaxf(tile_max[0], fmaxf(s[i][0], s[i][1]));
+    tile_max[1] = fmaxf(tile_max[1], fmaxf(s[i][2], s[i][3]));
+  }
+  float alpha[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float m_new = fmaxf(m[h], quad_max(tile_max[h]));
+    alpha[h] = (m_new == -INFINITY) ? 1.f : exp2f(m[h] - m_new);
+    m[h] = m_new;
+  }
+  float sum[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    s[i][0] = (m[0] == -INFINITY) ? 0.f : exp2f(s[i][0] - m[0]);
+    s[i][1] = (m[0] == -INFINITY) ? 0.f : exp2f(s[i][1] - m[0]);
+    s[i][2] = (m[1] == -INFINITY) ? 0.f : exp2f(s[i][2] - m[1]);
+    s[i][3] = (m[1] == -INFINITY) ? 0.f : exp2f(s[i][3] - m[1]);
+    sum[0] += s[i][0] + s[i][1];
+    sum[1] += s[i][2] + s[i][3];
+  }
+  l[0] = l[0] * alpha[0] + sum[0];
+  l[1] = l[1] * alpha[1] + sum[1];
+#pragma unroll
+  for (int i = 0; i < NTILES_D; ++i) {
+    o[i][0] *= alpha[0];
+    o[i][1] *= alpha[0];
+    o[i][2] *= alpha[1];
+    o[i][3] *= alpha[1];
+  }
+}
+
+// ------------------------------------------------------------------------------------ prefill
+constexpr int BM = 64, BN = 64, PREFILL_WARPS = 4;
+
+struct PrefillArgs {
+  const bf16* q;
+  int q_stride;
+  bf16* out;
+  int out_stride;
+  Pools pools;
+  const int* tile_request;
+  const int* tile_q0;
+  const int* context_lens;
+  const int* query_lens;
+  const int* query_start;
+  int group;         // query heads per kv head
+  int hpt;           // heads of the group per tile (rows of one token)
+  int tpt;           // tokens per tile
+  int head_chunks;   // ceil(group / hpt)
+  float scale_log2;
+  int window;
+  int* err;
+};
+
+__device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const int* row, int kvh, int k0,
+                                             int valid_lo, int valid_hi, bf16* k_dst, bf16* v_dst, int tid) {
+  // 128 threads, 64 rows: two threads per row, each copies half of the row's 16-byte pieces
+  const int r = tid >> 1, half = tid & 1;
+  const int key = k0 + r;
+  long long off = -1;
+  if (key >= valid_lo && key < valid_hi) off = kv_offset(a.pools, row, key, kvh, a.err);
+  const bool ok = off >= 0;
+  const bf16* ks = ok ? a.pools.k + off : a.pools.k;
+  const bf16* vs = ok ? a.pools.v + off : a.pools.v;
+#pragma unroll
+  for (int c = 0; c < CHUNKS / 2; ++c) {
+    const int chunk = half * (CHUNKS / 2) + c;
+    cp_async16(k_dst + r * ROW + chunk * 8, ks + chunk * 8, ok);
+    cp_async16(v_dst + r * ROW + chunk * 8, vs + chunk * 8, ok);
+  }
+}
+
+__global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const PrefillArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [BM][ROW]
+  bf16* k_s = q_s + BM * ROW;                     // [2][BN][ROW]
+  bf16* v_s = k_s + 2 * BN * ROW;                 // [2][BN][ROW]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x;
+  const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * a.hpt;
+  const int request = a.tile_request[tile], q0 = a.tile_q0[tile];
+  const int context = a.context_lens[request], q_len = a.query_lens[request];
+  const int first_token = a.query_start[request] + q0;
+  const int ntok = min(a.tpt, q_len - q0);
+  const int* table_row = a.pools.table + (size_t)request * a.pools.table_width;
+
+  // ---- Q tile: row r is token r / hpt, head h0 + r % hpt of the group
+  for (int idx = tid; idx < BM * CHUNKS; idx += PREFILL_WARPS * 32) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const int tok = r / a.hpt, hh = h0 + r % a.hpt;
+    const bool ok = tok < ntok && hh < a.group;
+    const bf16* src = ok ? a.q + (size_t)(first_token + tok) * a.q_stride + (size_t)(kvh * a.group + hh) * D + c * 8 : a.q;
+    cp_async16(q_s + r * ROW + c * 8, src, ok);
+  }
+  cp_async_commit();
+
+  const int pos_lo = context + q0, pos_hi = context + q0 + ntok - 1;
+  const int valid_lo = a.window > 0 ? max(0, pos_lo - a.window + 1) : 0;
+  const int valid_hi = pos_hi + 1;
+  const int k_begin = (valid_lo / BN) * BN;
+  const int tiles = (valid_hi - k_begin + BN - 1) / BN;
+
+  load_kv_tile(a, table_row, kvh, k_begin, valid_lo, valid_hi, k_s, v_s, tid);
+  cp_async_commit();
+
+  uint32_t q_frag[KSTEPS][4];
+  float o[NTILES_D][4];
+#pragma unroll
+  for (int i = 0; i < NTILES_D; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  // positions of the two rows this thread holds (-1: row not in use)
+  const int g = lane >> 2, t4 = lane & 3;
+  int row_pos[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + h * 8;
+    const int tok = r / a.hpt, hh = h0 + r % a.hpt;
+    row_pos[h] = (tok < ntok && hh < a.group) ? context + q0 + tok : -1;
+  }
+
+  for (int it = 0; it < tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < tiles) {
+      load_kv_tile(a, table_row, kvh, k_begin + (it + 1) * BN, valid_lo, valid_hi,
+                   k_s + (stage ^ 1) * BN * ROW, v_s + (stage ^ 1) * BN * ROW, tid);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk)
+        ldsm_x4(q_frag[kk], q_s + (warp * 16 + (lane & 15)) * ROW + kk * 16 + (lane >> 4) * 8);
+    }
+    const int k0 = k_begin + it * BN;
+    // a warp whose rows all lie before this tile's first key has nothing to add
+    const int warp_pos_hi = context + q0 + min(ntok - 1, (warp * 16 + 15) / a.hpt);
+    if (k0 <= warp_pos_hi) {
+      float s[BN / 8][4];
+      scores<BN / 16>(q_frag, k_s + stage * BN * ROW, s, lane);
+#pragma unroll
+      for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = k0 + i * 8 + 2 * t4 + (e & 1);
+          const int pos = row_pos[e >> 1];
+          const bool ok = key <= pos && (a.window <= 0 || key > pos - a.window);
+          s[i][e] = ok ? s[i][e] * a.scale_log2 : -INFINITY;
+        }
+      }
+      softmax_update<BN / 8>(s, m, l, o);
+      accumulate<BN / 16>(s, v_s + stage * BN * ROW, o, lane);
+    }
+    __syncthreads();
+  }
+
+  // ---- write out
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (row_pos[h] < 0) continue;
+    const float total = quad_sum(l[h]);
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    const int r = warp * 16 + g + h * 8;
+    const int tok = r / a.hpt, hh = h0 + r % a.hpt;
+    bf16* dst = a.out + (size_t)(first_token + tok) * a.out_stride + (size_t)(kvh * a.group + hh) * D;
+#pragma unroll
+    for (int i = 0; i < NTILES_D; ++i) {
+      const uint32_t packed = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = packed;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ decode
+constexpr int DECODE_WARPS = 4, DN = 16;
+
+struct DecodeArgs {
+  const bf16* q;          // row b of q_stride elements: the request's single query token
+  int q_stride;
+  bf16* out;
+  int out_stride;
+  Pools pools;
+  const int* context_lens;  // keys before the query token; it attends to context + 1 keys
+  int group;
+  int head_chunks;          // ceil(group / 16)
+  int splits;
+  float scale_log2;
+  int window;
+  float* partial_o;         // [requests][q_heads][splits][D]   (splits > 1)
+  float* partial_ml;        // [requests][q_heads][splits][2]
+  int q_heads;
+  int* err;
+};
+
+__device__ __forceinline__ void load_kv_tile16(const DecodeArgs& a, const int* row, int kvh, int k0,
+                                               int valid_hi, bf16* k_dst, bf16* v_dst, int lane) {
+  const int r = lane >> 1, half = lane & 1;
+  const int key = k0 + r;
+  long long off = -1;
+  if (key < valid_hi) off = kv_offset(a.pools, row, key, kvh, a.err);
+  const bool ok = off >= 0;
+  const bf16* ks = ok ? a.pools.k + off : a.pools.k;
+  const bf16* vs = ok ? a.pools.v + off : a.pools.v;
+#pragma unroll
+  for (int c = 0; c < CHUNKS / 2; ++c) {
+    const int chunk = half * (CHUNKS / 2) + c;
+    cp_async16(k_dst + r * ROW + chunk * 8, ks + chunk * 8, ok);
+    cp_async16(v_dst + r * ROW + chunk * 8, vs + chunk * 8, ok);
+  }
+}
+
+constexpr int DECODE_STAGE = 2 * DN * ROW;                       // K and V of one stage, elements
+constexpr int DECODE_WARP_ELEMS = 2 * DECODE_STAGE;              // two stages
+constexpr size_t DECODE_KV_BYTES = (size_t)DECODE_WARPS * DECODE_WARP_ELEMS * sizeof(bf16);
+constexpr size_t DECODE_MERGE_BYTES = (size_t)DECODE_WARPS * 16 * (D + 2) * sizeof(float);
+constexpr size_t DECODE_Q_BYTES = (size_t)16 * ROW * sizeof(bf16);
+constexpr size_t DECODE_SMEM =
+    DECODE_Q_BYTES + (DECODE_KV_BYTES > DECODE_MERGE_BYTES ? DECODE_KV_BYTES : DECODE_MERGE_BYTES);
+
+__global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                          // [16][ROW]
+  bf16* kv_s = reinterpret_cast<bf16*>(smem_raw + DECODE_Q_BYTES);        // per warp: 2 stages of K,V
+  float* merge_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES);   // aliased after the loop
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * 16;
+  const int request = blockIdx.z;
+  const int* table_row = a.pools.table + (size_t)request * a.pools.table_width;
+  const int length = a.context_lens[request] + 1;
+  const int first = (a.window > 0 && length > a.window) ? length - a.window : 0;
+  const int per_split = (((length - first + a.splits - 1) / a.splits) + DN - 1) / DN * DN;
+  const int begin = first + split * per_split;
+  const int end = min(length, begin + per_split);
+
+  for (int idx = tid; idx < 16 * CHUNKS; idx += DECODE_WARPS * 32) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = h0 + r < a.group;
+    const bf16* src = ok ? a.q + (size_t)request * a.q_stride + (size_t)(kvh * a.group + h0 + r) * D + c * 8 : a.q;
+    cp_async16(q_s + r * ROW + c * 8, src, ok);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  uint32_t q_frag[KSTEPS][4];
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk)
+    ldsm_x4(q_frag[kk], q_s + (lane & 15) * ROW + kk * 16 + (lane >> 4) * 8);
+
+  float o[NTILES_D][4];
+#pragma unroll
+  for (int i = 0; i < NTILES_D; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int t4 = lane & 3;
+
+  bf16* mine = kv_s + warp * DECODE_WARP_ELEMS;
+  const int tiles = begin < end ? (end - begin + DN - 1) / DN : 0;
+  // warp w takes tiles w, w + 4, ...
+  int it = warp;
+  if (it < tiles) load_kv_tile16(a, table_row, kvh, begin + it * DN, end, mine, mine + DN * ROW, lane);
+  cp_async_commit();
+  int stage = 0;
+  for (; it < tiles; it += DECODE_WARPS) {
+    const int next = it + DECODE_WARPS;
+    if (next < tiles) {
+      bf16* dst = mine + (stage ^ 1) * DECODE_STAGE;
+      load_kv_tile16(a, table_row, kvh, begin + next * DN, end, dst, dst + DN * ROW, lane);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const bf16* k_tile = mine + stage * DECODE_STAGE;
+    const bf16* v_tile = k_tile + DN * ROW;
+    float s[2][4];
+    scores<1>(q_frag, k_tile, s, lane);
+    const int k0 = begin + it * DN;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = k0 + i * 8 + 2 * t4 + (e & 1);
+        s[i][e] = key < end ? s[i][e] * a.scale_log2 : -INFINITY;
+      }
+    softmax_update<2>(s, m, l, o);
+    accumulate<1>(s, v_tile, o, lane);
+    __syncwarp();
+    stage ^= 1;
+  }
+  cp_async_wait<0>();
+  __syncthreads();   // every warp is done with its K/V buffers: reuse them for the merge
+
+  // ---- merge the four warps: per warp [16][D + 2] floats (o, then max, then sum)
+  const int g = lane >> 2;
+  float* my_merge = merge_s + warp * 16 * (D + 2);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + h * 8;
+    const float total = quad_sum(l[h]);
+#pragma unroll
+    for (int i = 0; i < NTILES_D; ++i) {
+      my_merge[r * (D + 2) + i * 8 + 2 * t4] = o[i][2 * h];
+      my_merge[r * (D + 2) + i * 8 + 2 * t4 + 1] = o[i][2 * h + 1];
+    }
+    if (t4 == 0) {
+      my_merge[r * (D + 2) + D] = m[h];
+      my_merge[r * (D + 2) + D + 1] = total;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < 16 * D; idx += DECODE_WARPS * 32) {
+    const int r = idx / D, d = idx % D;
+    if (h0 + r >= a.group) continue;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DECODE_WARPS; ++w) m_all = fmaxf(m_all, merge_s[(w * 16 + r) * (D + 2) + D]);
+    float sum = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DECODE_WARPS; ++w) {
+      const float mw = merge_s[(w * 16 + r) * (D + 2) + D];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m_all);
+      sum += merge_s[(w * 16 + r) * (D + 2) + D + 1] * f;
+      acc += merge_s[(w * 16 + r) * (D + 2) + d] * f;
+    }
+    const int head = kvh * a.group + h0 + r;
+    if (a.splits == 1) {
+      a.out[(size_t)request * a.out_stride + (size_t)head * D + d] =
+          __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+    } else {
+      const size_t slot = ((size_t)request * a.q_heads + head) * a.splits + split;
+      a.partial_o[slot * D + d] = acc;
+      if (d == 0) {
+        a.partial_ml[slot * 2] = m_all;
+        a.partial_ml[slot * 2 + 1] = sum;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(D) combine_kernel(const float* __restrict__ partial_o,
+                                                    const float* __restrict__ partial_ml,
+                                                    bf16* __restrict__ out, int out_stride,
+                                                    int q_heads, int splits) {
+  const int request = blockIdx.x / q_heads, head = blockIdx.x % q_heads, d = threadIdx.x;
+  const size_t base = ((size_t)request * q_heads + head) * splits;
+  float m_all = -INFINITY;
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, partial_ml[(base + s) * 2]);
+  float sum = 0.f, acc = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = partial_ml[(base + s) * 2];
+    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m_all);
+    sum += partial_ml[(base + s) * 2 + 1] * f;
+    acc += partial_o[(base + s) * D + d] * f;
+  }
+  out[(size_t)request * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+}
+
+}  // namespace cie
+
+using namespace cie;
+
+static const float kLog2e = 1.4426950408889634f;
+
+extern "C" int cie_attention_head_dim() { return D; }
+
+extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int out_stride,
+                                     const void* k_pool, const void* v_pool, const int* table,
+                                     int table_width, int num_pages, const int* tile_request,
+                                     const int* tile_q0, int num_tiles, const int* context_lens,
+                                     const int* query_lens, const int* query_start, int q_heads,
+                                     int kv_heads, int page_size, int hpt, float scale, int window,
+                                     int* err, void* stream) {
+  if (num_tiles <= 0) return 0;
+  if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_prefill: %d query heads over %d kv heads", q_heads, kv_heads);
+  const int group = q_heads / kv_heads;
+  if (hpt < 1 || hpt > BM || hpt > group) CIE_FAIL("attention_prefill: %d heads per tile with a group of %d", hpt, group);
+  if (q_stride % 8 || out_stride % 2) CIE_FAIL("attention_prefill: row strides must keep 16-byte alignment");
+  PrefillArgs a;
+  a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
+  a.pools = Pools{(const bf16*)k_pool, (const bf16*)v_pool, table, table_width, num_pages, kv_heads, page_size};
+  a.tile_request = tile_request; a.tile_q0 = tile_q0; a.context_lens = context_lens;
+  a.query_lens = query_lens; a.query_start = query_start;
+  a.group = group; a.hpt = hpt; a.tpt = BM / hpt; a.head_chunks = (group + hpt - 1) / hpt;
+  a.scale_log2 = scale * kLog2e; a.window = window; a.err = err;
+  const size_t smem = (size_t)(BM + 4 * BN) * ROW * sizeof(bf16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t status = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (status != cudaSuccess) CIE_FAIL("attention_prefill: shared memory %zu: %s", smem, cudaGetErrorString(status));
+    configured = true;
+  }
+  dim3 grid(num_tiles, kv_heads * a.head_chunks);
+  prefill_kernel<<<grid, PREFILL_WARPS * 32, smem, (cudaStream_t)stream>>>(a);
+  CIE_CHECK_LAUNCH("attention_prefill");
+  return 0;
+}
+
+// partial_o / partial_ml: float32 scratch of requests*q_heads*splits*D and *2 elements (splits > 1).
+extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int out_stride,
+                                    const void* k_pool, const void* v_pool, const int* table,
+                                    int table_width, int num_pages, const int* context_lens,
+                                    int requests, int q_heads, int kv_heads, int page_size,
+                                    int splits, float scale, int window, float* partial_o,
+                                    float* partial_ml, int* err, void* stream) {
+  if (requests <= 0) return 0;
+  if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_decode: %d query heads over %d kv heads", q_heads, kv_heads);
+  if (splits < 1) CIE_FAIL("attention_decode: splits %d", splits);
+  if (splits > 1 && (!partial_o || !partial_ml)) CIE_FAIL("attention_decode: split runs need scratch buffers");
+  if (q_stride % 8) CIE_FAIL("attention_decode: row stride must keep 16-byte alignment");
+  DecodeArgs a;
+  a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
+  a.pools = Pools{(const bf16*)k_pool, (const bf16*)v_pool, table, table_width, num_pages, kv_heads, page_size};
+  a.context_lens = context_lens; a.group = q_heads / kv_heads; a.head_chunks = (a.group + 15) / 16;
+  a.splits = splits; a.scale_log2 = scale * kLog2e; a.window = window;
+  a.partial_o = partial_o; a.partial_ml = partial_ml; a.q_heads = q_heads; a.err = err;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t status = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+    if (status != cudaSuccess) CIE_FAIL("attention_decode: shared memory %zu: %s", (size_t)DECODE_SMEM, cudaGetErrorString(status));
+    configured = true;
+  }
+  dim3 grid(splits, kv_heads * a.head_chunks, requests);
+  decode_kernel<<<grid, DECODE_WARPS * 32, DECODE_SMEM, (cudaStream_t)stream>>>(a);
+  CIE_CHECK_LAUNCH("attention_decode");
+  if (splits > 1) {
+    combine_kernel<<<requests * q_heads, D, 0, (cudaStream_t)stream>>>(partial_o, partial_ml, (bf16*)out, out_stride, q_heads, splits);
+    CIE_CHECK_LAUNCH("attention_combine");
+  }
+  return 0;
+}

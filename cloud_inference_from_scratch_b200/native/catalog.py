@@ -5,5 +5,12 @@ from __future__ import annotations
 GENERIC = ("elementwise.cu", "gemm_simt.cu", "attention_generic.cu", "sampling.cu")
 
 
+# head sizes the tensor-core attention library is built for ahead of time; any other multiple of
+# 16 up to 256 is built when a model first asks for it
+ATTENTION_HEAD_DIMS = (64, 128)
+
+
 def all_libraries() -> list[tuple[str, dict]]:
-    return [(source, {}) for source in GENERIC]
+    libraries: list[tuple[str, dict]] = [(source, {}) for source in GENERIC]
+    libraries += [("attention_tensor.cu", {"HEAD_DIM": dim}) for dim in ATTENTION_HEAD_DIMS]
+    return libraries

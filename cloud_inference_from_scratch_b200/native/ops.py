@@ -113,7 +113,19 @@ class Ops:
 
     def require_attention(self, head_dim: int) -> None:
         """Builds, at model set-up, the attention kernels a head size needs."""
-        return
+        if self.code == BF16:
+            from . import tensor_attention
+
+            if head_dim not in self._tensor_attention and tensor_attention.supports(head_dim):
+                self._tensor_attention[head_dim] = tensor_attention.TensorAttention(self, head_dim)
+
+    def plan_attention(self, host: Any, group: int) -> dict[str, Any]:
+        """Integer work lists the attention kernels want in a step's metadata (may be empty)."""
+        if self.code != BF16 or bool((host.query_lens == 1).all()):
+            return {}
+        from . import tensor_attention
+
+        return tensor_attention.plan_tiles(host.query_lens, group)
 
     def check_errors(self) -> None:
         """Reads the device error word (synchronises) and raises if a kernel flagged a fault."""
@@ -184,8 +196,10 @@ class Ops:
     def attention(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
                   head_dim: int, scale: float, window: int) -> None:
         fast = self._tensor_attention.get(head_dim)
-        if fast is not None and fast.run(qkv, out, ctx, kv, q_heads, kv_heads, scale, window):
-            return
+        if fast is not None:
+            plan = ctx.extras.get(("attention", q_heads // kv_heads)) or None
+            if fast.run(qkv, out, ctx, kv, q_heads, kv_heads, scale, window, plan):
+                return
         self.attention_generic(qkv, out, ctx, kv, q_heads, kv_heads, head_dim, scale, window)
 
     def attention_generic(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int,

@@ -47,6 +47,14 @@ class Attention(Mixer):
         self.kv_width = self.num_kv_heads * self.head_dim
         self.qkv_width = self.q_width + 2 * self.kv_width
 
+    @property
+    def plan_key(self):
+        return ("attention", self.num_heads // self.num_kv_heads)
+
+    def plan(self, host, cache):
+        """Work lists for this step's attention kernels, added to the step's metadata copy."""
+        return self.runtime.ops.plan_attention(host, self.num_heads // self.num_kv_heads)
+
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)
 

@@ -317,3 +317,52 @@ def test_sampling_draws_follow_the_distribution(ops):
     item.sample(logits, temps, keys, out)
     counts = torch.bincount(out.long().cpu(), minlength=4).float() / 4000
     torch.testing.assert_close(counts, torch.tensor([0.125, 0.25, 0.625, 0.0]), atol=0.03, rtol=0)
+
+
+# ------------------------------------------------------------------ tensor-core attention (bfloat16)
+def tensor_case(ops, dim, *args, **kwargs):
+    item = ops[torch.bfloat16]
+    item.require_attention(dim)
+    assert dim in item._tensor_attention, "the tensor-core attention library was not loaded"
+    before = item.launches
+    worst = attention_case(ops, torch.bfloat16, *args, **kwargs, fn="attention")
+    assert item.launches > before
+    return worst
+
+
+@pytest.mark.parametrize("query_len", [1, 2, 7, 16])
+@pytest.mark.parametrize("batch", [1, 2, 4, 8, 16])
+def test_tensor_attention_context_matrix(ops, query_len, batch):
+    """The reference's kernel matrix (tests/remote_ragged_gpu_tests.py:118-121): batches of 1..16,
+    contexts across page edges up to 4000, query lengths 1, 2, 7, 16."""
+    contexts = [0, 15, 16, 17, 127, 128, 511, 1024, 2047, 4000]
+    chosen = [contexts[(i * 3 + batch) % len(contexts)] for i in range(batch)]
+    tensor_case(ops, 128, chosen, [query_len] * batch, 16, 2, 128, 16, seed=batch)
+
+
+@pytest.mark.parametrize("dim,page,q_heads,kv_heads", [
+    (16, 4, 4, 2), (48, 8, 5, 5), (64, 8, 2, 1), (128, 32, 8, 1), (256, 16, 2, 1), (80, 5, 3, 1),
+    (32, 16, 14, 2), (64, 16, 20, 1), (128, 16, 28, 4),
+])
+def test_tensor_attention_sizes(ops, dim, page, q_heads, kv_heads):
+    tensor_case(ops, dim, [3, 0, 200, 61, 0], [5, 1, 1, 40, 130], q_heads, kv_heads, dim, page, seed=3)
+    tensor_case(ops, dim, [3, 0, 700, 61], [1, 1, 1, 1], q_heads, kv_heads, dim, page, seed=4)
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 100])
+def test_tensor_attention_window(ops, window):
+    tensor_case(ops, 32, [0, 33, 150], [20, 9, 1], 4, 2, 32, 8, window=window, seed=5)
+    tensor_case(ops, 32, [10, 33, 450], [1, 1, 1], 4, 2, 32, 8, window=window, seed=6)
+
+
+def test_tensor_attention_far_key(ops):
+    """The last query is aligned with key 3 of 900 (prefill kernel) and of 4000 (split decode
+    kernel): its output must be that key's value, wherever its page lies."""
+    tensor_case(ops, 64, [899, 10], [1, 4], 2, 1, 64, 16, seed=6, plant=(0, 3, 4.0))
+    tensor_case(ops, 64, [3999, 10], [1, 1], 2, 1, 64, 16, seed=7, plant=(0, 3, 4.0))
+    tensor_case(ops, 128, [2047], [1], 16, 2, 128, 16, seed=8, plant=(0, 2040, 4.0))
+
+
+def test_tensor_attention_long_prompt_whole(ops):
+    tensor_case(ops, 128, [0], [1500], 16, 2, 128, 16, seed=9)
+    tensor_case(ops, 64, [300, 0], [700, 64], 14, 2, 64, 16, seed=10)
