@@ -136,6 +136,12 @@ def random_prompts(count: int, length: int, vocab: int, seed: int) -> list[list[
     return [rng.integers(0, vocab, size=length).tolist() for _ in range(count)]
 
 
+def nvtx_range(name: str):
+    from cloud_inference_from_scratch_b200.engine.profiling import nvtx_range as ranged
+
+    return ranged(name)
+
+
 def make_engine(cfg: dict, batch: int, layers: int | None = None):
     from cloud_inference_from_scratch_b200 import InferenceEngine, build_config
 
@@ -178,8 +184,9 @@ def time_decode(engine, cfg: dict, batch: int, steps: int, warmup: int, sample_c
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall = time.perf_counter()
     start.record()
-    for _ in range(steps):
-        scheduler.step()
+    with nvtx_range("bench.decode"):
+        for _ in range(steps):
+            scheduler.step()
     stop.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - wall
@@ -210,7 +217,8 @@ def time_prefill(engine, cfg: dict, repeats: int = 5) -> dict:
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        core.step.run([StepEntry("prefill", prompt, want=(PROMPT_TOKENS - 1,))])
+        with nvtx_range("bench.prefill" if index == repeats + 2 else "bench.prefill.warm"):
+            core.step.run([StepEntry("prefill", prompt, want=(PROMPT_TOKENS - 1,))])
         stop.record()
         torch.cuda.synchronize()
         core.step.release("prefill")
@@ -231,15 +239,22 @@ def run_own(args: argparse.Namespace) -> int:
     numbers = model_numbers(cfg)
     results = {}
     main = None
-    for batch in (args.batch, 1, 64):
+    batches = (args.batch, 1, 64) if args.only == "all" else (args.batch,)
+    prefill = dict(ms=float("nan"))
+    for batch in batches:
         if batch in results:
             continue
         engine, used = make_engine(cfg, batch, args.layers)
         numbers = model_numbers(used)
-        if batch == args.batch:
+        if batch == args.batch and args.only in ("all", "prefill"):
             prefill = time_prefill(engine, used)
-        results[batch] = time_decode(engine, used, batch, args.steps, args.warmup,
-                                     sample_clocks=batch == args.batch)
+        if args.only == "prefill":
+            results[batch] = dict(ms_per_step=float("nan"), tokens_per_s=float("nan"),
+                                  e2e_tokens_per_s=float("nan"), clocks=None, context=PROMPT_TOKENS,
+                                  launches=0, h2d=0, d2h=0)
+        else:
+            results[batch] = time_decode(engine, used, batch, args.steps, args.warmup,
+                                         sample_clocks=batch == args.batch)
         engine.close()
         del engine
         torch.cuda.empty_cache()
@@ -280,10 +295,9 @@ def run_own(args: argparse.Namespace) -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4),
                      "peaks": peak["source"]},
-        "points": {"decode_b1": round(results[1]["tokens_per_s"], 1),
-                   "decode_b64": round(results[64]["tokens_per_s"], 1),
-                   "decode_b1_ms": round(results[1]["ms_per_step"], 4),
-                   "decode_b64_ms": round(results[64]["ms_per_step"], 4)},
+        "points": {f"decode_b{b}{suffix}": round(results[b][key], digits)
+                   for b in (1, 64) if b in results
+                   for suffix, key, digits in (("", "tokens_per_s", 1), ("_ms", "ms_per_step", 4))},
         "clocks": main["clocks"],
     }
     print(json.dumps(line))
@@ -306,6 +320,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the model has (named in config; for quick runs)")
     parser.add_argument("--impl", default="own", choices=("own", "reference"))
+    parser.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
+                        help="measure only the decode step at --batch, or only the prefill "
+                             "(for profiling; the full line needs 'all')")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")

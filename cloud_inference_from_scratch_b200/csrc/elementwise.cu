@@ -31,20 +31,37 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 // One block per output row.  rows == nullptr: row r is residual row r and residual is updated
 // in place with `update`.  rows != nullptr: row r reads residual row rows[r]; residual is not
 // written.  out = gain * ((x) * rsqrt(mean(x^2) + eps)), x = residual (+ update), all float32.
+// `update` is either one tensor of the activation type, or (partial_splits > 0) float32 partial
+// sums [splits][rows][hidden] of a matrix product cut along K, plus an optional bias; the partial
+// sums are added in ascending split order.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ update,
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict__ update,
+                                   int partial_splits, size_t partial_stride,
+                                   const float* __restrict__ update_bias,
                                    const float* __restrict__ gain, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * hidden;
-  const T* upd = update ? update + (size_t)src * hidden : nullptr;
-  const bool write_back = (rows == nullptr) && (upd != nullptr);
-  float sumsq = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+  const bool has_update = update != nullptr;
+  const T* upd = (has_update && partial_splits == 0) ? reinterpret_cast<const T*>(update) + (size_t)src * hidden : nullptr;
+  const float* part = (has_update && partial_splits > 0) ? reinterpret_cast<const float*>(update) + (size_t)src * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && has_update;
+  auto value = [&](int i) {
     float x = res[i];
     if (upd) x += to_float(upd[i]);
+    if (part) {
+      float u = part[i];
+      for (int s = 1; s < partial_splits; ++s) u += part[(size_t)s * partial_stride + i];
+      if (update_bias) u += update_bias[i];
+      x += u;
+    }
+    return x;
+  };
+  float sumsq = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float x = value(i);
     if (write_back) res[i] = x;
     sumsq += x * x;
   }
@@ -52,8 +69,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
   const float inv = rsqrtf(total / (float)hidden + eps);
   T* dst = out + (size_t)r * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float x = res[i];
-    if (upd && !write_back) x += to_float(upd[i]);
+    const float x = write_back ? res[i] : value(i);
     dst[i] = from_float<T>(gain[i] * (x * inv));
   }
 }
@@ -62,8 +78,14 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
 // qkv: [T, (Hq + 2 Hkv) * D], q heads first, then k heads, then v heads.  q is rotated in place.
 // k is rotated and written, v is copied, to pool[page][kv_head][pos % page][D] with
 // page = table[request][pos / page].  Element j < rot/2 pairs with j + rot/2 (rotate-half).
+// The source row is either qkv itself (partial_splits == 0; then q_out == qkv and q is rotated
+// in place) or float32 partial sums [splits][T][width] of the projection plus its bias
+// (partial_splits > 0; then the rotated q is written to q_out, rows of q_stride elements).
 template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_splits,
+                                     size_t partial_stride, const float* __restrict__ bias,
+                                     T* __restrict__ q_out, int q_stride,
+                                     const int* __restrict__ positions,
                                      const int* __restrict__ request_of_token,
                                      const int* __restrict__ table, int table_width, int num_pages,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
@@ -72,7 +94,16 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int width = (q_heads + 2 * kv_heads) * dim;
-  T* row = qkv + (size_t)t * width;
+  const T* row_t = partial_splits == 0 ? reinterpret_cast<const T*>(src) + (size_t)t * width : nullptr;
+  const float* row_p = partial_splits > 0 ? reinterpret_cast<const float*>(src) + (size_t)t * width : nullptr;
+  auto value = [&](int i) {
+    if (row_t) return to_float(row_t[i]);
+    float v = row_p[i];
+    for (int s = 1; s < partial_splits; ++s) v += row_p[(size_t)s * partial_stride + i];
+    if (bias) v += bias[i];
+    return v;
+  };
+  T* q_row = q_out + (size_t)t * q_stride;
   const int half = rot / 2;
 
   size_t slot_base = 0;
@@ -97,41 +128,51 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
     const float angle = (float)pos * inv_freq[j];
     float s, c;
     sincosf(angle, &s, &c);
-    T* x = row + (size_t)h * dim;
-    const float a = to_float(x[j]), b = to_float(x[j + half]);
+    const float a = value(h * dim + j), b = value(h * dim + j + half);
     const T ra = from_float<T>(a * c - b * s), rb = from_float<T>(b * c + a * s);
     if (h < q_heads) {
-      x[j] = ra;
-      x[j + half] = rb;
+      q_row[h * dim + j] = ra;
+      q_row[h * dim + j + half] = rb;
     } else if (slot_ok) {
       T* dst = k_pool + slot_base + (size_t)(h - q_heads) * head_stride;
       dst[j] = ra;
       dst[j + half] = rb;
     }
   }
-  if (!slot_ok) return;
-  // the part of k beyond the rotary dims passes through
+  // the part of q and k beyond the rotary dims passes through
   const int tail = dim - rot;
+  if (tail > 0 && row_p) {
+    for (int i = threadIdx.x; i < q_heads * tail; i += blockDim.x) {
+      const int h = i / tail, d = rot + i % tail;
+      q_row[h * dim + d] = from_float<T>(value(h * dim + d));
+    }
+  }
+  if (!slot_ok) return;
   for (int i = threadIdx.x; i < kv_heads * tail; i += blockDim.x) {
     const int h = i / tail, d = rot + i % tail;
-    k_pool[slot_base + (size_t)h * head_stride + d] = row[(size_t)(q_heads + h) * dim + d];
+    k_pool[slot_base + (size_t)h * head_stride + d] = from_float<T>(value((q_heads + h) * dim + d));
   }
   for (int i = threadIdx.x; i < kv_heads * dim; i += blockDim.x) {
     const int h = i / dim, d = i % dim;
-    v_pool[slot_base + (size_t)h * head_stride + d] = row[(size_t)(q_heads + kv_heads + h) * dim + d];
+    v_pool[slot_base + (size_t)h * head_stride + d] =
+        from_float<T>(value((q_heads + kv_heads + h) * dim + d));
   }
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
+// gate_up: [T, 2 * inter] where channel c has its gate at column (c / block) * 2 * block + c % block
+// and its up value `block` columns further (block == inter: all gates first, then all ups).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens,
-                                int inter) {
+                                int inter, int block) {
   const size_t total = (size_t)tokens * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
-    const size_t t = i / inter, c = i % inter;
-    const float g = to_float(gate_up[t * 2 * inter + c]);
-    const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+    const size_t t = i / inter;
+    const int c = (int)(i % inter);
+    const size_t col = (size_t)(c / block) * 2 * block + c % block;
+    const float g = to_float(gate_up[t * 2 * inter + col]);
+    const float u = to_float(gate_up[t * 2 * inter + col + block]);
     out[i] = from_float<T>((g / (1.f + expf(-g))) * u);
   }
 }
@@ -162,43 +203,48 @@ extern "C" int cie_embedding(const int* ids, const void* table, float* residual,
   return 0;
 }
 
-extern "C" int cie_add_rmsnorm(float* residual, const void* update, const float* gain, void* out,
-                               const int* rows, int count, int hidden, float eps, int dtype,
-                               void* stream) {
+extern "C" int cie_add_rmsnorm(float* residual, const void* update, int partial_splits,
+                               long long partial_stride, const float* update_bias,
+                               const float* gain, void* out, const int* rows, int count, int hidden,
+                               float eps, int dtype, void* stream) {
   if (count <= 0) return 0;
   DISPATCH_DTYPE(dtype, "add_rmsnorm", {
     add_rmsnorm_kernel<T><<<count, threads_for(hidden / 4), 0, (cudaStream_t)stream>>>(
-        residual, (const T*)update, gain, (T*)out, rows, hidden, eps);
+        residual, update, partial_splits, (size_t)partial_stride, update_bias, gain, (T*)out, rows,
+        hidden, eps);
   })
   CIE_CHECK_LAUNCH("add_rmsnorm");
   return 0;
 }
 
-extern "C" int cie_rope_kv_write(void* qkv, const int* positions, const int* request_of_token,
-                                 const int* table, int table_width, int num_pages, void* k_pool,
-                                 void* v_pool, const float* inv_freq, int tokens, int q_heads,
-                                 int kv_heads, int dim, int rot, int page_size, int write_cache,
-                                 int dtype, int* err, void* stream) {
+extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long partial_stride,
+                                 const float* bias, void* q_out, int q_stride, const int* positions,
+                                 const int* request_of_token, const int* table, int table_width,
+                                 int num_pages, void* k_pool, void* v_pool, const float* inv_freq,
+                                 int tokens, int q_heads, int kv_heads, int dim, int rot,
+                                 int page_size, int write_cache, int dtype, int* err, void* stream) {
   if (tokens <= 0) return 0;
   if (rot % 2 || rot > dim || rot < 0) CIE_FAIL("rope_kv_write: rotary size %d does not fit head size %d", rot, dim);
   DISPATCH_DTYPE(dtype, "rope_kv_write", {
     const int work = (q_heads + kv_heads) * (rot / 2) > kv_heads * dim ? (q_heads + kv_heads) * (rot / 2) : kv_heads * dim;
     rope_kv_write_kernel<T><<<tokens, threads_for(work), 0, (cudaStream_t)stream>>>(
-        (T*)qkv, positions, request_of_token, table, table_width, num_pages, (T*)k_pool, (T*)v_pool,
-        inv_freq, q_heads, kv_heads, dim, rot, page_size, write_cache, err);
+        src, partial_splits, (size_t)partial_stride, bias, (T*)q_out, q_stride, positions,
+        request_of_token, table, table_width, num_pages, (T*)k_pool, (T*)v_pool, inv_freq, q_heads,
+        kv_heads, dim, rot, page_size, write_cache, err);
   })
   CIE_CHECK_LAUNCH("rope_kv_write");
   return 0;
 }
 
-extern "C" int cie_silu_mul(const void* gate_up, void* out, int tokens, int inter, int dtype,
-                            void* stream) {
+extern "C" int cie_silu_mul(const void* gate_up, void* out, int tokens, int inter, int block,
+                            int dtype, void* stream) {
   if (tokens <= 0) return 0;
+  if (block < 1 || inter % block) CIE_FAIL("silu_mul: %d channels do not divide into blocks of %d", inter, block);
   const size_t total = (size_t)tokens * inter;
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   DISPATCH_DTYPE(dtype, "silu_mul", {
-    silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, tokens, inter);
+    silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, tokens, inter, block);
   })
   CIE_CHECK_LAUNCH("silu_mul");
   return 0;

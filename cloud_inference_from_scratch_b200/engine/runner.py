@@ -192,6 +192,7 @@ class EngineRunner:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             self.core.runtime.workspace.frozen = True
+            self.ops.freeze_scratch()
             launches_before = self.ops.launches
             with torch.cuda.graph(graph):
                 logits = self.core.model.forward(ctx)

@@ -27,6 +27,32 @@ def _ptr(tensor: Any) -> int | None:
     return None if tensor is None else tensor.data_ptr()
 
 
+class Partials:
+    """Float32 partial sums [splits, rows, width] of a matrix product that was cut along K, with
+    the bias still to be added.  The kernels that consume a projection (residual-add + RMSNorm,
+    rotary + cache write) add the parts up themselves, in ascending split order."""
+
+    def __init__(self, data: Any, splits: int, rows: int, width: int, bias: Any) -> None:
+        self.data, self.splits, self.rows, self.width, self.bias = data, splits, rows, width, bias
+
+    @property
+    def shape(self) -> tuple[int, int]:
+        return (self.rows, self.width)
+
+
+class GateUpWeight:
+    """Stacked gate and up matrices [2I, H].  ``block`` == I: all gate rows, then all up rows.
+    ``block`` < I: rows interleaved in blocks (``block`` gate rows, the matching ``block`` up
+    rows, ...), which lets one CTA of the streaming kernel finish SiLU(gate) * up by itself."""
+
+    def __init__(self, weight: Any, inter: int, block: int) -> None:
+        self.weight, self.inter, self.block = weight, inter, block
+
+
+SM_COUNT = 148
+STREAM_MAX_ROWS = 64
+
+
 class _Lib:
     """A loaded library whose entry points return 0 or set ``cie_last_error``."""
 
@@ -74,11 +100,13 @@ class Ops:
         v, i, f = c_void_p, c_int, c_float
         ew = _Lib(load_library("elementwise.cu"))
         self._embedding = ew.function("cie_embedding", [v, v, v, i, i, i, i, v, v])
-        self._add_rmsnorm = ew.function("cie_add_rmsnorm", [v, v, v, v, v, i, i, f, i, v])
+        ll = ctypes.c_longlong
+        self._add_rmsnorm = ew.function("cie_add_rmsnorm", [v, v, i, ll, v, v, v, v, i, i, f, i, v])
         self._rope_kv_write = ew.function(
-            "cie_rope_kv_write", [v, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, v, v]
+            "cie_rope_kv_write",
+            [v, i, ll, v, v, i, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, v, v],
         )
-        self._silu_mul = ew.function("cie_silu_mul", [v, v, i, i, i, v])
+        self._silu_mul = ew.function("cie_silu_mul", [v, v, i, i, i, i, v])
         gs = _Lib(load_library("gemm_simt.cu"))
         self._gemm_simt = gs.function("cie_gemm_simt", [v, v, v, v, i, i, i, i, i, i, v])
         ag = _Lib(load_library("attention_generic.cu"))
@@ -90,6 +118,12 @@ class Ops:
         self._sample = sm.function("cie_sample", [v, i, i, v, v, v, v])
         self._tensor_gemm = None
         self._tensor_attention: dict[int, Any] = {}
+        self._gemm_stream = None
+        self._partial_buffers: dict[str, Any] = {}
+        self.scratch_frozen = False
+        if self.code == BF16 and self.gemm_mode != "simt":
+            st = _Lib(load_library("gemm_stream.cu"))
+            self._gemm_stream = st.function("cie_gemm_stream", [v, v, v, v, i, i, i, i, i, i, v])
         if self.code == BF16 and self.gemm_mode == "tensor":
             from .tensor_gemm import TensorGemm
 
@@ -147,27 +181,125 @@ class Ops:
 
     def add_rmsnorm(self, residual: Any, update: Any, gain: Any, eps: float, out: Any,
                     rows: Any = None) -> None:
+        """``update``: None, a tensor [T, H] of the compute dtype, or ``Partials``."""
         count, hidden = out.shape
         self.launches += 1
-        self._add_rmsnorm(_ptr(residual), _ptr(update), _ptr(gain), _ptr(out), _ptr(rows), count,
-                          hidden, eps, self._code_of(out), self.stream)
+        if isinstance(update, Partials):
+            self._add_rmsnorm(_ptr(residual), _ptr(update.data), update.splits,
+                              update.rows * update.width, _ptr(update.bias), _ptr(gain), _ptr(out),
+                              _ptr(rows), count, hidden, eps, self._code_of(out), self.stream)
+        else:
+            self._add_rmsnorm(_ptr(residual), _ptr(update), 0, 0, None, _ptr(gain), _ptr(out),
+                              _ptr(rows), count, hidden, eps, self._code_of(out), self.stream)
 
-    def linear(self, x: Any, weight: Any, bias: Any, out: Any) -> None:
-        """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias); out is the compute dtype or float32."""
+    def stream_plan(self, m: int, n: int, k: int, allow_partials: bool) -> tuple[int, int] | None:
+        """(weight rows per CTA, splits along K) for the streaming kernel, or None if the shape
+        is not its kind (more than 64 rows, or K not a multiple of 8)."""
+        if self._gemm_stream is None or m > STREAM_MAX_ROWS or k % 8 or k < 8:
+            return None
+        block_rows = 64 if (m > 16 and n >= 64 * 2 * SM_COUNT) else 32
+        tiles = -(-n // block_rows)
+        splits = 1
+        if allow_partials:
+            splits = max(1, min(-(-2 * SM_COUNT // tiles), k // 512))
+        return block_rows, splits
+
+    def scratch(self, tag: str, elements: int, reserve: int = 0) -> Any:
+        """Float32 scratch memory by name.  A buffer is made for ``max(elements, reserve)`` at
+        first use and may grow later, but not once ``freeze_scratch`` was called (a CUDA graph
+        then holds its address)."""
+        torch = self.torch
+        held = self._partial_buffers.get(tag)
+        if held is None or held.numel() < elements:
+            if held is not None and self.scratch_frozen:
+                raise KernelError(
+                    f"scratch buffer {tag!r} would have to grow from {held.numel()} to {elements} "
+                    "elements while a CUDA graph that uses it is alive"
+                )
+            held = torch.empty(max(elements, reserve, 1), dtype=torch.float32, device=self.device)
+            self._partial_buffers[tag] = held
+        return held
+
+    def freeze_scratch(self) -> None:
+        self.scratch_frozen = True
+
+    def linear(self, x: Any, weight: Any, bias: Any, out: Any, allow_partials: bool = False,
+               tag: str = "") -> Any:
+        """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias); out is the compute dtype or float32.
+
+        Returns ``out``, or, when ``allow_partials`` and the product was cut along K, a
+        ``Partials`` that a consuming kernel adds up (then ``out`` was not written)."""
         m, k = x.shape
         n = weight.shape[0]
         if weight.shape[1] != k or tuple(out.shape) != (m, n):
             raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)}")
         if m == 0:
-            return
+            return out
+        plan = self.stream_plan(m, n, k, allow_partials) if self.code == BF16 else None
+        if plan is not None:
+            block_rows, splits = plan
+            self.launches += 1
+            if splits > 1:
+                scratch = self.scratch("partials." + (tag or "linear"), splits * m * n,
+                                       reserve=splits * STREAM_MAX_ROWS * n)
+                self._gemm_stream(_ptr(x), _ptr(weight), None, _ptr(scratch), m, n, k, splits, 2,
+                                  block_rows, self.stream)
+                return Partials(scratch, splits, m, n, bias)
+            mode = 1 if out.dtype == self.torch.float32 else 0
+            self._gemm_stream(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k, 1, mode,
+                              block_rows, self.stream)
+            return out
         if self._tensor_gemm is not None and self._tensor_gemm.run(x, weight, bias, out):
-            return
+            return out
         if self.gemm_mode == "cublas" and self.code == BF16:
             self._cublas_linear(x, weight, bias, out)
-            return
+            return out
         self.launches += 1
         self._gemm_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k, self._code_of(x),
                         self._code_of(out), 0 if self.code == F32 else 1, self.stream)
+        return out
+
+    def resolve(self, value: Any, out: Any) -> Any:
+        """A plain tensor for a part that cannot consume ``Partials`` itself."""
+        if not isinstance(value, Partials):
+            return value
+        total = value.data[: value.splits * value.rows * value.width].view(value.splits, value.rows, value.width).sum(0)
+        if value.bias is not None:
+            total = total + value.bias
+        out.copy_(total)
+        return out
+
+    def prepare_gate_up(self, gate: Any, up: Any) -> GateUpWeight:
+        """Stacks gate and up; for bfloat16, interleaved in blocks of 16 rows when the channel
+        count allows, so that the streaming kernel can apply SiLU(gate) * up in its epilogue."""
+        torch = self.torch
+        inter = gate.shape[0]
+        block = inter
+        if self._gemm_stream is not None and inter % 16 == 0:
+            block = 16
+            hidden = gate.shape[1]
+            stacked = torch.stack([gate.view(inter // block, block, hidden),
+                                   up.view(inter // block, block, hidden)], dim=1)
+            weight = stacked.reshape(2 * inter, hidden)
+        else:
+            weight = torch.cat([gate, up])
+        return GateUpWeight(self.prepare_weight(weight), inter, block)
+
+    def gate_up(self, x: Any, weight: GateUpWeight, hidden_out: Any, workspace: Any) -> Any:
+        """hidden_out[T, I] = SiLU(x Wg^T) * (x Wu^T)."""
+        m, k = x.shape
+        inter = weight.inter
+        if self.code == BF16 and weight.block == 16:
+            plan = self.stream_plan(m, 2 * inter, k, False)
+            if plan is not None:
+                self.launches += 1
+                self._gemm_stream(_ptr(x), _ptr(weight.weight), None, _ptr(hidden_out), m, 2 * inter,
+                                  k, 1, 3, 32, self.stream)
+                return hidden_out
+        both = workspace.get("swiglu.gate_up", m, 2 * inter, self.dtype)
+        self.linear(x, weight.weight, None, both)
+        self.silu_mul(both, hidden_out, weight.block)
+        return hidden_out
 
     def _cublas_linear(self, x: Any, weight: Any, bias: Any, out: Any) -> None:
         """Library matrix product (cuBLAS through torch), as the reference uses for every
@@ -181,17 +313,30 @@ class Ops:
             out.add_(bias.to(out.dtype))
 
     def rope_kv_write(self, qkv: Any, ctx: Any, kv: Any, position: Any, q_heads: int,
-                      kv_heads: int, head_dim: int, write_cache: bool = True) -> None:
-        tokens = qkv.shape[0]
+                      kv_heads: int, head_dim: int, write_cache: bool = True,
+                      q_buffer: Any = None) -> Any:
+        """Rotates q and k, writes k and v into the pages; returns the tensor that holds the
+        rotated q (head h of token t at [t, h * head_dim]).  ``qkv`` is a tensor (q is rotated in
+        place) or ``Partials`` (then q goes to ``q_buffer``)."""
         rot = position.rotary_dim if position is not None else 0
         inv_freq = position.inv_freq if position is not None else None
         table = ctx.block_tables[kv.group]
         self.launches += 1
-        self._rope_kv_write(_ptr(qkv), _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
+        if isinstance(qkv, Partials):
+            tokens = qkv.rows
+            src, splits, stride, bias = qkv.data, qkv.splits, qkv.rows * qkv.width, qkv.bias
+            target = q_buffer
+        else:
+            tokens = qkv.shape[0]
+            src, splits, stride, bias = qkv, 0, 0, None
+            target = qkv
+        self._rope_kv_write(_ptr(src), splits, stride, _ptr(bias), _ptr(target), target.shape[1],
+                            _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
                             table.shape[1], kv.num_pages, _ptr(kv.k), _ptr(kv.v), _ptr(inv_freq),
                             tokens, q_heads, kv_heads, head_dim, rot, kv.page_size,
-                            1 if write_cache else 0, self._code_of(qkv), _ptr(self.error_word),
+                            1 if write_cache else 0, self._code_of(target), _ptr(self.error_word),
                             self.stream)
+        return target
 
     def attention(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
                   head_dim: int, scale: float, window: int) -> None:
@@ -212,10 +357,11 @@ class Ops:
                                 kv_heads, head_dim, kv.page_size, scale, window,
                                 self._code_of(qkv), _ptr(self.error_word), self.stream)
 
-    def silu_mul(self, gate_up: Any, out: Any) -> None:
+    def silu_mul(self, gate_up: Any, out: Any, block: int | None = None) -> None:
         tokens, inter = out.shape
         self.launches += 1
-        self._silu_mul(_ptr(gate_up), _ptr(out), tokens, inter, self._code_of(out), self.stream)
+        self._silu_mul(_ptr(gate_up), _ptr(out), tokens, inter, inter if block is None else block,
+                       self._code_of(out), self.stream)
 
     def sample(self, logits: Any, temperature: Any, keys: Any, out: Any) -> None:
         """logits float32 [R, V]; temperature float32 [R] or None (greedy); keys int64 [R]."""

@@ -58,15 +58,12 @@ class TensorAttention:
             "cie_attention_decode",
             [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, f, i, v, v, v, v],
         )
-        self._scratch: dict[str, Any] = {}
 
-    def _buffer(self, name: str, elements: int) -> Any:
-        torch = self.ops.torch
-        held = self._scratch.get(name)
-        if held is None or held.numel() < elements:
-            held = torch.empty(max(elements, 1), dtype=torch.float32, device=self.ops.device)
-            self._scratch[name] = held
-        return held
+    def _buffer(self, name: str, per_slot: int, requests: int, q_heads: int, splits: int) -> Any:
+        # requests * splits never exceeds 2 * SM_COUNT + requests; reserve for 256 requests
+        reserve = (2 * SM_COUNT + max(requests, 256)) * q_heads * per_slot
+        return self.ops.scratch(f"attention.{name}.d{self.head_dim}",
+                                requests * q_heads * splits * per_slot, reserve=reserve)
 
     @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int) -> int:
@@ -90,8 +87,8 @@ class TensorAttention:
             splits = self.splits_for(requests, kv_heads, group, max_keys)
             partial_o = partial_ml = None
             if splits > 1:
-                partial_o = self._buffer("o", requests * q_heads * splits * self.head_dim)
-                partial_ml = self._buffer("ml", requests * q_heads * splits * 2)
+                partial_o = self._buffer("o", self.head_dim, requests, q_heads, splits)
+                partial_ml = self._buffer("ml", 2, requests, q_heads, splits)
             ops.launches += 2 if splits > 1 else 1
             self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                          kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,

@@ -92,20 +92,21 @@ class Attention(Mixer):
         rt = self.runtime
         tokens = x.shape[0]
         qkv = rt.workspace.get("attention.qkv", tokens, self.qkv_width, rt.dtype)
-        rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        # for few tokens the projection may come back as partial sums that the next kernel adds up
+        qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, allow_partials=True, tag="attention.qkv")
         kv = binding.kv
-        rt.ops.rope_kv_write(
+        q = rt.ops.rope_kv_write(
             qkv, ctx, kv, self.position, self.num_heads, self.num_kv_heads, self.head_dim,
             write_cache=binding.owns_cache,
+            q_buffer=rt.workspace.get("attention.q", tokens, self.q_width, rt.dtype),
         )
         mixed = rt.workspace.get("attention.out", tokens, self.q_width, rt.dtype)
         rt.ops.attention(
-            qkv, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
+            q, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
             self.scale, self.window,
         )
         update = rt.workspace.get("mixer.update", tokens, self.hidden_size, rt.dtype)
-        rt.ops.linear(mixed, self.w_o, None, update)
-        return update
+        return rt.ops.linear(mixed, self.w_o, None, update, allow_partials=True, tag="mixer.update")
 
 
 register_part("mixer", "attention", Attention, replace=True)

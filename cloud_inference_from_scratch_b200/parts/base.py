@@ -88,7 +88,9 @@ class Norm(Part):
         rows: "torch.Tensor | None" = None,
     ) -> "torch.Tensor":
         """``residual`` is the float32 stream [T, H].  Adds ``update`` to it in place (32-bit
-        sum) when given, and returns the normalised rows in the compute dtype.  With ``rows``
+        sum) when given, and returns the normalised rows in the compute dtype.  ``update`` is a
+        tensor [T, H] or the ``Partials`` a split matrix product returned (a norm that cannot
+        add those up itself calls ``runtime.ops.resolve``).  With ``rows``
         only those rows are normalised and returned, and ``residual`` is left as it was."""
         raise NotImplementedError
 

@@ -24,24 +24,18 @@ class SwiGLU(FeedForward):
         }
 
     def bind(self, tensors, runtime) -> None:
-        import torch
-
         self.runtime = runtime
-        self.w_gate_up = runtime.ops.prepare_weight(
-            torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]])
-        )
+        self.w_gate_up = runtime.ops.prepare_gate_up(tensors["gate_proj.weight"], tensors["up_proj.weight"])
         self.w_down = runtime.ops.prepare_weight(tensors["down_proj.weight"])
 
     def forward(self, x, ctx):
         rt = self.runtime
         tokens = x.shape[0]
-        gate_up = rt.workspace.get("swiglu.gate_up", tokens, 2 * self.intermediate_size, rt.dtype)
-        rt.ops.linear(x, self.w_gate_up, None, gate_up)
         hidden = rt.workspace.get("swiglu.hidden", tokens, self.intermediate_size, rt.dtype)
-        rt.ops.silu_mul(gate_up, hidden)
+        rt.ops.gate_up(x, self.w_gate_up, hidden, rt.workspace)
         update = rt.workspace.get("feed_forward.update", tokens, self.hidden_size, rt.dtype)
-        rt.ops.linear(hidden, self.w_down, None, update)
-        return update
+        return rt.ops.linear(hidden, self.w_down, None, update, allow_partials=True,
+                             tag="feed_forward.update")
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -366,3 +366,92 @@ def test_tensor_attention_far_key(ops):
 def test_tensor_attention_long_prompt_whole(ops):
     tensor_case(ops, 128, [0], [1500], 16, 2, 128, 16, seed=9)
     tensor_case(ops, 64, [300, 0], [700, 64], 14, 2, 64, 16, seed=10)
+
+
+# ------------------------------------------------------------------ streaming matrix product (decode)
+@pytest.mark.parametrize("m", [1, 2, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k", [(331, 96), (2560, 2048), (2048, 11008), (1000, 136)])
+def test_gemm_stream_outputs(ops, m, n, k):
+    item = ops[torch.bfloat16]
+    x = rand(m, k, dtype=torch.bfloat16, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n)
+    bias = rand(n, seed=k)
+    want = plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).cuda()
+    scale = float(want.abs().max())
+    out = torch.empty(m, n, dtype=torch.bfloat16).cuda()
+    assert item.stream_plan(m, n, k, False) is not None
+    assert item.linear(x, w, bias, out) is out
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2 * max(1.0, scale / 4))
+    logits = torch.empty(m, n, dtype=torch.float32).cuda()
+    item.linear(x, w, bias, logits)
+    torch.testing.assert_close(logits, want, rtol=2e-3, atol=2e-3 * max(1.0, scale))
+    parts = item.linear(x, w, bias, out, allow_partials=True, tag=f"test{n}")
+    if item.stream_plan(m, n, k, True)[1] > 1:
+        from cloud_inference_from_scratch_b200.native.ops import Partials
+
+        assert isinstance(parts, Partials) and parts.splits > 1
+        total = torch.empty(m, n, dtype=torch.float32).cuda()
+        item.resolve(parts, total)
+        torch.testing.assert_close(total, want, rtol=2e-3, atol=2e-3 * max(1.0, scale))
+        # the consumers add the parts up themselves
+        residual = rand(m, n, seed=3)
+        gain = 1 + rand(n, scale=0.1, seed=4)
+        normed = torch.empty(m, n, dtype=torch.bfloat16).cuda()
+        work = residual.clone()
+        item.add_rmsnorm(work, parts, gain, 1e-6, normed)
+        torch.testing.assert_close(work, residual + want, rtol=2e-3, atol=2e-3 * max(1.0, scale))
+        expect = plain_model.rms_norm((residual + want).cpu(), gain.cpu(), 1e-6).cuda()
+        torch.testing.assert_close(normed.float(), expect, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("m", [1, 8, 40])
+@pytest.mark.parametrize("inter", [208, 11008, 408])
+def test_gate_up_fused_silu(ops, m, inter):
+    item = ops[torch.bfloat16]
+    hidden = 256
+    gate = rand(inter, hidden, dtype=torch.bfloat16, scale=0.1, seed=1)
+    up = rand(inter, hidden, dtype=torch.bfloat16, scale=0.1, seed=2)
+    weight = item.prepare_gate_up(gate, up)
+    assert weight.block == (16 if inter % 16 == 0 else inter)
+    for rows in (m, 100):      # few rows: streaming kernel; many rows: product + SiLU kernel
+        x = rand(rows, hidden, dtype=torch.bfloat16, seed=rows)
+        out = torch.empty(rows, inter, dtype=torch.bfloat16).cuda()
+        from cloud_inference_from_scratch_b200.engine.runtime import Workspace
+
+        item.gate_up(x, weight, out, Workspace("cuda:0"))
+        xf = x.float().cpu()
+        want = torch.nn.functional.silu(xf @ gate.float().cpu().t()) * (xf @ up.float().cpu().t())
+        torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("splits_case", ["partials", "tensor"])
+def test_rope_from_partial_sums(ops, splits_case):
+    item = ops[torch.bfloat16]
+    q_heads, kv_heads, dim, page = 16, 2, 128, 16
+    width = (q_heads + 2 * kv_heads) * dim
+    tokens, hidden = 5, 2048
+    x = rand(tokens, hidden, dtype=torch.bfloat16, seed=1)
+    w = rand(width, hidden, dtype=torch.bfloat16, scale=0.03, seed=2)
+    bias = rand(width, seed=3)
+    qkv_buf = torch.empty(tokens, width, dtype=torch.bfloat16).cuda()
+    qkv = item.linear(x, w, bias, qkv_buf, allow_partials=splits_case == "partials", tag="ropetest")
+    positions = torch.tensor([0, 7, 15, 16, 300], dtype=torch.int32).cuda()
+    request = torch.arange(tokens, dtype=torch.int32).cuda()
+    k_pool, v_pool, table, _, total = paged_setup([1, 8, 16, 17, 301], page, kv_heads, dim, torch.bfloat16)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).cuda()
+    ctx = SimpleNamespace(positions=positions, request_of_token=request, block_tables=[table])
+    kv = SimpleNamespace(group=0, k=k_pool, v=v_pool, num_pages=total, page_size=page)
+    q_buffer = torch.zeros(tokens, q_heads * dim, dtype=torch.bfloat16).cuda()
+    q = item.rope_kv_write(qkv, ctx, kv, SimpleNamespace(rotary_dim=dim, inv_freq=inv_freq),
+                           q_heads, kv_heads, dim, q_buffer=q_buffer)
+    full = plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).view(tokens, -1, dim)
+    cos, sin = plain_model.rope_tables(dim, positions.cpu().tolist(), 1e6)
+    want_q = plain_model.apply_rope(full[:, :q_heads], cos, sin)
+    want_k = plain_model.apply_rope(full[:, q_heads:q_heads + kv_heads], cos, sin)
+    got_q = q.float().cpu()[:, :q_heads * dim].view(tokens, q_heads, dim)
+    torch.testing.assert_close(got_q, want_q, rtol=2e-2, atol=2e-2)
+    for t in range(tokens):
+        pos = int(positions[t])
+        page_id = int(table[t, pos // page])
+        torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(v_pool[page_id, :, pos % page].float().cpu(), full[t, q_heads + kv_heads:], rtol=2e-2, atol=2e-2)
