@@ -455,3 +455,67 @@ def test_rope_from_partial_sums(ops, splits_case):
         page_id = int(table[t, pos // page])
         torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(v_pool[page_id, :, pos % page].float().cpu(), full[t, q_heads + kv_heads:], rtol=2e-2, atol=2e-2)
+
+
+# ------------------------------------------------------------------ tcgen05 matrix product
+@pytest.fixture(scope="module")
+def tensor_ops():
+    from cloud_inference_from_scratch_b200.native import Ops
+
+    item = Ops("cuda:0", torch.bfloat16, gemm="tensor")
+    yield item
+    item.check_errors()
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 64), (128, 128, 128), (256, 384, 512), (2048, 2560, 2048), (200, 331, 96),
+    (65, 1000, 136), (1000, 64, 2048), (130, 2048, 11008), (300, 777, 1024),
+    (1, 128, 64), (8, 256, 512), (16, 2560, 2048), (17, 331, 96), (33, 1000, 136), (64, 2048, 11008),
+    (3, 151936, 256),
+])
+def test_gemm_tcgen05(tensor_ops, m, n, k):
+    item = tensor_ops
+    x = rand(m, k, dtype=torch.bfloat16, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n)
+    bias = rand(n, seed=k)
+    want = plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).cuda()
+    scale = max(1.0, float(want.abs().max()))
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16).cuda()
+    assert item._tensor_gemm.run(x, w, bias, out)
+    item.check_errors()
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2 * scale / 4)
+    logits = torch.full((m, n), float("nan"), dtype=torch.float32).cuda()
+    assert item._tensor_gemm.run(x, w, None, logits)
+    item.check_errors()
+    torch.testing.assert_close(logits, plain_model.linear(x.float().cpu(), w.float().cpu()).cuda(),
+                               rtol=2e-3, atol=2e-3 * scale)
+
+
+@pytest.mark.parametrize("m", [1, 8, 30, 64])
+@pytest.mark.parametrize("n,k,splits", [(2560, 2048, 4), (2048, 11008, 8), (384, 192, 3)])
+def test_gemm_tcgen05_partials(tensor_ops, m, n, k, splits):
+    item = tensor_ops
+    x = rand(m, k, dtype=torch.bfloat16, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n)
+    parts = torch.full((splits, m, n), float("nan"), dtype=torch.float32).cuda()
+    item._tensor_gemm.launch(x, w, None, parts, 2, splits)
+    item.check_errors()
+    want = plain_model.linear(x.float().cpu(), w.float().cpu()).cuda()
+    torch.testing.assert_close(parts.sum(0), want, rtol=2e-3, atol=2e-3 * max(1.0, float(want.abs().max())))
+
+
+@pytest.mark.parametrize("m", [1, 8, 40])
+def test_gemm_tcgen05_silu_epilogue(tensor_ops, m):
+    item = tensor_ops
+    hidden, inter = 256, 11008
+    gate = rand(inter, hidden, dtype=torch.bfloat16, scale=0.1, seed=1)
+    up = rand(inter, hidden, dtype=torch.bfloat16, scale=0.1, seed=2)
+    weight = item.prepare_gate_up(gate, up)
+    assert weight.block == 16
+    x = rand(m, hidden, dtype=torch.bfloat16, seed=m)
+    out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16).cuda()
+    item._tensor_gemm.launch(x, weight.weight, None, out, 3, 1)
+    item.check_errors()
+    xf = x.float().cpu()
+    want = torch.nn.functional.silu(xf @ gate.float().cpu().t()) * (xf @ up.float().cpu().t())
+    torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
