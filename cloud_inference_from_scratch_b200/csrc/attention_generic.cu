@@ -30,6 +30,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   __shared__ float q_s[kWarps][kMaxDim];
   __shared__ float p_s[kWarps][32];
   __shared__ long long off_s[kWarps][32];
+  pdl_wait();
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * kWarps + warp;
   if (item >= tokens * q_heads) return;
@@ -123,18 +125,17 @@ extern "C" int cie_attention_generic(const void* q, int q_stride, void* out, int
   const int blocks = (int)((items + kWarps - 1) / kWarps);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kFloat32) {
-    attention_generic_kernel<float><<<blocks, kWarps * 32, 0, s>>>(
+    CIE_LAUNCH("attention_generic", attention_generic_kernel<float>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
         positions, request_of_token, table, table_width, num_pages, tokens, q_heads, kv_heads, dim,
         page_size, scale, window, err);
   } else if (dtype == kBFloat16) {
-    attention_generic_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, s>>>(
+    CIE_LAUNCH("attention_generic", attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
         (const __nv_bfloat16*)v_pool, positions, request_of_token, table, table_width, num_pages, tokens,
         q_heads, kv_heads, dim, page_size, scale, window, err);
   } else {
     CIE_FAIL("attention_generic: unknown element type code %d", dtype);
   }
-  CIE_CHECK_LAUNCH("attention_generic");
   return 0;
 }

@@ -16,6 +16,8 @@
 // 64 or 128).  Here head sizes are the multiples of 16 up to 256, any page size and grouping.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 #include <cfloat>
 
 #ifndef HEAD_DIM
@@ -26,6 +28,7 @@ CIE_DEFINE_LAST_ERROR()
 
 namespace cie {
 
+namespace cg = cooperative_groups;
 using bf16 = __nv_bfloat16;
 constexpr int D = HEAD_DIM;
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
@@ -33,6 +36,8 @@ constexpr int ROW = D + 8;          // shared-memory row in elements: odd number
 constexpr int CHUNKS = D / 8;       // 16-byte pieces of a row
 constexpr int KSTEPS = D / 16;
 constexpr int NTILES_D = D / 8;
+constexpr int kErrTimeout = 8;
+constexpr uint32_t ROW_BYTES = D * sizeof(__nv_bfloat16);
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -44,6 +49,37 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// ---- bulk asynchronous copies (TMA without a tensor map) completing on an mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up (error bit, false) after about two seconds.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - start > 4000000000ll) {
+      atomicOr(err, kErrTimeout);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -99,8 +135,14 @@ __device__ __forceinline__ long long kv_offset(const Pools& pools, const int* ro
 template <int NB>
 __device__ __forceinline__ void scores(const uint32_t (&q_frag)[KSTEPS][4], const bf16* k_tile,
                                        float (&s)[NB * 2][4], int lane) {
+  // two accumulator sets (even and odd k-steps) halve the chain of dependent tensor-core
+  // instructions; they are added at the end
+  float s2[NB * 2][4];
 #pragma unroll
-  for (int i = 0; i < NB * 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+  for (int i = 0; i < NB * 2; ++i) {
+    s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.f;
+  }
   const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
   for (int kk = 0; kk < KSTEPS; ++kk) {
@@ -108,9 +150,18 @@ __device__ __forceinline__ void scores(const uint32_t (&q_frag)[KSTEPS][4], cons
     for (int nb = 0; nb < NB; ++nb) {
       uint32_t b[4];
       ldsm_x4(b, k_tile + (nb * 16 + (mi >> 1) * 8 + r) * ROW + kk * 16 + (mi & 1) * 8);
-      mma_bf16(s[2 * nb], q_frag[kk], b[0], b[1]);
-      mma_bf16(s[2 * nb + 1], q_frag[kk], b[2], b[3]);
+      if (kk & 1) {
+        mma_bf16(s2[2 * nb], q_frag[kk], b[0], b[1]);
+        mma_bf16(s2[2 * nb + 1], q_frag[kk], b[2], b[3]);
+      } else {
+        mma_bf16(s[2 * nb], q_frag[kk], b[0], b[1]);
+        mma_bf16(s[2 * nb + 1], q_frag[kk], b[2], b[3]);
+      }
     }
+  }
+#pragma unroll
+  for (int i = 0; i < NB * 2; ++i) {
+    s[i][0] += s2[i][0]; s[i][1] += s2[i][1]; s[i][2] += s2[i][2]; s[i][3] += s2[i][3];
   }
 }
 
@@ -138,20 +189,26 @@ __device__ __forceinline__ void accumulate(const float (&p)[NB * 2][4], const bf
 
 // Running-maximum softmax update for the two rows (g, g + 8) a thread holds.
 // s holds scores already multiplied by scale * log2(e); masked entries are -inf.
-template <int NT>
+// HALVES == 1: rows 8..15 of the block are not in use (at most 8 heads share a kv head) and are
+// skipped.  The accumulator is rescaled only when some row's maximum moved (a warp-wide vote).
+template <int NT, int HALVES = 2>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2],
                                                float (&o)[NTILES_D][4]) {
   float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
   for (int i = 0; i < NT; ++i) {
     tile_max[0] = fmaxf(tile_max[0], fmaxf(s[i][0], s[i][1]));
-    tile_max[1] = fmaxf(tile_max[1], fmaxf(s[i][2], s[i][3]));
+    if (HALVES == 2) tile_max[1] = fmaxf(tile_max[1], fmaxf(s[i][2], s[i][3]));
   }
-  float alpha[2];
+  float alpha[2] = {1.f, 1.f};
+  bool moved = false;
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < HALVES; ++h) {
     const float m_new = fmaxf(m[h], quad_max(tile_max[h]));
-    alpha[h] = (m_new == -INFINITY) ? 1.f : exp2f(m[h] - m_new);
+    if (m_new != m[h]) {
+      alpha[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new);
+      moved = true;
+    }
     m[h] = m_new;
   }
   float sum[2] = {0.f, 0.f};
@@ -159,19 +216,27 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
   for (int i = 0; i < NT; ++i) {
     s[i][0] = (m[0] == -INFINITY) ? 0.f : exp2f(s[i][0] - m[0]);
     s[i][1] = (m[0] == -INFINITY) ? 0.f : exp2f(s[i][1] - m[0]);
-    s[i][2] = (m[1] == -INFINITY) ? 0.f : exp2f(s[i][2] - m[1]);
-    s[i][3] = (m[1] == -INFINITY) ? 0.f : exp2f(s[i][3] - m[1]);
     sum[0] += s[i][0] + s[i][1];
-    sum[1] += s[i][2] + s[i][3];
+    if (HALVES == 2) {
+      s[i][2] = (m[1] == -INFINITY) ? 0.f : exp2f(s[i][2] - m[1]);
+      s[i][3] = (m[1] == -INFINITY) ? 0.f : exp2f(s[i][3] - m[1]);
+      sum[1] += s[i][2] + s[i][3];
+    } else {
+      s[i][2] = s[i][3] = 0.f;
+    }
   }
   l[0] = l[0] * alpha[0] + sum[0];
-  l[1] = l[1] * alpha[1] + sum[1];
+  if (HALVES == 2) l[1] = l[1] * alpha[1] + sum[1];
+  if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-  for (int i = 0; i < NTILES_D; ++i) {
-    o[i][0] *= alpha[0];
-    o[i][1] *= alpha[0];
-    o[i][2] *= alpha[1];
-    o[i][3] *= alpha[1];
+    for (int i = 0; i < NTILES_D; ++i) {
+      o[i][0] *= alpha[0];
+      o[i][1] *= alpha[0];
+      if (HALVES == 2) {
+        o[i][2] *= alpha[1];
+        o[i][3] *= alpha[1];
+      }
+    }
   }
 }
 
@@ -198,22 +263,22 @@ struct PrefillArgs {
   int* err;
 };
 
+// One 64-key tile: thread t < 64 copies key row t of K, thread 64 + t row t of V, each with one bulk
+// asynchronous copy of a whole row (a row never crosses a page, so any page size works).  Rows
+// outside [valid_lo, valid_hi) are not copied.  Thread 0 arms the stage's mbarrier.
 __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const int* row, int kvh, int k0,
-                                             int valid_lo, int valid_hi, bf16* k_dst, bf16* v_dst, int tid) {
-  // 128 threads, 64 rows: two threads per row, each copies half of the row's 16-byte pieces
-  const int r = tid >> 1, half = tid & 1;
+                                             int valid_lo, int valid_hi, bf16* k_dst, bf16* v_dst,
+                                             uint64_t* bar, int tid) {
+  const int lo = max(k0, valid_lo), hi = min(k0 + BN, valid_hi);
+  const int rows = max(0, hi - lo);
+  if (tid == 0) mbar_expect_tx(bar, (uint32_t)rows * 2u * ROW_BYTES);
+  const int r = tid & (BN - 1);
   const int key = k0 + r;
-  long long off = -1;
-  if (key >= valid_lo && key < valid_hi) off = kv_offset(a.pools, row, key, kvh, a.err);
-  const bool ok = off >= 0;
-  const bf16* ks = ok ? a.pools.k + off : a.pools.k;
-  const bf16* vs = ok ? a.pools.v + off : a.pools.v;
-#pragma unroll
-  for (int c = 0; c < CHUNKS / 2; ++c) {
-    const int chunk = half * (CHUNKS / 2) + c;
-    cp_async16(k_dst + r * ROW + chunk * 8, ks + chunk * 8, ok);
-    cp_async16(v_dst + r * ROW + chunk * 8, vs + chunk * 8, ok);
-  }
+  if (key < lo || key >= hi) return;
+  long long off = kv_offset(a.pools, row, key, kvh, a.err);
+  if (off < 0) off = (long long)kvh * a.pools.page_size * D;   // page 0: the copy must still happen
+  if (tid < BN) bulk_copy(k_dst + r * ROW, a.pools.k + off, ROW_BYTES, bar);
+  else bulk_copy(v_dst + r * ROW, a.pools.v + off, ROW_BYTES, bar);
 }
 
 __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const PrefillArgs a) {
@@ -221,6 +286,8 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [BM][ROW]
   bf16* k_s = q_s + BM * ROW;                     // [2][BN][ROW]
   bf16* v_s = k_s + 2 * BN * ROW;                 // [2][BN][ROW]
+  pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;
   const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * a.hpt;
@@ -246,8 +313,11 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
   const int k_begin = (valid_lo / BN) * BN;
   const int tiles = (valid_hi - k_begin + BN - 1) / BN;
 
-  load_kv_tile(a, table_row, kvh, k_begin, valid_lo, valid_hi, k_s, v_s, tid);
-  cp_async_commit();
+  __shared__ __align__(8) uint64_t bars[2];
+  if (tid < 2) mbar_init(&bars[tid], 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  __syncthreads();
+  load_kv_tile(a, table_row, kvh, k_begin, valid_lo, valid_hi, k_s, v_s, &bars[0], tid);
 
   uint32_t q_frag[KSTEPS][4];
   float o[NTILES_D][4];
@@ -265,15 +335,27 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
     row_pos[h] = (tok < ntok && hh < a.group) ? context + q0 + tok : -1;
   }
 
-  for (int it = 0; it < tiles; ++it) {
+  bool alive = true;
+  for (int it = 0; it < tiles && alive; ++it) {
     const int stage = it & 1;
-    if (it + 1 < tiles) {
+    if (it + 1 < tiles)
       load_kv_tile(a, table_row, kvh, k_begin + (it + 1) * BN, valid_lo, valid_hi,
-                   k_s + (stage ^ 1) * BN * ROW, v_s + (stage ^ 1) * BN * ROW, tid);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+                   k_s + (stage ^ 1) * BN * ROW, v_s + (stage ^ 1) * BN * ROW, &bars[stage ^ 1], tid);
+    if (it == 0) cp_async_wait<0>();   // the queries
+    alive = mbar_wait(&bars[stage], (it >> 1) & 1, a.err);
+    const int k0 = k_begin + it * BN;
+    {
+      // rows of this tile that were not copied: their V must not hold NaN or Inf bits
+      const int lo = max(k0, valid_lo), hi = min(k0 + BN, valid_hi);
+      if (hi - lo < BN) {
+        bf16* v_tile = v_s + stage * BN * ROW;
+        for (int e = tid; e < BN * (D / 2); e += PREFILL_WARPS * 32) {
+          const int r = e / (D / 2), c = e % (D / 2);
+          if (k0 + r < lo || k0 + r >= hi) reinterpret_cast<uint32_t*>(v_tile + r * ROW)[c] = 0u;
+        }
+        // these ordinary stores must be ordered before later bulk copies into the same stage
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
     }
     __syncthreads();
     if (it == 0) {
@@ -281,7 +363,6 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
       for (int kk = 0; kk < KSTEPS; ++kk)
         ldsm_x4(q_frag[kk], q_s + (warp * 16 + (lane & 15)) * ROW + kk * 16 + (lane >> 4) * 8);
     }
-    const int k0 = k_begin + it * BN;
     // a warp whose rows all lie before this tile's first key has nothing to add
     const int warp_pos_hi = context + q0 + min(ntok - 1, (warp * 16 + 15) / a.hpt);
     if (k0 <= warp_pos_hi) {
@@ -321,7 +402,14 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
 }
 
 // ------------------------------------------------------------------------------------ decode
-constexpr int DECODE_WARPS = 4, DN = 16;
+#ifndef DECODE_WARPS_N
+#define DECODE_WARPS_N 8
+#endif
+constexpr int DECODE_WARPS = DECODE_WARPS_N;
+#ifndef DECODE_KEYS
+#define DECODE_KEYS 16
+#endif
+constexpr int DN = DECODE_KEYS;   // keys per warp and iteration
 
 struct DecodeArgs {
   const bf16* q;          // row b of q_stride elements: the request's single query token
@@ -332,45 +420,73 @@ struct DecodeArgs {
   const int* context_lens;  // keys before the query token; it attends to context + 1 keys
   int group;
   int head_chunks;          // ceil(group / 16)
-  int splits;
+  int page_shift;           // log2(page_size), or -1 if it is not a power of two
+  int splits;               // CTAs per cluster: 1, 2, 4 or 8
   float scale_log2;
   int window;
-  float* partial_o;         // [requests][q_heads][splits][D]   (splits > 1)
-  float* partial_ml;        // [requests][q_heads][splits][2]
   int q_heads;
   int* err;
 };
 
-__device__ __forceinline__ void load_kv_tile16(const DecodeArgs& a, const int* row, int kvh, int k0,
-                                               int valid_hi, bf16* k_dst, bf16* v_dst, int lane) {
-  const int r = lane >> 1, half = lane & 1;
-  const int key = k0 + r;
-  long long off = -1;
-  if (key < valid_hi) off = kv_offset(a.pools, row, key, kvh, a.err);
-  const bool ok = off >= 0;
-  const bf16* ks = ok ? a.pools.k + off : a.pools.k;
-  const bf16* vs = ok ? a.pools.v + off : a.pools.v;
+constexpr int DECODE_PAGE_SLOTS = 1024;   // block-table entries of a CTA's key range kept in shared memory
+#ifndef DECODE_STAGES_N
+#define DECODE_STAGES_N (HEAD_DIM <= 128 ? 2 : 1)
+#endif
+constexpr int DECODE_STAGES = DECODE_STAGES_N;   // per warp; all but one in flight while one is multiplied
+
+// One DN-key tile of K and V for one warp with 16-byte cp.async: the 32 lanes walk the tile 16
+// rows at a time, two lanes per key row, each pair fetching whole 32-byte sectors.  The page of a
+// key comes from the CTA's copy of its block-table range (or from global memory if the range did
+// not fit).  Rows past `valid_hi` are filled with zeros.
+__device__ __forceinline__ void load_kv_tile_warp(const DecodeArgs& a, const int* row, const int* pages_s,
+                                                  int first_index, int cached, int kvh, int k0,
+                                                  int valid_hi, bf16* k_dst, bf16* v_dst, int lane) {
+  const int half = lane & 1;
 #pragma unroll
-  for (int c = 0; c < CHUNKS / 2; ++c) {
-    const int chunk = half * (CHUNKS / 2) + c;
-    cp_async16(k_dst + r * ROW + chunk * 8, ks + chunk * 8, ok);
-    cp_async16(v_dst + r * ROW + chunk * 8, vs + chunk * 8, ok);
+  for (int block = 0; block < DN / 16; ++block) {
+    const int r = block * 16 + (lane >> 1);
+    const int key = k0 + r;
+    long long off = -1;
+    if (key < valid_hi) {
+      int index, within;
+      if (a.page_shift >= 0) { index = key >> a.page_shift; within = key & (a.pools.page_size - 1); }
+      else { index = key / a.pools.page_size; within = key - index * a.pools.page_size; }
+      int page;
+      if (index - first_index < cached) page = pages_s[index - first_index];
+      else page = index < a.pools.table_width ? row[index] : -1;
+      if (page < 0 || page >= a.pools.num_pages) atomicOr(a.err, kErrBadPage);
+      else off = (((long long)page * a.pools.kv_heads + kvh) * a.pools.page_size + within) * D;
+    }
+    // one source pointer and one destination address per row; the pieces are constant offsets
+    const int bytes = off >= 0 ? 16 : 0;
+    const bf16* ks = a.pools.k + (off >= 0 ? off : 0) + half * 8;
+    const bf16* vs = a.pools.v + (off >= 0 ? off : 0) + half * 8;
+    const uint32_t kd = smem_u32(k_dst + r * ROW + half * 8), vd = smem_u32(v_dst + r * ROW + half * 8);
+#pragma unroll
+    for (int c = 0; c < CHUNKS / 2; ++c) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(kd + c * 32), "l"(ks + c * 16), "r"(bytes));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vd + c * 32), "l"(vs + c * 16), "r"(bytes));
+    }
   }
 }
 
 constexpr int DECODE_STAGE = 2 * DN * ROW;                       // K and V of one stage, elements
-constexpr int DECODE_WARP_ELEMS = 2 * DECODE_STAGE;              // two stages
+constexpr int DECODE_WARP_ELEMS = DECODE_STAGES * DECODE_STAGE;
 constexpr size_t DECODE_KV_BYTES = (size_t)DECODE_WARPS * DECODE_WARP_ELEMS * sizeof(bf16);
 constexpr size_t DECODE_MERGE_BYTES = (size_t)DECODE_WARPS * 16 * (D + 2) * sizeof(float);
 constexpr size_t DECODE_Q_BYTES = (size_t)16 * ROW * sizeof(bf16);
-constexpr size_t DECODE_SMEM =
-    DECODE_Q_BYTES + (DECODE_KV_BYTES > DECODE_MERGE_BYTES ? DECODE_KV_BYTES : DECODE_MERGE_BYTES);
+constexpr size_t DECODE_PART_BYTES = (size_t)16 * (D + 2) * sizeof(float);
+constexpr size_t DECODE_WORK_BYTES = DECODE_KV_BYTES > DECODE_MERGE_BYTES ? DECODE_KV_BYTES : DECODE_MERGE_BYTES;
+constexpr size_t DECODE_SMEM = DECODE_Q_BYTES + DECODE_WORK_BYTES + DECODE_PART_BYTES;
 
 __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                          // [16][ROW]
   bf16* kv_s = reinterpret_cast<bf16*>(smem_raw + DECODE_Q_BYTES);        // per warp: 2 stages of K,V
   float* merge_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES);   // aliased after the loop
+  float* part_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES + DECODE_WORK_BYTES);
+  pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * 16;
@@ -389,7 +505,30 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
     cp_async16(q_s + r * ROW + c * 8, src, ok);
   }
   cp_async_commit();
-  cp_async_wait<0>();
+  // this CTA's stretch of the block table goes to shared memory once, so that no tile load has
+  // to wait for a table entry from global memory first
+  __shared__ int pages_s[DECODE_PAGE_SLOTS];
+  const int first_index = begin / a.pools.page_size;
+  int cached = begin < end ? (end - 1) / a.pools.page_size - first_index + 1 : 0;
+  if (cached > DECODE_PAGE_SLOTS) cached = DECODE_PAGE_SLOTS;
+  for (int i = tid; i < cached; i += DECODE_WARPS * 32)
+    pages_s[i] = first_index + i < a.pools.table_width ? table_row[first_index + i] : -1;
+  __syncthreads();
+
+  bf16* mine = kv_s + warp * DECODE_WARP_ELEMS;
+  const int tiles = begin < end ? (end - begin + DN - 1) / DN : 0;
+  // warp w takes tiles w, w + 4, ...
+  auto issue = [&](int tile, int slot) {
+    if (tile < tiles) {
+      bf16* dst = mine + slot * DECODE_STAGE;
+      load_kv_tile_warp(a, table_row, pages_s, first_index, cached, kvh, begin + tile * DN, end, dst,
+                        dst + DN * ROW, lane);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int p = 0; p < DECODE_STAGES - 1; ++p) issue(warp + p * DECODE_WARPS, p);
+  cp_async_wait<DECODE_STAGES - 1>();   // the queries (first group) have landed
   __syncthreads();
   uint32_t q_frag[KSTEPS][4];
 #pragma unroll
@@ -402,38 +541,35 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   const int t4 = lane & 3;
 
-  bf16* mine = kv_s + warp * DECODE_WARP_ELEMS;
-  const int tiles = begin < end ? (end - begin + DN - 1) / DN : 0;
-  // warp w takes tiles w, w + 4, ...
-  int it = warp;
-  if (it < tiles) load_kv_tile16(a, table_row, kvh, begin + it * DN, end, mine, mine + DN * ROW, lane);
-  cp_async_commit();
   int stage = 0;
-  for (; it < tiles; it += DECODE_WARPS) {
-    const int next = it + DECODE_WARPS;
-    if (next < tiles) {
-      bf16* dst = mine + (stage ^ 1) * DECODE_STAGE;
-      load_kv_tile16(a, table_row, kvh, begin + next * DN, end, dst, dst + DN * ROW, lane);
-    }
-    cp_async_commit();
-    cp_async_wait<1>();
+  for (int it = warp; it < tiles; it += DECODE_WARPS) {
+    issue(it + (DECODE_STAGES - 1) * DECODE_WARPS, (stage + DECODE_STAGES - 1) % DECODE_STAGES);
+    cp_async_wait<DECODE_STAGES - 1>();
     __syncwarp();
     const bf16* k_tile = mine + stage * DECODE_STAGE;
     const bf16* v_tile = k_tile + DN * ROW;
-    float s[2][4];
-    scores<1>(q_frag, k_tile, s, lane);
     const int k0 = begin + it * DN;
+    float s[DN / 8][4];
+    scores<DN / 16>(q_frag, k_tile, s, lane);
+    if (k0 + DN <= end) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < DN / 8; ++i)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = k0 + i * 8 + 2 * t4 + (e & 1);
-        s[i][e] = key < end ? s[i][e] * a.scale_log2 : -INFINITY;
-      }
-    softmax_update<2>(s, m, l, o);
-    accumulate<1>(s, v_tile, o, lane);
+        for (int e = 0; e < 4; ++e) s[i][e] *= a.scale_log2;
+    } else {
+#pragma unroll
+      for (int i = 0; i < DN / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = k0 + i * 8 + 2 * t4 + (e & 1);
+          s[i][e] = key < end ? s[i][e] * a.scale_log2 : -INFINITY;
+        }
+    }
+    if (a.group - h0 <= 8) softmax_update<DN / 8, 1>(s, m, l, o);
+    else softmax_update<DN / 8, 2>(s, m, l, o);
+    accumulate<DN / 16>(s, v_tile, o, lane);
     __syncwarp();
-    stage ^= 1;
+    stage = (stage + 1) % DECODE_STAGES;
   }
   cp_async_wait<0>();
   __syncthreads();   // every warp is done with its K/V buffers: reuse them for the merge
@@ -456,51 +592,73 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < 16 * D; idx += DECODE_WARPS * 32) {
-    const int r = idx / D, d = idx % D;
-    if (h0 + r >= a.group) continue;
+  // this CTA's share: part_s[16][D + 2] = (unnormalised output, running maximum, sum)
+  for (int idx = tid; idx < 16 * (D + 1); idx += DECODE_WARPS * 32) {
+    const int r = idx / (D + 1), d = idx % (D + 1);
     float m_all = -INFINITY;
 #pragma unroll
     for (int w = 0; w < DECODE_WARPS; ++w) m_all = fmaxf(m_all, merge_s[(w * 16 + r) * (D + 2) + D]);
-    float sum = 0.f, acc = 0.f;
+    float acc = 0.f;
 #pragma unroll
     for (int w = 0; w < DECODE_WARPS; ++w) {
       const float mw = merge_s[(w * 16 + r) * (D + 2) + D];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m_all);
-      sum += merge_s[(w * 16 + r) * (D + 2) + D + 1] * f;
-      acc += merge_s[(w * 16 + r) * (D + 2) + d] * f;
+      // column D of a warp's block holds its maximum; column D + 1 its sum
+      acc += merge_s[(w * 16 + r) * (D + 2) + (d < D ? d : D + 1)] * f;
     }
-    const int head = kvh * a.group + h0 + r;
-    if (a.splits == 1) {
-      a.out[(size_t)request * a.out_stride + (size_t)head * D + d] =
-          __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+    if (d < D) {
+      part_s[r * (D + 2) + d] = acc;
     } else {
-      const size_t slot = ((size_t)request * a.q_heads + head) * a.splits + split;
-      a.partial_o[slot * D + d] = acc;
-      if (d == 0) {
-        a.partial_ml[slot * 2] = m_all;
-        a.partial_ml[slot * 2 + 1] = sum;
+      part_s[r * (D + 2) + D] = m_all;
+      part_s[r * (D + 2) + D + 1] = acc;
+    }
+  }
+  if (a.splits == 1) {
+    __syncthreads();
+    for (int idx = tid; idx < 16 * D; idx += DECODE_WARPS * 32) {
+      const int r = idx / D, d = idx % D;
+      if (h0 + r >= a.group) continue;
+      const float sum = part_s[r * (D + 2) + D + 1];
+      a.out[(size_t)request * a.out_stride + (size_t)(kvh * a.group + h0 + r) * D + d] =
+          __float2bfloat16_rn(sum > 0.f ? part_s[r * (D + 2) + d] / sum : 0.f);
+    }
+    return;
+  }
+  // ---- the CTAs of a cluster hold the splits of one (request, kv head, head chunk): after a
+  // cluster barrier each CTA merges some of the 16 head rows, reading its peers' shares through
+  // distributed shared memory.  No scratch in global memory, no second kernel.
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  const int rank = (int)cluster.block_rank();
+  for (int idx = tid; idx < 16 * D; idx += DECODE_WARPS * 32) {
+    const int r = idx / D, d = idx % D;
+    if (r % a.splits != rank || h0 + r >= a.group) continue;
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      if (c < a.splits) {
+        const float* peer = cluster.map_shared_rank(part_s, c);
+        ms[c] = peer[r * (D + 2) + D];
+        ls[c] = peer[r * (D + 2) + D + 1];
+        os[c] = peer[r * (D + 2) + d];
+      } else {
+        ms[c] = -INFINITY; ls[c] = 0.f; os[c] = 0.f;
       }
     }
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) m_all = fmaxf(m_all, ms[c]);
+    float sum = 0.f, acc = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float f = (ms[c] == -INFINITY) ? 0.f : exp2f(ms[c] - m_all);
+      sum += ls[c] * f;
+      acc += os[c] * f;
+    }
+    a.out[(size_t)request * a.out_stride + (size_t)(kvh * a.group + h0 + r) * D + d] =
+        __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
   }
-}
-
-__global__ void __launch_bounds__(D) combine_kernel(const float* __restrict__ partial_o,
-                                                    const float* __restrict__ partial_ml,
-                                                    bf16* __restrict__ out, int out_stride,
-                                                    int q_heads, int splits) {
-  const int request = blockIdx.x / q_heads, head = blockIdx.x % q_heads, d = threadIdx.x;
-  const size_t base = ((size_t)request * q_heads + head) * splits;
-  float m_all = -INFINITY;
-  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, partial_ml[(base + s) * 2]);
-  float sum = 0.f, acc = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = partial_ml[(base + s) * 2];
-    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - m_all);
-    sum += partial_ml[(base + s) * 2 + 1] * f;
-    acc += partial_o[(base + s) * D + d] * f;
-  }
-  out[(size_t)request * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+  cluster.sync();   // nobody leaves while a peer may still read its share
 }
 
 }  // namespace cie
@@ -538,41 +696,54 @@ extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int
     configured = true;
   }
   dim3 grid(num_tiles, kv_heads * a.head_chunks);
-  prefill_kernel<<<grid, PREFILL_WARPS * 32, smem, (cudaStream_t)stream>>>(a);
-  CIE_CHECK_LAUNCH("attention_prefill");
+  CIE_LAUNCH("attention_prefill", prefill_kernel, grid, dim3(PREFILL_WARPS * 32), smem, (cudaStream_t)stream, a);
   return 0;
 }
 
-// partial_o / partial_ml: float32 scratch of requests*q_heads*splits*D and *2 elements (splits > 1).
+// splits: CTAs that share the keys of one request (a thread-block cluster): 1, 2, 4 or 8.
 extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int out_stride,
                                     const void* k_pool, const void* v_pool, const int* table,
                                     int table_width, int num_pages, const int* context_lens,
                                     int requests, int q_heads, int kv_heads, int page_size,
-                                    int splits, float scale, int window, float* partial_o,
-                                    float* partial_ml, int* err, void* stream) {
+                                    int splits, float scale, int window, int* err, void* stream) {
   if (requests <= 0) return 0;
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_decode: %d query heads over %d kv heads", q_heads, kv_heads);
-  if (splits < 1) CIE_FAIL("attention_decode: splits %d", splits);
-  if (splits > 1 && (!partial_o || !partial_ml)) CIE_FAIL("attention_decode: split runs need scratch buffers");
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) CIE_FAIL("attention_decode: splits must be 1, 2, 4 or 8, got %d", splits);
   if (q_stride % 8) CIE_FAIL("attention_decode: row stride must keep 16-byte alignment");
   DecodeArgs a;
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
   a.pools = Pools{(const bf16*)k_pool, (const bf16*)v_pool, table, table_width, num_pages, kv_heads, page_size};
   a.context_lens = context_lens; a.group = q_heads / kv_heads; a.head_chunks = (a.group + 15) / 16;
-  a.splits = splits; a.scale_log2 = scale * kLog2e; a.window = window;
-  a.partial_o = partial_o; a.partial_ml = partial_ml; a.q_heads = q_heads; a.err = err;
+  a.splits = splits; a.scale_log2 = scale * kLog2e; a.window = window; a.q_heads = q_heads; a.err = err;
+  a.page_shift = -1;
+  for (int shift = 0; shift < 31; ++shift)
+    if ((1 << shift) == page_size) a.page_shift = shift;
   static bool configured = false;
   if (!configured) {
     cudaError_t status = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
     if (status != cudaSuccess) CIE_FAIL("attention_decode: shared memory %zu: %s", (size_t)DECODE_SMEM, cudaGetErrorString(status));
     configured = true;
   }
-  dim3 grid(splits, kv_heads * a.head_chunks, requests);
-  decode_kernel<<<grid, DECODE_WARPS * 32, DECODE_SMEM, (cudaStream_t)stream>>>(a);
-  CIE_CHECK_LAUNCH("attention_decode");
-  if (splits > 1) {
-    combine_kernel<<<requests * q_heads, D, 0, (cudaStream_t)stream>>>(partial_o, partial_ml, (bf16*)out, out_stride, q_heads, splits);
-    CIE_CHECK_LAUNCH("attention_combine");
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(splits, kv_heads * a.head_chunks, requests);
+  config.blockDim = dim3(DECODE_WARPS * 32);
+  config.dynamicSmemBytes = DECODE_SMEM;
+  config.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  attributes[count].id = cudaLaunchAttributeClusterDimension;
+  attributes[count].val.clusterDim.x = splits;
+  attributes[count].val.clusterDim.y = 1;
+  attributes[count].val.clusterDim.z = 1;
+  ++count;
+  if (pdl_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
   }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  cudaError_t status = cudaLaunchKernelEx(&config, decode_kernel, a);
+  if (status != cudaSuccess) CIE_FAIL("attention_decode: launch failed: %s", cudaGetErrorString(status));
   return 0;
 }

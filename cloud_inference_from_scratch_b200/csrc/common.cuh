@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 namespace cie {
 
@@ -63,6 +64,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
   return total;
 }
 
+// Programmatic dependent launch.  A kernel launched with the attribute may start while the
+// kernel before it in the stream is still running; `pdl_wait` blocks until that kernel (and, through
+// its own wait, every earlier one) has completed and its writes are visible.  Before the wait a
+// kernel may only do what does not depend on earlier kernels and writes nothing they read:
+// set-up and prefetching weights.  `pdl_trigger` lets the next kernel in the stream start its own
+// set-up.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char* value = getenv("CIE_PDL");
+    return !(value && value[0] == '0');
+  }();
+  return enabled;
+}
+
+// Launches `kernel` on `stream`, as a programmatic dependent of the kernel before it unless
+// CIE_PDL=0 is set in the environment.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
+}
+
 }  // namespace cie
 
 // Every library keeps the text of its last failure for the Python side to raise.
@@ -74,6 +110,13 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
   do {                                                                                \
     snprintf(cie_error_text, sizeof(cie_error_text), __VA_ARGS__);                    \
     return 1;                                                                         \
+  } while (0)
+
+#define CIE_LAUNCH(name, ...)                                                         \
+  do {                                                                                \
+    cudaError_t cie_status = cie::launch(__VA_ARGS__);                                \
+    if (cie_status != cudaSuccess)                                                    \
+      CIE_FAIL("%s: launch failed: %s", name, cudaGetErrorString(cie_status));        \
   } while (0)
 
 #define CIE_CHECK_LAUNCH(name)                                                        \

@@ -16,6 +16,8 @@ namespace cie {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ residual, int hidden, int vocab, int* err) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -34,6 +36,21 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 // `update` is either one tensor of the activation type, or (partial_splits > 0) float32 partial
 // sums [splits][rows][hidden] of a matrix product cut along K, plus an optional bias; the partial
 // sums are added in ascending split order.
+constexpr int kMaxSplits = 8;   // partial sums a consumer adds up (the streaming product cuts K at most so often)
+
+// Sum of up to kMaxSplits partial values; the loads are issued together, then added in split order.
+__device__ __forceinline__ float sum_partials(const float* __restrict__ part, int splits, size_t stride) {
+  float v[kMaxSplits];
+#pragma unroll
+  for (int s = 0; s < kMaxSplits; ++s) v[s] = s < splits ? part[(size_t)s * stride] : 0.f;
+  float total = v[0];
+#pragma unroll
+  for (int s = 1; s < kMaxSplits; ++s) total += v[s];
+  return total;
+}
+
+constexpr int kNormPerThread = 8;   // elements a thread keeps in registers (rows up to 8 * blockDim)
+
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict__ update,
                                    int partial_splits, size_t partial_stride,
@@ -41,6 +58,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
                                    const float* __restrict__ gain, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * hidden;
@@ -52,13 +71,34 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
     float x = res[i];
     if (upd) x += to_float(upd[i]);
     if (part) {
-      float u = part[i];
-      for (int s = 1; s < partial_splits; ++s) u += part[(size_t)s * partial_stride + i];
+      float u = sum_partials(part + i, partial_splits, partial_stride);
       if (update_bias) u += update_bias[i];
       x += u;
     }
     return x;
   };
+  T* dst = out + (size_t)r * hidden;
+  if (hidden <= kNormPerThread * (int)blockDim.x) {
+    float x[kNormPerThread];
+    float sumsq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kNormPerThread; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      x[j] = i < hidden ? value(i) : 0.f;
+      sumsq += x[j] * x[j];
+    }
+    const float total = block_sum(sumsq, scratch);
+    const float inv = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int j = 0; j < kNormPerThread; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < hidden) {
+        if (write_back) res[i] = x[j];
+        dst[i] = from_float<T>(gain[i] * (x[j] * inv));
+      }
+    }
+    return;
+  }
   float sumsq = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float x = value(i);
@@ -67,7 +107,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
   }
   const float total = block_sum(sumsq, scratch);
   const float inv = rsqrtf(total / (float)hidden + eps);
-  T* dst = out + (size_t)r * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float x = write_back ? res[i] : value(i);
     dst[i] = from_float<T>(gain[i] * (x * inv));
@@ -91,6 +130,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const float* __restrict__ inv_freq, int q_heads, int kv_heads,
                                      int dim, int rot, int page_size, int write_cache, int* err) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int width = (q_heads + 2 * kv_heads) * dim;
@@ -98,8 +139,7 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
   const float* row_p = partial_splits > 0 ? reinterpret_cast<const float*>(src) + (size_t)t * width : nullptr;
   auto value = [&](int i) {
     if (row_t) return to_float(row_t[i]);
-    float v = row_p[i];
-    for (int s = 1; s < partial_splits; ++s) v += row_p[(size_t)s * partial_stride + i];
+    float v = sum_partials(row_p + i, partial_splits, partial_stride);
     if (bias) v += bias[i];
     return v;
   };
@@ -165,6 +205,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens,
                                 int inter, int block) {
+  pdl_wait();
+  pdl_trigger();
   const size_t total = (size_t)tokens * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -196,10 +238,9 @@ extern "C" int cie_embedding(const int* ids, const void* table, float* residual,
                              int hidden, int vocab, int dtype, int* err, void* stream) {
   if (tokens <= 0) return 0;
   DISPATCH_DTYPE(dtype, "embedding", {
-    embedding_kernel<T><<<tokens, threads_for(hidden / 4), 0, (cudaStream_t)stream>>>(
-        ids, (const T*)table, residual, hidden, vocab, err);
+    CIE_LAUNCH("embedding", embedding_kernel<T>, dim3(tokens), dim3(threads_for(hidden / 4)), 0,
+               (cudaStream_t)stream, ids, (const T*)table, residual, hidden, vocab, err);
   })
-  CIE_CHECK_LAUNCH("embedding");
   return 0;
 }
 
@@ -208,12 +249,12 @@ extern "C" int cie_add_rmsnorm(float* residual, const void* update, int partial_
                                const float* gain, void* out, const int* rows, int count, int hidden,
                                float eps, int dtype, void* stream) {
   if (count <= 0) return 0;
+  if (partial_splits > kMaxSplits) CIE_FAIL("add_rmsnorm: at most %d partial sums, got %d", kMaxSplits, partial_splits);
   DISPATCH_DTYPE(dtype, "add_rmsnorm", {
-    add_rmsnorm_kernel<T><<<count, threads_for(hidden / 4), 0, (cudaStream_t)stream>>>(
-        residual, update, partial_splits, (size_t)partial_stride, update_bias, gain, (T*)out, rows,
-        hidden, eps);
+    CIE_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, dim3(count), dim3(threads_for(hidden / 4)), 0,
+               (cudaStream_t)stream, residual, update, partial_splits, (size_t)partial_stride,
+               update_bias, gain, (T*)out, rows, hidden, eps);
   })
-  CIE_CHECK_LAUNCH("add_rmsnorm");
   return 0;
 }
 
@@ -225,14 +266,14 @@ extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long 
                                  int page_size, int write_cache, int dtype, int* err, void* stream) {
   if (tokens <= 0) return 0;
   if (rot % 2 || rot > dim || rot < 0) CIE_FAIL("rope_kv_write: rotary size %d does not fit head size %d", rot, dim);
+  if (partial_splits > kMaxSplits) CIE_FAIL("rope_kv_write: at most %d partial sums, got %d", kMaxSplits, partial_splits);
   DISPATCH_DTYPE(dtype, "rope_kv_write", {
     const int work = (q_heads + kv_heads) * (rot / 2) > kv_heads * dim ? (q_heads + kv_heads) * (rot / 2) : kv_heads * dim;
-    rope_kv_write_kernel<T><<<tokens, threads_for(work), 0, (cudaStream_t)stream>>>(
-        src, partial_splits, (size_t)partial_stride, bias, (T*)q_out, q_stride, positions,
-        request_of_token, table, table_width, num_pages, (T*)k_pool, (T*)v_pool, inv_freq, q_heads,
-        kv_heads, dim, rot, page_size, write_cache, err);
+    CIE_LAUNCH("rope_kv_write", rope_kv_write_kernel<T>, dim3(tokens), dim3(threads_for(work)), 0,
+               (cudaStream_t)stream, src, partial_splits, (size_t)partial_stride, bias, (T*)q_out,
+               q_stride, positions, request_of_token, table, table_width, num_pages, (T*)k_pool,
+               (T*)v_pool, inv_freq, q_heads, kv_heads, dim, rot, page_size, write_cache, err);
   })
-  CIE_CHECK_LAUNCH("rope_kv_write");
   return 0;
 }
 
@@ -244,8 +285,8 @@ extern "C" int cie_silu_mul(const void* gate_up, void* out, int tokens, int inte
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   DISPATCH_DTYPE(dtype, "silu_mul", {
-    silu_mul_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, tokens, inter, block);
+    CIE_LAUNCH("silu_mul", silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+               (const T*)gate_up, (T*)out, tokens, inter, block);
   })
-  CIE_CHECK_LAUNCH("silu_mul");
   return 0;
 }

@@ -19,6 +19,8 @@ gemm_simt_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w, const flo
                  TOut* __restrict__ c, int m_total, int n_total, int k_total) {
   __shared__ float a_tile[kTileK][kTileM + 4];
   __shared__ float w_tile[kTileK][kTileN + 4];
+  pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * kTileM, n0 = blockIdx.x * kTileN;
   const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
@@ -71,6 +73,8 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256)
 gemm_small_m_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w, const float* __restrict__ bias,
                     TOut* __restrict__ c, int m_total, int n_total, int k_total) {
+  pdl_wait();
+  pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= n_total) return;
   const TIn* wrow = w + (size_t)warp * k_total;
@@ -99,16 +103,16 @@ gemm_small_m_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w, const 
 using namespace cie;
 
 template <typename TIn, typename TOut>
-static void launch(const void* a, const void* w, const float* bias, void* c, int m, int n, int k,
-                   int allow_small, cudaStream_t stream) {
+static cudaError_t launch_simt(const void* a, const void* w, const float* bias, void* c, int m, int n,
+                               int k, int allow_small, cudaStream_t stream) {
   if (allow_small && m <= kSmallM) {
     const int warps_per_block = 8;
-    gemm_small_m_kernel<TIn, TOut><<<(n + warps_per_block - 1) / warps_per_block, 256, 0, stream>>>(
-        (const TIn*)a, (const TIn*)w, bias, (TOut*)c, m, n, k);
-    return;
+    return cie::launch(gemm_small_m_kernel<TIn, TOut>, dim3((n + warps_per_block - 1) / warps_per_block),
+                       dim3(256), 0, stream, (const TIn*)a, (const TIn*)w, bias, (TOut*)c, m, n, k);
   }
   dim3 grid((n + kTileN - 1) / kTileN, (m + kTileM - 1) / kTileM);
-  gemm_simt_kernel<TIn, TOut><<<grid, 256, 0, stream>>>((const TIn*)a, (const TIn*)w, bias, (TOut*)c, m, n, k);
+  return cie::launch(gemm_simt_kernel<TIn, TOut>, grid, dim3(256), 0, stream, (const TIn*)a,
+                     (const TIn*)w, bias, (TOut*)c, m, n, k);
 }
 
 // in_dtype: element type of A and W; out_dtype: element type of C (float32 for logits).
@@ -118,10 +122,11 @@ extern "C" int cie_gemm_simt(const void* a, const void* w, const float* bias, vo
   if (m <= 0 || n <= 0) return 0;
   if (k <= 0) CIE_FAIL("gemm_simt: K must be positive, got %d", k);
   cudaStream_t s = (cudaStream_t)stream;
-  if (in_dtype == kFloat32 && out_dtype == kFloat32) launch<float, float>(a, w, bias, c, m, n, k, allow_small, s);
-  else if (in_dtype == kBFloat16 && out_dtype == kBFloat16) launch<__nv_bfloat16, __nv_bfloat16>(a, w, bias, c, m, n, k, allow_small, s);
-  else if (in_dtype == kBFloat16 && out_dtype == kFloat32) launch<__nv_bfloat16, float>(a, w, bias, c, m, n, k, allow_small, s);
+  cudaError_t status;
+  if (in_dtype == kFloat32 && out_dtype == kFloat32) status = launch_simt<float, float>(a, w, bias, c, m, n, k, allow_small, s);
+  else if (in_dtype == kBFloat16 && out_dtype == kBFloat16) status = launch_simt<__nv_bfloat16, __nv_bfloat16>(a, w, bias, c, m, n, k, allow_small, s);
+  else if (in_dtype == kBFloat16 && out_dtype == kFloat32) status = launch_simt<__nv_bfloat16, float>(a, w, bias, c, m, n, k, allow_small, s);
   else CIE_FAIL("gemm_simt: unsupported element types in=%d out=%d", in_dtype, out_dtype);
-  CIE_CHECK_LAUNCH("gemm_simt");
+  if (status != cudaSuccess) CIE_FAIL("gemm_simt: launch failed: %s", cudaGetErrorString(status));
   return 0;
 }

@@ -70,11 +70,14 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
   const int k_end = min(a.k, k_begin + a.k_per_split);
   const int steps = (k_end - k_begin + BK - 1) / BK;
 
-  auto load_stage = [&](int step) {
-    const int slot = step % STAGES;
-    const int k0 = k_begin + step * BK;
-    bf16* wd = w_s + slot * BN * WROW;
-    bf16* xd = x_s + slot * MP * WROW;
+  // CTAs walk their K slice from different starting tiles, so that hundreds of CTAs do not ask
+  // L2 for the same lines of x at the same moment
+  const int rotate = steps > 0 ? (int)(blockIdx.x % (unsigned)steps) : 0;
+  auto load_w = [&](int step) {
+    int tile = step + rotate;
+    if (tile >= steps) tile -= steps;
+    const int k0 = k_begin + tile * BK;
+    bf16* wd = w_s + (step % STAGES) * BN * WROW;
 #pragma unroll
     for (int i = 0; i < (BN * 16) / THREADS; ++i) {   // BN rows x 16 pieces of 16 bytes
       const int e = tid + i * THREADS;
@@ -83,6 +86,12 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
       const bool ok = row < a.n && col < k_end;
       cp_async16(wd + r * WROW + c * 8, ok ? a.w + (size_t)row * a.k + col : a.w, ok);
     }
+  };
+  auto load_x = [&](int step) {
+    int tile = step + rotate;
+    if (tile >= steps) tile -= steps;
+    const int k0 = k_begin + tile * BK;
+    bf16* xd = x_s + (step % STAGES) * MP * WROW;
     for (int e = tid; e < MP * 16; e += THREADS) {
       const int r = e >> 4, c = e & 15;
       const int col = k0 + c * 8;
@@ -90,10 +99,21 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
       cp_async16(xd + r * WROW + c * 8, ok ? a.x + (size_t)r * a.k + col : a.x, ok);
     }
   };
+  auto load_stage = [&](int step) {
+    load_w(step);
+    load_x(step);
+  };
 
+  // The weights do not depend on the kernel before this one: their first tiles are requested
+  // before waiting for it, so the weight stream overlaps the tail of that kernel.
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s)
+    if (s < steps) load_w(s);
+  pdl_wait();
+  pdl_trigger();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < steps) load_stage(s);
+    if (s < steps) load_x(s);
     cp_async_commit();
   }
 
@@ -178,8 +198,7 @@ static int launch(const StreamArgs& a, int splits, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid((a.n + BN - 1) / BN, splits);
-  gemm_stream_kernel<MT, BN><<<grid, BN * 2, smem, stream>>>(a);
-  CIE_CHECK_LAUNCH("gemm_stream");
+  CIE_LAUNCH("gemm_stream", gemm_stream_kernel<MT, BN>, grid, dim3(BN * 2), smem, stream, a);
   return 0;
 }
 

@@ -128,6 +128,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   __shared__ __align__(8) uint64_t acc_bar;
   __shared__ uint32_t tmem_base_s;
 
+  pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int a_row0 = blockIdx.x * BM;
   const int b_row0 = blockIdx.y * BN;
@@ -346,8 +348,7 @@ static int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcAr
     if (status != cudaSuccess) CIE_FAIL("gemm_tcgen05: shared memory %zu: %s", smem, cudaGetErrorString(status));
     configured = true;
   }
-  gemm_tc_kernel<BN, STAGES><<<grid, 128, smem, stream>>>(map_a, map_b, a);
-  CIE_CHECK_LAUNCH("gemm_tcgen05");
+  CIE_LAUNCH("gemm_tcgen05", gemm_tc_kernel<BN, STAGES>, grid, dim3(128), smem, stream, map_a, map_b, a);
   return 0;
 }
 

@@ -36,6 +36,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   __shared__ float seg_sum[kThreads];
   __shared__ float bcast[2];
   __shared__ int chosen;
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)r * vocab;
 
@@ -115,7 +117,7 @@ extern "C" int cie_sample(const float* logits, int rows, int vocab, const float*
   if (rows <= 0) return 0;
   if (vocab < 1) CIE_FAIL("sample: vocabulary size %d", vocab);
   if (temperature && !keys) CIE_FAIL("sample: temperature rows need draw keys");
-  sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, vocab, temperature, keys, out);
-  CIE_CHECK_LAUNCH("sample");
+  CIE_LAUNCH("sample", sample_kernel, dim3(rows), dim3(kThreads), 0, (cudaStream_t)stream, logits,
+             vocab, temperature, keys, out);
   return 0;
 }

@@ -50,7 +50,7 @@ class GateUpWeight:
 
 
 SM_COUNT = 148
-STREAM_MAX_ROWS = 64
+STREAM_MAX_ROWS = 16   # more rows than this go to the tile kernels (tcgen05 or the library)
 
 
 class _Lib:
@@ -197,11 +197,11 @@ class Ops:
         is not its kind (more than 64 rows, or K not a multiple of 8)."""
         if self._gemm_stream is None or m > STREAM_MAX_ROWS or k % 8 or k < 8:
             return None
-        block_rows = 64 if (m > 16 and n >= 64 * 2 * SM_COUNT) else 32
+        block_rows = 32
         tiles = -(-n // block_rows)
         splits = 1
         if allow_partials:
-            splits = max(1, min(-(-2 * SM_COUNT // tiles), k // 512))
+            splits = max(1, min(-(-4 * SM_COUNT // tiles), k // 256, 8))
         return block_rows, splits
 
     def scratch(self, tag: str, elements: int, reserve: int = 0) -> Any:

@@ -17,7 +17,7 @@ from .build import load_library
 
 BM = 64            # query rows of a prefill tile (must match the kernel)
 SM_COUNT = 148
-MIN_KEYS_PER_SPLIT = 256
+MIN_KEYS_PER_SPLIT = 128
 
 
 def supports(head_dim: int) -> bool:
@@ -56,20 +56,21 @@ class TensorAttention:
         )
         self._decode = lib.function(
             "cie_attention_decode",
-            [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, f, i, v, v, v, v],
+            [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, f, i, v, v],
         )
-
-    def _buffer(self, name: str, per_slot: int, requests: int, q_heads: int, splits: int) -> Any:
-        # requests * splits never exceeds 2 * SM_COUNT + requests; reserve for 256 requests
-        reserve = (2 * SM_COUNT + max(requests, 256)) * q_heads * per_slot
-        return self.ops.scratch(f"attention.{name}.d{self.head_dim}",
-                                requests * q_heads * splits * per_slot, reserve=reserve)
 
     @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int) -> int:
+        """CTAs (of one cluster) that share a request's keys: enough to put work on every SM,
+        at least MIN_KEYS_PER_SPLIT keys each, a power of two up to 8."""
         ctas = requests * kv_heads * -(-group // 16)
-        wanted = -(-2 * SM_COUNT // ctas)
-        return max(1, min(wanted, max_keys // MIN_KEYS_PER_SPLIT))
+        limit = max(1, max_keys // MIN_KEYS_PER_SPLIT)
+        splits = 1
+        while splits < 8 and ctas * splits * 2 <= SM_COUNT and splits * 2 <= limit:
+            splits *= 2
+        if splits == 8 and ctas * splits > SM_COUNT // 2:
+            splits = 4   # big clusters cost more than they bring once half the SMs have work
+        return splits
 
     def run(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
             scale: float, window: int, plan: dict[str, Any] | None = None) -> bool:
@@ -85,18 +86,11 @@ class TensorAttention:
             if window > 0:
                 max_keys = min(max_keys, window)
             splits = self.splits_for(requests, kv_heads, group, max_keys)
-            partial_o = partial_ml = None
-            if splits > 1:
-                partial_o = self._buffer("o", self.head_dim, requests, q_heads, splits)
-                partial_ml = self._buffer("ml", 2, requests, q_heads, splits)
-            ops.launches += 2 if splits > 1 else 1
+            ops.launches += 1
             self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                          kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
                          ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, kv.page_size,
-                         splits, scale, window,
-                         None if partial_o is None else partial_o.data_ptr(),
-                         None if partial_ml is None else partial_ml.data_ptr(),
-                         ops.error_word.data_ptr(), ops.stream)
+                         splits, scale, window, ops.error_word.data_ptr(), ops.stream)
             return True
         if plan is None:
             tiles = plan_tiles(ctx.host.query_lens, group)

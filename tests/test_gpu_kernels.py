@@ -369,7 +369,7 @@ def test_tensor_attention_long_prompt_whole(ops):
 
 
 # ------------------------------------------------------------------ streaming matrix product (decode)
-@pytest.mark.parametrize("m", [1, 2, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("m", [1, 2, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(331, 96), (2560, 2048), (2048, 11008), (1000, 136)])
 def test_gemm_stream_outputs(ops, m, n, k):
     item = ops[torch.bfloat16]
@@ -404,7 +404,7 @@ def test_gemm_stream_outputs(ops, m, n, k):
         torch.testing.assert_close(normed.float(), expect, rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("m", [1, 8, 40])
+@pytest.mark.parametrize("m", [1, 8, 16])
 @pytest.mark.parametrize("inter", [208, 11008, 408])
 def test_gate_up_fused_silu(ops, m, inter):
     item = ops[torch.bfloat16]
