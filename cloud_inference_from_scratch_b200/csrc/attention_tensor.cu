@@ -241,7 +241,7 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
 }
 
 // ------------------------------------------------------------------------------------ prefill
-constexpr int BM = 64, BN = 64, PREFILL_WARPS = 4;
+constexpr int BM = 128, BN = 64, PREFILL_WARPS = 8;
 
 struct PrefillArgs {
   const bf16* q;
@@ -272,6 +272,7 @@ __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const int* ro
   const int lo = max(k0, valid_lo), hi = min(k0 + BN, valid_hi);
   const int rows = max(0, hi - lo);
   if (tid == 0) mbar_expect_tx(bar, (uint32_t)rows * 2u * ROW_BYTES);
+  if (tid >= 2 * BN) return;
   const int r = tid & (BN - 1);
   const int key = k0 + r;
   if (key < lo || key >= hi) return;

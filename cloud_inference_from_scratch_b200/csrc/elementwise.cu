@@ -118,7 +118,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
 // k is rotated and written, v is copied, to pool[page][kv_head][pos % page][D] with
 // page = table[request][pos / page].  Element j < rot/2 pairs with j + rot/2 (rotate-half).
 // The source row is either qkv itself (partial_splits == 0; then q_out == qkv and q is rotated
-// in place) or float32 partial sums [splits][T][width] of the projection plus its bias
+// in place; a bias not yet added may be given) or float32 partial sums [splits][T][width] of the projection plus its bias
 // (partial_splits > 0; then the rotated q is written to q_out, rows of q_stride elements).
 template <typename T>
 __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_splits,
@@ -138,7 +138,7 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
   const T* row_t = partial_splits == 0 ? reinterpret_cast<const T*>(src) + (size_t)t * width : nullptr;
   const float* row_p = partial_splits > 0 ? reinterpret_cast<const float*>(src) + (size_t)t * width : nullptr;
   auto value = [&](int i) {
-    if (row_t) return to_float(row_t[i]);
+    if (row_t) return bias ? to_float(row_t[i]) + bias[i] : to_float(row_t[i]);
     float v = sum_partials(row_p + i, partial_splits, partial_stride);
     if (bias) v += bias[i];
     return v;
@@ -161,27 +161,30 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
   }
   const size_t head_stride = (size_t)page_size * dim;
 
-  // rotated pairs of q and k heads
+  // rotated pairs of q and k heads: a thread owns pair j of some heads, so the sine and cosine
+  // of (position, j) are computed once per thread, not once per head
   const int rot_heads = q_heads + kv_heads;
-  for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
-    const int h = i / half, j = i % half;
-    const float angle = (float)pos * inv_freq[j];
+  const int lanes_per_head_set = half > 0 ? max(1, (int)blockDim.x / half) : 1;
+  if (half > 0 && threadIdx.x < lanes_per_head_set * half) {
+    const int j = threadIdx.x % half, first_head = threadIdx.x / half;
     float s, c;
-    sincosf(angle, &s, &c);
-    const float a = value(h * dim + j), b = value(h * dim + j + half);
-    const T ra = from_float<T>(a * c - b * s), rb = from_float<T>(b * c + a * s);
-    if (h < q_heads) {
-      q_row[h * dim + j] = ra;
-      q_row[h * dim + j + half] = rb;
-    } else if (slot_ok) {
-      T* dst = k_pool + slot_base + (size_t)(h - q_heads) * head_stride;
-      dst[j] = ra;
-      dst[j + half] = rb;
+    sincosf((float)pos * inv_freq[j], &s, &c);
+    for (int h = first_head; h < rot_heads; h += lanes_per_head_set) {
+      const float a = value(h * dim + j), b = value(h * dim + j + half);
+      const T ra = from_float<T>(a * c - b * s), rb = from_float<T>(b * c + a * s);
+      if (h < q_heads) {
+        q_row[h * dim + j] = ra;
+        q_row[h * dim + j + half] = rb;
+      } else if (slot_ok) {
+        T* dst = k_pool + slot_base + (size_t)(h - q_heads) * head_stride;
+        dst[j] = ra;
+        dst[j + half] = rb;
+      }
     }
   }
   // the part of q and k beyond the rotary dims passes through
   const int tail = dim - rot;
-  if (tail > 0 && row_p) {
+  if (tail > 0 && (row_p || bias)) {
     for (int i = threadIdx.x; i < q_heads * tail; i += blockDim.x) {
       const int h = i / tail, d = rot + i % tail;
       q_row[h * dim + d] = from_float<T>(value(h * dim + d));
@@ -216,6 +219,33 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     const float g = to_float(gate_up[t * 2 * inter + col]);
     const float u = to_float(gate_up[t * 2 * inter + col + block]);
     out[i] = from_float<T>((g / (1.f + expf(-g))) * u);
+  }
+}
+
+// bfloat16, 8 channels (16 bytes) per thread; needs inter % 8 == 0 and block % 8 == 0.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up,
+                                       __nv_bfloat16* __restrict__ out, int tokens, int inter, int block) {
+  pdl_wait();
+  pdl_trigger();
+  const int vectors = inter / 8;
+  const size_t total = (size_t)tokens * vectors;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
+       v += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = v / vectors;
+    const int c = (int)(v % vectors) * 8;
+    const size_t col = (size_t)(c / block) * 2 * block + c % block;
+    const uint4 graw = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + col);
+    const uint4 uraw = *reinterpret_cast<const uint4*>(gate_up + t * 2 * inter + col + block);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    uint4 packed;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+      o2[j] = __floats2bfloat162_rn((g.x / (1.f + expf(-g.x))) * u.x, (g.y / (1.f + expf(-g.y))) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + c) = packed;
   }
 }
 
@@ -269,7 +299,10 @@ extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long 
   if (partial_splits > kMaxSplits) CIE_FAIL("rope_kv_write: at most %d partial sums, got %d", kMaxSplits, partial_splits);
   DISPATCH_DTYPE(dtype, "rope_kv_write", {
     const int work = (q_heads + kv_heads) * (rot / 2) > kv_heads * dim ? (q_heads + kv_heads) * (rot / 2) : kv_heads * dim;
-    CIE_LAUNCH("rope_kv_write", rope_kv_write_kernel<T>, dim3(tokens), dim3(threads_for(work)), 0,
+    // few tokens: spread one token over many threads; many tokens: fewer threads that each reuse
+    // a pair's sine and cosine over several heads
+    const int threads = tokens <= 64 ? threads_for(work) : 256;
+    CIE_LAUNCH("rope_kv_write", rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), 0,
                (cudaStream_t)stream, src, partial_splits, (size_t)partial_stride, bias, (T*)q_out,
                q_stride, positions, request_of_token, table, table_width, num_pages, (T*)k_pool,
                (T*)v_pool, inv_freq, q_heads, kv_heads, dim, rot, page_size, write_cache, err);
@@ -282,6 +315,14 @@ extern "C" int cie_silu_mul(const void* gate_up, void* out, int tokens, int inte
   if (tokens <= 0) return 0;
   if (block < 1 || inter % block) CIE_FAIL("silu_mul: %d channels do not divide into blocks of %d", inter, block);
   const size_t total = (size_t)tokens * inter;
+  if (dtype == kBFloat16 && inter % 8 == 0 && block % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    int vblocks = (int)((total / 8 + 255) / 256);
+    if (vblocks > 148 * 16) vblocks = 148 * 16;
+    CIE_LAUNCH("silu_mul", silu_mul_bf16x8_kernel, dim3(vblocks), dim3(256), 0, (cudaStream_t)stream,
+               (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, tokens, inter, block);
+    return 0;
+  }
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   DISPATCH_DTYPE(dtype, "silu_mul", {

@@ -28,9 +28,13 @@ def _ptr(tensor: Any) -> int | None:
 
 
 class Partials:
-    """Float32 partial sums [splits, rows, width] of a matrix product that was cut along K, with
-    the bias still to be added.  The kernels that consume a projection (residual-add + RMSNorm,
-    rotary + cache write) add the parts up themselves, in ascending split order."""
+    """A projection whose last additions are left to the kernel that consumes it.
+
+    ``splits`` > 0: ``data`` holds float32 partial sums [splits, rows, width] of a matrix product
+    that was cut along K.  ``splits`` == 0: ``data`` is the product itself [rows, width] in the
+    compute dtype.  In both cases ``bias`` (or None) is still to be added.  The consumers
+    (residual-add + RMSNorm, rotary + cache write) add everything up in float32, parts in
+    ascending split order."""
 
     def __init__(self, data: Any, splits: int, rows: int, width: int, bias: Any) -> None:
         self.data, self.splits, self.rows, self.width, self.bias = data, splits, rows, width, bias
@@ -184,6 +188,8 @@ class Ops:
         """``update``: None, a tensor [T, H] of the compute dtype, or ``Partials``."""
         count, hidden = out.shape
         self.launches += 1
+        if isinstance(update, Partials) and update.splits == 0:
+            update = self.resolve(update, None)
         if isinstance(update, Partials):
             self._add_rmsnorm(_ptr(residual), _ptr(update.data), update.splits,
                               update.rows * update.width, _ptr(update.bias), _ptr(gain), _ptr(out),
@@ -224,7 +230,7 @@ class Ops:
         self.scratch_frozen = True
 
     def linear(self, x: Any, weight: Any, bias: Any, out: Any, allow_partials: bool = False,
-               tag: str = "") -> Any:
+               tag: str = "", defer_bias: bool = False) -> Any:
         """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias); out is the compute dtype or float32.
 
         Returns ``out``, or, when ``allow_partials`` and the product was cut along K, a
@@ -252,6 +258,9 @@ class Ops:
         if self._tensor_gemm is not None and self._tensor_gemm.run(x, weight, bias, out):
             return out
         if self.gemm_mode == "cublas" and self.code == BF16:
+            if defer_bias and bias is not None and out.dtype == self.dtype:
+                self._cublas_linear(x, weight, None, out)
+                return Partials(out, 0, m, n, bias)   # the consumer adds the bias in float32
             self._cublas_linear(x, weight, bias, out)
             return out
         self.launches += 1
@@ -263,6 +272,10 @@ class Ops:
         """A plain tensor for a part that cannot consume ``Partials`` itself."""
         if not isinstance(value, Partials):
             return value
+        if value.splits == 0:
+            if value.bias is not None:
+                value.data.add_(value.bias.to(value.data.dtype))
+            return value.data
         total = value.data[: value.splits * value.rows * value.width].view(value.splits, value.rows, value.width).sum(0)
         if value.bias is not None:
             total = total + value.bias
@@ -322,7 +335,11 @@ class Ops:
         inv_freq = position.inv_freq if position is not None else None
         table = ctx.block_tables[kv.group]
         self.launches += 1
-        if isinstance(qkv, Partials):
+        if isinstance(qkv, Partials) and qkv.splits == 0:
+            tokens = qkv.rows
+            src, splits, stride, bias = qkv.data, 0, 0, qkv.bias
+            target = qkv.data
+        elif isinstance(qkv, Partials):
             tokens = qkv.rows
             src, splits, stride, bias = qkv.data, qkv.splits, qkv.rows * qkv.width, qkv.bias
             target = q_buffer

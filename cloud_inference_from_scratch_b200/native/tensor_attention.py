@@ -15,7 +15,7 @@ import numpy as np
 
 from .build import load_library
 
-BM = 64            # query rows of a prefill tile (must match the kernel)
+BM = 128           # query rows of a prefill tile (must match the kernel)
 SM_COUNT = 148
 MIN_KEYS_PER_SPLIT = 128
 

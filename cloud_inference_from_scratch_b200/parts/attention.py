@@ -93,7 +93,8 @@ class Attention(Mixer):
         tokens = x.shape[0]
         qkv = rt.workspace.get("attention.qkv", tokens, self.qkv_width, rt.dtype)
         # for few tokens the projection may come back as partial sums that the next kernel adds up
-        qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, allow_partials=True, tag="attention.qkv")
+        qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, allow_partials=True, tag="attention.qkv",
+                            defer_bias=True)
         kv = binding.kv
         q = rt.ops.rope_kv_write(
             qkv, ctx, kv, self.position, self.num_heads, self.num_kv_heads, self.head_dim,
