@@ -238,3 +238,73 @@ extern "C" int cie_gemm_stream(const void* x, const void* w, const float* bias, 
   }
   CIE_FAIL("gemm_stream: block_rows must be 32 or 64, got %d", block_rows);
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see gemm_stream_noalloc.h for who needs it and the rules).
+#include "gemm_stream_noalloc.h"
+
+namespace cie {
+
+// Scratch for the partial sums of cie_gemm_stream_noalloc.  In host code this name is only a
+// stand-in for the device symbol, never a device address: the host asks the runtime for the
+// address once per device (scratch_address) and hands that to the kernels.
+static __device__ __align__(256) float noalloc_scratch[CIE_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+
+// out[m][n] = bf16(sum over splits of partial[s][m][n] + bias[n]); the splits in ascending order.
+__global__ void noalloc_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
+                                      bf16* __restrict__ out, int m, int n, int splits) {
+  const size_t total = (size_t)m * n;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    float v = partial[i];
+    for (int s = 1; s < splits; ++s) v += partial[(size_t)s * total + i];
+    if (bias) v += bias[i % n];
+    out[i] = __float2bfloat16_rn(v);
+  }
+}
+
+// Device address of the scratch array on the current device, looked up on first use per device.
+static int scratch_address(float** address) {
+  static float* known[kMaxDevices] = {};
+  int device = -1;
+  cudaError_t status = cudaGetDevice(&device);
+  if (status != cudaSuccess) CIE_FAIL("gemm_stream_noalloc: cudaGetDevice: %s", cudaGetErrorString(status));
+  if (device < 0 || device >= kMaxDevices) CIE_FAIL("gemm_stream_noalloc: device index %d is outside 0..%d", device, kMaxDevices - 1);
+  if (!known[device]) {
+    float* found = nullptr;
+    status = cudaGetSymbolAddress(reinterpret_cast<void**>(&found), noalloc_scratch);
+    if (status != cudaSuccess || !found)
+      CIE_FAIL("gemm_stream_noalloc: cudaGetSymbolAddress on device %d: %s", device, cudaGetErrorString(status));
+    known[device] = found;
+  }
+  *address = known[device];
+  return 0;
+}
+
+}  // namespace cie
+
+extern "C" int cie_gemm_stream_noalloc(const void* x, const void* w, const float* bias, void* out, int m,
+                                       int n, int k, int splits, void* stream) {
+  if (m <= 0 || n <= 0) return 0;
+  if (m > 16) CIE_FAIL("gemm_stream_noalloc: takes at most 16 rows, got %d", m);
+  if (k < 8 || k % 8) CIE_FAIL("gemm_stream_noalloc: K must be a multiple of 8, got %d", k);
+  if (splits < 1 || splits > 8) CIE_FAIL("gemm_stream_noalloc: splits must be 1..8, got %d", splits);
+  if ((long long)splits * m * n > (long long)CIE_NOALLOC_SCRATCH_FLOATS)
+    CIE_FAIL("gemm_stream_noalloc: %d splits x %d rows x %d columns = %lld partial sums exceed the built-in scratch of %d",
+             splits, m, n, (long long)splits * m * n, CIE_NOALLOC_SCRATCH_FLOATS);
+  if (!x || !w || !out) CIE_FAIL("gemm_stream_noalloc: null operand");
+  float* scratch = nullptr;
+  if (cie::scratch_address(&scratch) != 0) return 1;
+  // partial sums of the existing kernel go to the built-in scratch ...
+  if (cie_gemm_stream(x, w, nullptr, scratch, m, n, k, splits, kOutPartial, 32, stream) != 0) return 1;
+  // ... and are added up, with the bias, by one more kernel (launched without programmatic
+  // overlap, so it starts after the product has finished)
+  const size_t total = (size_t)m * n;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 1024) blocks = 1024;
+  noalloc_reduce_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(scratch, bias, (bf16*)out, m, n, splits);
+  CIE_CHECK_LAUNCH("gemm_stream_noalloc");
+  return 0;
+}
