@@ -177,7 +177,12 @@ class InferenceEngine:
         if not self.ready or self.scheduler is None:
             raise RuntimeError("engine not started")
         gen_config = gen_config or self.new_generation_config()
-        request = self.scheduler.submit(list(prompt_token_ids), gen_config, label=label)
+        prompt_token_ids = [int(t) for t in prompt_token_ids]
+        if self.core is not None and prompt_token_ids:
+            vocab = self.core.spec.vocab_size
+            if min(prompt_token_ids) < 0 or max(prompt_token_ids) >= vocab:
+                raise ValueError(f"prompt holds a token id outside the vocabulary of {vocab}")
+        request = self.scheduler.submit(prompt_token_ids, gen_config, label=label)
         return RequestHandle(request, self)
 
     def run_until_idle(self) -> None:

@@ -157,15 +157,17 @@ def forward(config, weights, token_ids, schedule=None, window=0):
     """Logits [T, vocab] of one whole sequence starting at position 0 (model.py:194-228).
 
     ``schedule``: list of (layer index, index of the earlier run whose k/v to read, or None).
+    ``window``: one window for every run, or a list with one window per run (0: all keys).
     """
     positions = list(range(len(token_ids)))
     h = embedding(weights["model.embed_tokens.weight"], token_ids)
     if schedule is None:
         schedule = [(index, None) for index in range(config["num_hidden_layers"])]
     produced = []
-    for layer, reads in schedule:
+    windows = list(window) if isinstance(window, (list, tuple)) else [window] * len(schedule)
+    for (layer, reads), run_window in zip(schedule, windows):
         shared = produced[reads] if reads is not None else None
-        h, kv = decoder_layer(h, weights, layer, config, positions, window, shared)
+        h, kv = decoder_layer(h, weights, layer, config, positions, run_window, shared)
         produced.append(kv)
     h = rms_norm(h, weights["model.norm.weight"], config["rms_norm_eps"])
     return lm_head(h, weights, config)
