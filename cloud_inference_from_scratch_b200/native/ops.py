@@ -118,8 +118,7 @@ class Ops:
             "cie_attention_generic",
             [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, f, i, i, v, v],
         )
-        sm = _Lib(load_library("sampling.cu"))
-        self._sample = sm.function("cie_sample", [v, i, i, v, v, v, v])
+        self._sample = None   # sampling.cu is built when something is first sampled
         self._tensor_gemm = None
         self._tensor_attention: dict[int, Any] = {}
         self._gemm_stream = None
@@ -383,5 +382,8 @@ class Ops:
     def sample(self, logits: Any, temperature: Any, keys: Any, out: Any) -> None:
         """logits float32 [R, V]; temperature float32 [R] or None (greedy); keys int64 [R]."""
         rows, vocab = logits.shape
+        if self._sample is None:
+            v, i = c_void_p, c_int
+            self._sample = _Lib(load_library("sampling.cu")).function("cie_sample", [v, i, i, v, v, v, v])
         self.launches += 1
         self._sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(keys), _ptr(out), self.stream)
