@@ -17,6 +17,7 @@
 #include "common.cuh"
 
 #include <cooperative_groups.h>
+#include <cuda.h>
 
 #include <cfloat>
 
@@ -132,9 +133,20 @@ __device__ __forceinline__ long long kv_offset(const Pools& pools, const int* ro
 
 // One 16-row block against NB*16 keys held in shared memory (rows of ROW elements).
 // q_frag: A fragments of the 16 query rows.  s: NB*2 score tiles of 16 x 8.
-template <int NB>
+// Address of element (row, col) of a key/value tile in shared memory, col a multiple of 8.
+// SW == false: rows of ROW elements (padded).  SW == true: the layout a TMA tensor copy with
+// 128-byte swizzle leaves: 16-row sub-tiles of 64 columns, 2 KB each, the 16-byte piece c of
+// row r stored at piece position c ^ (r & 7).
+template <bool SW>
+__device__ __forceinline__ const bf16* tile_ptr(const bf16* base, int row, int col) {
+  if constexpr (!SW) return base + row * ROW + col;
+  else return base + (col >> 6) * 1024 + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
+}
+
+template <int NB, bool SW = false>
 __device__ __forceinline__ void scores(const uint32_t (&q_frag)[KSTEPS][4], const bf16* k_tile,
                                        float (&s)[NB * 2][4], int lane) {
+  static_assert(!SW || NB == 1, "swizzled tiles hold 16 keys");
   // two accumulator sets (even and odd k-steps) halve the chain of dependent tensor-core
   // instructions; they are added at the end
   float s2[NB * 2][4];
@@ -149,7 +161,7 @@ __device__ __forceinline__ void scores(const uint32_t (&q_frag)[KSTEPS][4], cons
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
       uint32_t b[4];
-      ldsm_x4(b, k_tile + (nb * 16 + (mi >> 1) * 8 + r) * ROW + kk * 16 + (mi & 1) * 8);
+      ldsm_x4(b, tile_ptr<SW>(k_tile, nb * 16 + (mi >> 1) * 8 + r, kk * 16 + (mi & 1) * 8));
       if (kk & 1) {
         mma_bf16(s2[2 * nb], q_frag[kk], b[0], b[1]);
         mma_bf16(s2[2 * nb + 1], q_frag[kk], b[2], b[3]);
@@ -166,7 +178,7 @@ __device__ __forceinline__ void scores(const uint32_t (&q_frag)[KSTEPS][4], cons
 }
 
 // o += P V for NB*16 keys; p: probabilities in the score-tile layout.
-template <int NB>
+template <int NB, bool SW = false>
 __device__ __forceinline__ void accumulate(const float (&p)[NB * 2][4], const bf16* v_tile,
                                            float (&o)[NTILES_D][4], int lane) {
   const int mi = lane >> 3, r = lane & 7;
@@ -180,7 +192,7 @@ __device__ __forceinline__ void accumulate(const float (&p)[NB * 2][4], const bf
 #pragma unroll
     for (int db = 0; db < KSTEPS; ++db) {
       uint32_t b[4];
-      ldsm_x4_trans(b, v_tile + (kb * 16 + (mi & 1) * 8 + r) * ROW + db * 16 + (mi >> 1) * 8);
+      ldsm_x4_trans(b, tile_ptr<SW>(v_tile, kb * 16 + (mi & 1) * 8 + r, db * 16 + (mi >> 1) * 8));
       mma_bf16(o[2 * db], a, b[0], b[1]);
       mma_bf16(o[2 * db + 1], a, b[2], b[3]);
     }
@@ -404,13 +416,10 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
 
 // ------------------------------------------------------------------------------------ decode
 #ifndef DECODE_WARPS_N
-#define DECODE_WARPS_N 8
+#define DECODE_WARPS_N 12
 #endif
 constexpr int DECODE_WARPS = DECODE_WARPS_N;
-#ifndef DECODE_KEYS
-#define DECODE_KEYS 16
-#endif
-constexpr int DN = DECODE_KEYS;   // keys per warp and iteration
+constexpr int DN = 16;   // keys per warp and iteration
 
 struct DecodeArgs {
   const bf16* q;          // row b of q_stride elements: the request's single query token
@@ -430,62 +439,86 @@ struct DecodeArgs {
 };
 
 constexpr int DECODE_PAGE_SLOTS = 1024;   // block-table entries of a CTA's key range kept in shared memory
-#ifndef DECODE_STAGES_N
-#define DECODE_STAGES_N (HEAD_DIM <= 128 ? 2 : 1)
-#endif
-constexpr int DECODE_STAGES = DECODE_STAGES_N;   // per warp; all but one in flight while one is multiplied
 
-// One DN-key tile of K and V for one warp with 16-byte cp.async: the 32 lanes walk the tile 16
-// rows at a time, two lanes per key row, each pair fetching whole 32-byte sectors.  The page of a
-// key comes from the CTA's copy of its block-table range (or from global memory if the range did
-// not fit).  Rows past `valid_hi` are filled with zeros.
+// Stages per warp: all but one are in flight while one is multiplied.
+//  cp.async variant: padded rows (ROW elements), two stages (one for head sizes over 128).
+//  TMA variant: unpadded swizzled tiles, two stages.
+constexpr int DECODE_STAGES_LSU = D <= 128 ? 2 : 1;
+#ifndef DECODE_STAGES_TMA_N
+#define DECODE_STAGES_TMA_N (HEAD_DIM <= 128 ? 2 : 1)
+#endif
+constexpr int DECODE_STAGES_TMA = DECODE_STAGES_TMA_N;
+constexpr int DECODE_STAGE_LSU = 2 * DN * ROW;   // K and V of one stage, elements
+constexpr int DECODE_STAGE_TMA = 2 * DN * D;
+constexpr size_t DECODE_Q_BYTES = ((size_t)16 * ROW * sizeof(bf16) + 1023) / 1024 * 1024;
+constexpr size_t DECODE_MERGE_BYTES = (size_t)DECODE_WARPS * 16 * (D + 2) * sizeof(float);
+constexpr size_t DECODE_PART_BYTES = (size_t)16 * (D + 2) * sizeof(float);
+template <bool kTma>
+constexpr size_t decode_work_bytes() {
+  const size_t kv = (size_t)DECODE_WARPS * (kTma ? DECODE_STAGES_TMA * DECODE_STAGE_TMA : DECODE_STAGES_LSU * DECODE_STAGE_LSU) * sizeof(bf16);
+  const size_t need = kv > DECODE_MERGE_BYTES ? kv : DECODE_MERGE_BYTES;
+  return (need + 1023) / 1024 * 1024;
+}
+template <bool kTma>
+constexpr size_t decode_smem() { return 1024 + DECODE_Q_BYTES + decode_work_bytes<kTma>() + DECODE_PART_BYTES; }
+
+// One 16-key tile of K and V for one warp with 16-byte cp.async, two lanes per key row.  The page
+// of a key comes from the CTA's copy of its block-table range (or from global memory if the range
+// did not fit).  Rows past `valid_hi` are filled with zeros.
 __device__ __forceinline__ void load_kv_tile_warp(const DecodeArgs& a, const int* row, const int* pages_s,
                                                   int first_index, int cached, int kvh, int k0,
                                                   int valid_hi, bf16* k_dst, bf16* v_dst, int lane) {
   const int half = lane & 1;
+  const int r = lane >> 1;
+  const int key = k0 + r;
+  long long off = -1;
+  if (key < valid_hi) {
+    int index, within;
+    if (a.page_shift >= 0) { index = key >> a.page_shift; within = key & (a.pools.page_size - 1); }
+    else { index = key / a.pools.page_size; within = key - index * a.pools.page_size; }
+    int page;
+    if (index - first_index < cached) page = pages_s[index - first_index];
+    else page = index < a.pools.table_width ? row[index] : -1;
+    if (page < 0 || page >= a.pools.num_pages) atomicOr(a.err, kErrBadPage);
+    else off = (((long long)page * a.pools.kv_heads + kvh) * a.pools.page_size + within) * D;
+  }
+  // one source pointer and one destination address per row; the pieces are constant offsets
+  const int bytes = off >= 0 ? 16 : 0;
+  const bf16* ks = a.pools.k + (off >= 0 ? off : 0) + half * 8;
+  const bf16* vs = a.pools.v + (off >= 0 ? off : 0) + half * 8;
+  const uint32_t kd = smem_u32(k_dst + r * ROW + half * 8), vd = smem_u32(v_dst + r * ROW + half * 8);
 #pragma unroll
-  for (int block = 0; block < DN / 16; ++block) {
-    const int r = block * 16 + (lane >> 1);
-    const int key = k0 + r;
-    long long off = -1;
-    if (key < valid_hi) {
-      int index, within;
-      if (a.page_shift >= 0) { index = key >> a.page_shift; within = key & (a.pools.page_size - 1); }
-      else { index = key / a.pools.page_size; within = key - index * a.pools.page_size; }
-      int page;
-      if (index - first_index < cached) page = pages_s[index - first_index];
-      else page = index < a.pools.table_width ? row[index] : -1;
-      if (page < 0 || page >= a.pools.num_pages) atomicOr(a.err, kErrBadPage);
-      else off = (((long long)page * a.pools.kv_heads + kvh) * a.pools.page_size + within) * D;
-    }
-    // one source pointer and one destination address per row; the pieces are constant offsets
-    const int bytes = off >= 0 ? 16 : 0;
-    const bf16* ks = a.pools.k + (off >= 0 ? off : 0) + half * 8;
-    const bf16* vs = a.pools.v + (off >= 0 ? off : 0) + half * 8;
-    const uint32_t kd = smem_u32(k_dst + r * ROW + half * 8), vd = smem_u32(v_dst + r * ROW + half * 8);
-#pragma unroll
-    for (int c = 0; c < CHUNKS / 2; ++c) {
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(kd + c * 32), "l"(ks + c * 16), "r"(bytes));
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vd + c * 32), "l"(vs + c * 16), "r"(bytes));
-    }
+  for (int c = 0; c < CHUNKS / 2; ++c) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(kd + c * 32), "l"(ks + c * 16), "r"(bytes));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vd + c * 32), "l"(vs + c * 16), "r"(bytes));
   }
 }
 
-constexpr int DECODE_STAGE = 2 * DN * ROW;                       // K and V of one stage, elements
-constexpr int DECODE_WARP_ELEMS = DECODE_STAGES * DECODE_STAGE;
-constexpr size_t DECODE_KV_BYTES = (size_t)DECODE_WARPS * DECODE_WARP_ELEMS * sizeof(bf16);
-constexpr size_t DECODE_MERGE_BYTES = (size_t)DECODE_WARPS * 16 * (D + 2) * sizeof(float);
-constexpr size_t DECODE_Q_BYTES = (size_t)16 * ROW * sizeof(bf16);
-constexpr size_t DECODE_PART_BYTES = (size_t)16 * (D + 2) * sizeof(float);
-constexpr size_t DECODE_WORK_BYTES = DECODE_KV_BYTES > DECODE_MERGE_BYTES ? DECODE_KV_BYTES : DECODE_MERGE_BYTES;
-constexpr size_t DECODE_SMEM = DECODE_Q_BYTES + DECODE_WORK_BYTES + DECODE_PART_BYTES;
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
 
-__global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+// kTma == false: keys and values come through the load/store unit (cp.async), any page size and
+// window.  kTma == true: each 16-key tile is fetched by one lane with D/64 tensor copies per
+// matrix (boxes of 16 rows x 64 columns, 128-byte swizzle) that complete on the stage's mbarrier;
+// it needs pages of a multiple of 16 tokens, a head size that is a multiple of 64 and no window,
+// so that a tile never straddles two pages.
+template <bool kTma>
+__global__ void __launch_bounds__(DECODE_WARPS * 32)
+decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+              const DecodeArgs a) {
+  constexpr int STAGES = kTma ? DECODE_STAGES_TMA : DECODE_STAGES_LSU;
+  constexpr int STAGE = kTma ? DECODE_STAGE_TMA : DECODE_STAGE_LSU;
+  extern __shared__ __align__(16) unsigned char smem_unaligned[];
+  unsigned char* smem_raw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                          // [16][ROW]
-  bf16* kv_s = reinterpret_cast<bf16*>(smem_raw + DECODE_Q_BYTES);        // per warp: 2 stages of K,V
+  bf16* kv_s = reinterpret_cast<bf16*>(smem_raw + DECODE_Q_BYTES);        // per warp: STAGES of K,V
   float* merge_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES);   // aliased after the loop
-  float* part_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES + DECODE_WORK_BYTES);
+  float* part_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES + decode_work_bytes<kTma>());
+  __shared__ int pages_s[DECODE_PAGE_SLOTS];
+  __shared__ __align__(8) uint64_t bars[DECODE_WARPS][kTma ? DECODE_STAGES_TMA : 1];
   pdl_wait();
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -506,9 +539,12 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
     cp_async16(q_s + r * ROW + c * 8, src, ok);
   }
   cp_async_commit();
+  if constexpr (kTma) {
+    if (tid < DECODE_WARPS * STAGES) mbar_init(&bars[tid / STAGES][tid % STAGES], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   // this CTA's stretch of the block table goes to shared memory once, so that no tile load has
   // to wait for a table entry from global memory first
-  __shared__ int pages_s[DECODE_PAGE_SLOTS];
   const int first_index = begin / a.pools.page_size;
   int cached = begin < end ? (end - 1) / a.pools.page_size - first_index + 1 : 0;
   if (cached > DECODE_PAGE_SLOTS) cached = DECODE_PAGE_SLOTS;
@@ -516,20 +552,42 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
     pages_s[i] = first_index + i < a.pools.table_width ? table_row[first_index + i] : -1;
   __syncthreads();
 
-  bf16* mine = kv_s + warp * DECODE_WARP_ELEMS;
+  bf16* mine = kv_s + warp * STAGES * STAGE;
   const int tiles = begin < end ? (end - begin + DN - 1) / DN : 0;
-  // warp w takes tiles w, w + 4, ...
+  // warp w takes tiles w, w + DECODE_WARPS, ...
   auto issue = [&](int tile, int slot) {
-    if (tile < tiles) {
-      bf16* dst = mine + slot * DECODE_STAGE;
-      load_kv_tile_warp(a, table_row, pages_s, first_index, cached, kvh, begin + tile * DN, end, dst,
-                        dst + DN * ROW, lane);
+    bf16* dst = mine + slot * STAGE;
+    if constexpr (kTma) {
+      if (tile < tiles && lane == 0) {
+        const int key = begin + tile * DN;   // a multiple of 16: the tile lies inside one page
+        const int index = key >> a.page_shift, within = key & (a.pools.page_size - 1);
+        int page;
+        if (index - first_index < cached) page = pages_s[index - first_index];
+        else page = index < a.pools.table_width ? table_row[index] : -1;
+        if (page < 0 || page >= a.pools.num_pages) {
+          atomicOr(a.err, kErrBadPage);
+          page = 0;   // the copies must still happen, or the barrier would never complete
+        }
+        const int row0 = (page * a.pools.kv_heads + kvh) * a.pools.page_size + within;
+        uint64_t* bar = &bars[warp][slot];
+        mbar_expect_tx(bar, (uint32_t)(2 * DN * D * sizeof(bf16)));
+#pragma unroll
+        for (int sub = 0; sub < D / 64; ++sub) {
+          tma_load_2d(dst + sub * 1024, &k_map, bar, sub * 64, row0);
+          tma_load_2d(dst + DN * D + sub * 1024, &v_map, bar, sub * 64, row0);
+        }
+      }
+    } else {
+      if (tile < tiles)
+        load_kv_tile_warp(a, table_row, pages_s, first_index, cached, kvh, begin + tile * DN, end, dst,
+                          dst + DN * ROW, lane);
+      cp_async_commit();
     }
-    cp_async_commit();
   };
 #pragma unroll
-  for (int p = 0; p < DECODE_STAGES - 1; ++p) issue(warp + p * DECODE_WARPS, p);
-  cp_async_wait<DECODE_STAGES - 1>();   // the queries (first group) have landed
+  for (int p = 0; p < STAGES - 1; ++p) issue(warp + p * DECODE_WARPS, p);
+  if constexpr (kTma) cp_async_wait<0>();
+  else cp_async_wait<STAGES - 1>();   // the queries (first group) have landed
   __syncthreads();
   uint32_t q_frag[KSTEPS][4];
 #pragma unroll
@@ -543,15 +601,22 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
   const int t4 = lane & 3;
 
   int stage = 0;
-  for (int it = warp; it < tiles; it += DECODE_WARPS) {
-    issue(it + (DECODE_STAGES - 1) * DECODE_WARPS, (stage + DECODE_STAGES - 1) % DECODE_STAGES);
-    cp_async_wait<DECODE_STAGES - 1>();
-    __syncwarp();
-    const bf16* k_tile = mine + stage * DECODE_STAGE;
-    const bf16* v_tile = k_tile + DN * ROW;
+  uint32_t phases = 0;   // TMA variant: bit s is the parity to wait for on stage s
+  bool alive = true;
+  for (int it = warp; it < tiles && alive; it += DECODE_WARPS) {
+    issue(it + (STAGES - 1) * DECODE_WARPS, (stage + STAGES - 1) % STAGES);
+    if constexpr (kTma) {
+      alive = mbar_wait(&bars[warp][stage], (phases >> stage) & 1u, a.err);
+      phases ^= 1u << stage;
+    } else {
+      cp_async_wait<STAGES - 1>();
+      __syncwarp();
+    }
+    const bf16* k_tile = mine + stage * STAGE;
+    const bf16* v_tile = k_tile + (kTma ? DN * D : DN * ROW);
     const int k0 = begin + it * DN;
     float s[DN / 8][4];
-    scores<DN / 16>(q_frag, k_tile, s, lane);
+    scores<DN / 16, kTma>(q_frag, k_tile, s, lane);
     if (k0 + DN <= end) {
 #pragma unroll
       for (int i = 0; i < DN / 8; ++i)
@@ -568,14 +633,14 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
     }
     if (a.group - h0 <= 8) softmax_update<DN / 8, 1>(s, m, l, o);
     else softmax_update<DN / 8, 2>(s, m, l, o);
-    accumulate<DN / 16>(s, v_tile, o, lane);
+    accumulate<DN / 16, kTma>(s, v_tile, o, lane);
     __syncwarp();
-    stage = (stage + 1) % DECODE_STAGES;
+    stage = (stage + 1) % STAGES;
   }
-  cp_async_wait<0>();
+  if constexpr (!kTma) cp_async_wait<0>();
   __syncthreads();   // every warp is done with its K/V buffers: reuse them for the merge
 
-  // ---- merge the four warps: per warp [16][D + 2] floats (o, then max, then sum)
+  // ---- merge the warps: per warp [16][D + 2] floats (o, then max, then sum)
   const int g = lane >> 2;
   float* my_merge = merge_s + warp * 16 * (D + 2);
 #pragma unroll
@@ -662,6 +727,44 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_kernel(const DecodeA
   cluster.sync();   // nobody leaves while a peer may still read its share
 }
 
+// ------------------------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+// Tensor map of one layer's key (or value) pool seen as a matrix [pages * kv_heads * page_size, D],
+// read in boxes of 16 rows x 64 columns with 128-byte swizzle.  Maps are kept by pool address.
+static bool pool_map(const void* pool, long long rows, CUtensorMap* out) {
+  struct Entry { const void* pool; long long rows; CUtensorMap map; };
+  static Entry cache[512];
+  static int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].pool == pool && cache[i].rows == rows) { *out = cache[i].map; return true; }
+  static EncodeTiled encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess ||
+        status != cudaDriverEntryPointSuccess)
+      return false;
+    encode = reinterpret_cast<EncodeTiled>(fn);
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
+  cuuint32_t box[2] = {64, 16};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (used == 512) used = 0;
+  cache[used++] = Entry{pool, rows, map};
+  *out = map;
+  return true;
+}
+
 }  // namespace cie
 
 using namespace cie;
@@ -702,11 +805,48 @@ extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int
 }
 
 // splits: CTAs that share the keys of one request (a thread-block cluster): 1, 2, 4 or 8.
+// use_tma: 1 lets the kernel fetch keys and values with tensor copies where the shapes allow it
+// (pages of a multiple of 16 tokens, head size a multiple of 64, no window); 0 keeps cp.async.
+template <bool kTma>
+static int launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, const DecodeArgs& a,
+                         int requests, cudaStream_t stream) {
+  constexpr size_t smem = decode_smem<kTma>();
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t status = cudaFuncSetAttribute(decode_kernel<kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (status != cudaSuccess) CIE_FAIL("attention_decode: shared memory %zu: %s", smem, cudaGetErrorString(status));
+    configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(a.splits, a.pools.kv_heads * a.head_chunks, requests);
+  config.blockDim = dim3(DECODE_WARPS * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  attributes[count].id = cudaLaunchAttributeClusterDimension;
+  attributes[count].val.clusterDim.x = a.splits;
+  attributes[count].val.clusterDim.y = 1;
+  attributes[count].val.clusterDim.z = 1;
+  ++count;
+  if (pdl_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  cudaError_t status = cudaLaunchKernelEx(&config, decode_kernel<kTma>, k_map, v_map, a);
+  if (status != cudaSuccess) CIE_FAIL("attention_decode: launch failed: %s", cudaGetErrorString(status));
+  return 0;
+}
+
 extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int out_stride,
                                     const void* k_pool, const void* v_pool, const int* table,
                                     int table_width, int num_pages, const int* context_lens,
                                     int requests, int q_heads, int kv_heads, int page_size,
-                                    int splits, float scale, int window, int* err, void* stream) {
+                                    int splits, float scale, int window, int use_tma, int* err,
+                                    void* stream) {
   if (requests <= 0) return 0;
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_decode: %d query heads over %d kv heads", q_heads, kv_heads);
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) CIE_FAIL("attention_decode: splits must be 1, 2, 4 or 8, got %d", splits);
@@ -719,32 +859,14 @@ extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int 
   a.page_shift = -1;
   for (int shift = 0; shift < 31; ++shift)
     if ((1 << shift) == page_size) a.page_shift = shift;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t status = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
-    if (status != cudaSuccess) CIE_FAIL("attention_decode: shared memory %zu: %s", (size_t)DECODE_SMEM, cudaGetErrorString(status));
-    configured = true;
+  CUtensorMap k_map = {}, v_map = {};
+  const bool tma = use_tma && D % 64 == 0 && window <= 0 && a.page_shift >= 4 &&
+                   ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) == 0;
+  if (tma) {
+    const long long rows = (long long)num_pages * kv_heads * page_size;
+    if (!pool_map(k_pool, rows, &k_map) || !pool_map(v_pool, rows, &v_map))
+      CIE_FAIL("attention_decode: cuTensorMapEncodeTiled failed");
+    return launch_decode<true>(k_map, v_map, a, requests, (cudaStream_t)stream);
   }
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(splits, kv_heads * a.head_chunks, requests);
-  config.blockDim = dim3(DECODE_WARPS * 32);
-  config.dynamicSmemBytes = DECODE_SMEM;
-  config.stream = (cudaStream_t)stream;
-  cudaLaunchAttribute attributes[2];
-  int count = 0;
-  attributes[count].id = cudaLaunchAttributeClusterDimension;
-  attributes[count].val.clusterDim.x = splits;
-  attributes[count].val.clusterDim.y = 1;
-  attributes[count].val.clusterDim.z = 1;
-  ++count;
-  if (pdl_enabled()) {
-    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attributes[count].val.programmaticStreamSerializationAllowed = 1;
-    ++count;
-  }
-  config.attrs = attributes;
-  config.numAttrs = count;
-  cudaError_t status = cudaLaunchKernelEx(&config, decode_kernel, a);
-  if (status != cudaSuccess) CIE_FAIL("attention_decode: launch failed: %s", cudaGetErrorString(status));
-  return 0;
+  return launch_decode<false>(k_map, v_map, a, requests, (cudaStream_t)stream);
 }

@@ -56,8 +56,11 @@ class TensorAttention:
         )
         self._decode = lib.function(
             "cie_attention_decode",
-            [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, f, i, v, v],
+            [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, f, i, i, v, v],
         )
+        import os
+
+        self.use_tma = 0 if os.environ.get("CIE_DECODE_TMA", "1") == "0" else 1
 
     @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int) -> int:
@@ -90,7 +93,7 @@ class TensorAttention:
             self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                          kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
                          ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, kv.page_size,
-                         splits, scale, window, ops.error_word.data_ptr(), ops.stream)
+                         splits, scale, window, self.use_tma, ops.error_word.data_ptr(), ops.stream)
             return True
         if plan is None:
             tiles = plan_tiles(ctx.host.query_lens, group)
