@@ -299,8 +299,8 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [BM][ROW]
   bf16* k_s = q_s + BM * ROW;                     // [2][BN][ROW]
   bf16* v_s = k_s + 2 * BN * ROW;                 // [2][BN][ROW]
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;
   const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * a.hpt;
@@ -519,8 +519,8 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
   float* part_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES + decode_work_bytes<kTma>());
   __shared__ int pages_s[DECODE_PAGE_SLOTS];
   __shared__ __align__(8) uint64_t bars[DECODE_WARPS][kTma ? DECODE_STAGES_TMA : 1];
-  pdl_wait();
   pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * 16;

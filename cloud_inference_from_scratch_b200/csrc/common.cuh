@@ -69,7 +69,9 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // its own wait, every earlier one) has completed and its writes are visible.  Before the wait a
 // kernel may only do what does not depend on earlier kernels and writes nothing they read:
 // set-up and prefetching weights.  `pdl_trigger` lets the next kernel in the stream start its own
-// set-up.  Without the launch attribute both are no-ops.
+// set-up; kernels trigger BEFORE they wait, so several kernels of a chain can be resident at once,
+// each having asked for its weights, while the first of them is still running.  Without the
+// launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
