@@ -25,11 +25,31 @@ from .step import MetadataBuffer, StepEntry
 
 
 class _DecodeGraph:
-    def __init__(self, bucket: int, meta: MetadataBuffer, graph: Any, result_dev: Any) -> None:
+    """One captured decode step for one batch size: its metadata buffers, its result buffers."""
+
+    def __init__(self, bucket: int, meta: MetadataBuffer, graph: Any, result_dev: Any, ctx: Any,
+                 torch: Any) -> None:
         self.bucket = bucket
         self.meta = meta
         self.graph = graph
         self.result_dev = result_dev
+        self.result_host = torch.zeros(1 + bucket, dtype=torch.int32, pin_memory=True)
+        self.token_ids = ctx.token_ids          # device view: where the step reads its token ids
+        self.event = torch.cuda.Event()
+        self.feed_index = torch.zeros(bucket, dtype=torch.int64, device=result_dev.device)
+        self.feed_real = -1
+
+
+class _InFlight:
+    """A decode step that has been launched and whose tokens have not been read yet."""
+
+    def __init__(self, graph: _DecodeGraph, request_ids: list[str], spans: dict, real: int,
+                 committed: bool) -> None:
+        self.graph = graph
+        self.request_ids = request_ids
+        self.spans = spans
+        self.real = real
+        self.committed = committed
 
 
 class EngineRunner:
@@ -48,7 +68,12 @@ class EngineRunner:
         has_state = any(need.state is not None for need in core.model.cache_needs())
         self.use_graphs = bool(config.cuda_graph_decode) and not has_state
         self.table_width = -(-config.max_model_len // core.page_size)
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
+        self._parity = 0
+        self._ahead: _InFlight | None = None   # the next decode step, launched before it was asked for
+        self.pipeline_decode = True
+        self.steps_launched_ahead = 0
+        self.steps_ahead_adopted = 0
         self.forward_invocations = 0
         self.max_forward_request_count = 0
         self.cuda_graph_captures = 0
@@ -86,14 +111,18 @@ class EngineRunner:
         phase = "decode" if decode_only else "mixed"
         with nvtx_range(f"ragged.forward.{phase}.requests_{len(items)}.tokens_{plan.token_count}"):
             if decode_only and self.use_graphs and len(items) <= self.max_rows:
-                tokens = self._graphed_decode(entries, sampled)
+                tokens = self._pipelined_decode(items, entries)
             else:
+                self._ahead = None   # a step launched ahead is dropped: it committed nothing
                 tokens = self._eager(entries, sampled)
         return {item.request.request_id: int(tokens[i]) for i, item in enumerate(sampled)}
 
     # ------------------------------------------------------------------ sampling parameters
     @staticmethod
-    def _sampling_arrays(sampled: list[Any], rows: int) -> dict[str, np.ndarray]:
+    def _sampling_arrays(sampled: list[Any], rows: int, ahead: int = 0) -> dict[str, np.ndarray]:
+        """Temperature and draw key per sampled row; ``ahead`` = 1 for the step after the current
+        one (its output index is one further).  Rows beyond the real ones repeat the last real row,
+        so that a padded row samples what the row it repeats samples."""
         temperature = np.zeros(rows, dtype=np.float32)
         keys = np.zeros(rows, dtype=np.int64)
         for index, item in enumerate(sampled):
@@ -101,8 +130,11 @@ class EngineRunner:
             temperature[index] = request.config.temperature
             if request.config.temperature > 0:
                 keys[index] = as_signed(
-                    draw_key(request.config.seed, request.sequence_number, request.generated_count)
+                    draw_key(request.config.seed, request.sequence_number, request.generated_count + ahead)
                 )
+        if sampled and rows > len(sampled):
+            temperature[len(sampled):] = temperature[len(sampled) - 1]
+            keys[len(sampled):] = keys[len(sampled) - 1]
         return {"temperature": temperature.view(np.int32), "keys": keys.view(np.int32)}
 
     def _launch_sampling(self, logits: Any, ctx: Any, result_dev: Any, rows: int) -> None:
@@ -165,7 +197,12 @@ class EngineRunner:
         host.logit_rows = np.arange(bucket, dtype=np.int32)
         host.tables = [grow(table) for table in host.tables]
 
-    def _graphed_decode(self, entries: list[StepEntry], sampled: list[Any]) -> np.ndarray:
+    def _launch_decode(self, entries: list[StepEntry], sampled: list[Any], ahead: int,
+                       feed: _DecodeGraph | None) -> _InFlight:
+        """Prepares and launches one decode step from its CUDA graph (captured on first use).
+
+        ``feed``: take the token ids from the tokens the step in ``feed`` is sampling, on the
+        device, instead of from ``entries`` (whose ids are placeholders then)."""
         torch = self.torch
         step = self.step
         real = len(entries)
@@ -173,11 +210,14 @@ class EngineRunner:
         with nvtx_range("ragged.kv.ensure_capacity"):
             host, _, spans = step.prepare(entries, table_width=self.table_width)
         self._pad(host, bucket)
-        host.extras["sampling"] = self._sampling_arrays(sampled, bucket)
+        host.extras["sampling"] = self._sampling_arrays(sampled, bucket, ahead)
         for key, mixer in step.planners.items():
             host.extras[key] = mixer.plan(host, self.core.cache)
-        cached = self._graphs.get(bucket)
+        self._parity ^= 1
+        cached = self._graphs.get((bucket, self._parity))
         if cached is None:
+            if feed is not None:
+                raise RuntimeError("a decode graph is captured by a step that has its token ids")
             meta = MetadataBuffer(self.core.runtime.device, words=1 << 12)
             result_dev = torch.zeros(1 + bucket, dtype=torch.int32, device=self.core.runtime.device)
             ctx = step.upload(host, meta)
@@ -198,15 +238,78 @@ class EngineRunner:
                 logits = self.core.model.forward(ctx)
                 self._launch_sampling(logits, ctx, result_dev, bucket)
             self.launches_per_graph[bucket] = self.ops.launches - launches_before
-            cached = _DecodeGraph(bucket, meta, graph, result_dev)
-            self._graphs[bucket] = cached
+            cached = _DecodeGraph(bucket, meta, graph, result_dev, ctx, torch)
+            self._graphs[(bucket, self._parity)] = cached
             self.cuda_graph_captures += 1
         else:
             step.upload(host, cached.meta)
+            if feed is not None:
+                if cached.feed_real != real:
+                    index = np.minimum(np.arange(bucket), real - 1).astype(np.int64)
+                    cached.feed_index.copy_(torch.from_numpy(index))
+                    cached.feed_real = real
+                # row i reads the token that row i of the step before it is sampling
+                torch.index_select(feed.result_dev[1:], 0, cached.feed_index, out=cached.token_ids)
         cached.graph.replay()
         self.cuda_graph_replays += 1
-        with nvtx_range("ragged.kv.commit"):
-            self.core.cache.commit_lengths({rid: end for rid, (_, end) in spans.items()})
         step.steps_run += 1
         step.tokens_run += real
-        return self._read_back(cached.result_dev, bucket)[:real]
+        return _InFlight(cached, [entry.request_id for entry in entries], spans, real, committed=False)
+
+    def _commit(self, flight: _InFlight) -> None:
+        if not flight.committed:
+            with nvtx_range("ragged.kv.commit"):
+                self.core.cache.commit_lengths({rid: end for rid, (_, end) in flight.spans.items()})
+            flight.committed = True
+
+    def _launch_ahead(self, items: Any, current: _InFlight) -> _InFlight | None:
+        """Launches the decode step that will most likely be asked for next: the same requests,
+        one position further, their token ids taken on the device from what ``current`` samples.
+        It commits nothing; if the next plan turns out different it is simply dropped (what it
+        wrote lies beyond every committed length and is written again before it is read)."""
+        if not self.pipeline_decode or (current.graph.bucket, self._parity ^ 1) not in self._graphs:
+            return None
+        for item in items:
+            request = item.request
+            if request.generated_count + 1 >= request.config.max_output_tokens:
+                return None    # this request ends with the token being sampled now
+            if item.end_pos + 1 > self.config.max_model_len:
+                return None
+        entries = [StepEntry(item.request.request_id, (0,), want=(0,), start_pos=item.end_pos) for item in items]
+        try:
+            flight = self._launch_decode(entries, list(items), ahead=1, feed=current.graph)
+        except Exception as exc:  # noqa: BLE001 - no pages (or anything else): run the step when asked
+            if not bool(getattr(exc, "is_capacity_error", False)):
+                raise
+            self._parity ^= 1
+            return None
+        self.steps_launched_ahead += 1
+        return flight
+
+    def _pipelined_decode(self, items: Any, entries: list[StepEntry]) -> np.ndarray:
+        ahead, self._ahead = self._ahead, None
+        current = None
+        if ahead is not None:
+            same = ahead.request_ids == [item.request.request_id for item in items] and all(
+                ahead.spans[item.request.request_id][0] == item.start_pos for item in items
+            )
+            if same:
+                current = ahead
+                self.steps_ahead_adopted += 1
+        if current is None:
+            current = self._launch_decode(entries, list(items), ahead=0, feed=None)
+        self._commit(current)
+        graph = current.graph
+        with nvtx_range("ragged.sample.readback"):
+            graph.result_host.copy_(graph.result_dev, non_blocking=True)
+            graph.event.record()
+        # while the device works on the current step, the next one is prepared and queued
+        self._ahead = self._launch_ahead(items, current)
+        graph.event.synchronize()
+        self.d2h_bytes = 4 * (1 + graph.bucket)
+        values = graph.result_host.numpy()
+        if values[0]:
+            self._ahead = None
+            self.ops.error_word = graph.result_dev[0:1]
+            self.ops.check_errors()
+        return values[1:1 + current.real].copy()
