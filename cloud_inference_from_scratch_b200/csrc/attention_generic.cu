@@ -30,8 +30,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   __shared__ float q_s[kWarps][kMaxDim];
   __shared__ float p_s[kWarps][32];
   __shared__ long long off_s[kWarps][32];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * kWarps + warp;
   if (item >= tokens * q_heads) return;

@@ -299,8 +299,8 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [BM][ROW]
   bf16* k_s = q_s + BM * ROW;                     // [2][BN][ROW]
   bf16* v_s = k_s + 2 * BN * ROW;                 // [2][BN][ROW]
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;
   const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * a.hpt;
@@ -519,8 +519,15 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
   float* part_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES + decode_work_bytes<kTma>());
   __shared__ int pages_s[DECODE_PAGE_SLOTS];
   __shared__ __align__(8) uint64_t bars[DECODE_WARPS][kTma ? DECODE_STAGES_TMA : 1];
-  pdl_trigger();
-  pdl_wait();
+  // The TMA variant waits for the kernel before it only after it has asked for its first key
+  // tiles: block tables and context lengths come with the step's metadata, and older keys and
+  // values are not touched by the kernel before this one (it writes the newest token only), so
+  // only a tile that holds the newest key has to wait.  This rests on every kernel triggering its
+  // dependents AFTER its own wait: then at most the one kernel before this one is still running.
+  if constexpr (!kTma) {
+    pdl_wait();
+    pdl_trigger();
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * 16;
@@ -532,13 +539,6 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
   const int begin = first + split * per_split;
   const int end = min(length, begin + per_split);
 
-  for (int idx = tid; idx < 16 * CHUNKS; idx += DECODE_WARPS * 32) {
-    const int r = idx / CHUNKS, c = idx % CHUNKS;
-    const bool ok = h0 + r < a.group;
-    const bf16* src = ok ? a.q + (size_t)request * a.q_stride + (size_t)(kvh * a.group + h0 + r) * D + c * 8 : a.q;
-    cp_async16(q_s + r * ROW + c * 8, src, ok);
-  }
-  cp_async_commit();
   if constexpr (kTma) {
     if (tid < DECODE_WARPS * STAGES) mbar_init(&bars[tid / STAGES][tid % STAGES], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -584,8 +584,31 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
       cp_async_commit();
     }
   };
+  // tiles that can be asked for before the kernels before this one have finished: all but the
+  // one that holds the newest key (position length - 1)
+  int early = 0;   // how many of the first STAGES - 1 tiles of this warp were issued early
+  if constexpr (kTma) {
 #pragma unroll
-  for (int p = 0; p < STAGES - 1; ++p) issue(warp + p * DECODE_WARPS, p);
+    for (int p = 0; p < STAGES - 1; ++p) {
+      const int tile = warp + p * DECODE_WARPS;
+      if (tile < tiles && begin + (tile + 1) * DN <= length - 1) {
+        issue(tile, p);
+        early |= 1 << p;
+      }
+    }
+    pdl_wait();
+    pdl_trigger();
+  }
+  for (int idx = tid; idx < 16 * CHUNKS; idx += DECODE_WARPS * 32) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = h0 + r < a.group;
+    const bf16* src = ok ? a.q + (size_t)request * a.q_stride + (size_t)(kvh * a.group + h0 + r) * D + c * 8 : a.q;
+    cp_async16(q_s + r * ROW + c * 8, src, ok);
+  }
+  cp_async_commit();
+#pragma unroll
+  for (int p = 0; p < STAGES - 1; ++p)
+    if (!(early & (1 << p))) issue(warp + p * DECODE_WARPS, p);
   if constexpr (kTma) cp_async_wait<0>();
   else cp_async_wait<STAGES - 1>();   // the queries (first group) have landed
   __syncthreads();

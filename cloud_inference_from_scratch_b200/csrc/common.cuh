@@ -68,9 +68,10 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // kernel before it in the stream is still running; `pdl_wait` blocks until that kernel (and, through
 // its own wait, every earlier one) has completed and its writes are visible.  Before the wait a
 // kernel may only do what does not depend on earlier kernels and writes nothing they read:
-// set-up and prefetching weights.  `pdl_trigger` lets the next kernel in the stream start its own
-// set-up; kernels trigger BEFORE they wait, so several kernels of a chain can be resident at once,
-// each having asked for its weights, while the first of them is still running.  Without the
+// set-up and prefetching what earlier kernels do not write.  `pdl_trigger` lets the next kernel in
+// the stream start its own set-up.  Every kernel triggers AFTER its own wait: a kernel can then
+// overlap only the ONE kernel before it (whose own predecessors have all completed), which is
+// what the early loads of the streaming product and of decode attention rely on.  Without the
 // launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -16,8 +16,8 @@ namespace cie {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ residual, int hidden, int vocab, int* err) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) {
@@ -58,8 +58,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
                                    const float* __restrict__ gain, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * hidden;
@@ -130,8 +130,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const float* __restrict__ inv_freq, int q_heads, int kv_heads,
                                      int dim, int rot, int page_size, int write_cache, int* err) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int width = (q_heads + 2 * kv_heads) * dim;
@@ -208,8 +208,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens,
                                 int inter, int block) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const size_t total = (size_t)tokens * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -225,8 +225,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // bfloat16, 8 channels (16 bytes) per thread; needs inter % 8 == 0 and block % 8 == 0.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up,
                                        __nv_bfloat16* __restrict__ out, int tokens, int inter, int block) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int vectors = inter / 8;
   const size_t total = (size_t)tokens * vectors;
   for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;

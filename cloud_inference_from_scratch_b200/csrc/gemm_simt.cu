@@ -19,8 +19,8 @@ gemm_simt_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w, const flo
                  TOut* __restrict__ c, int m_total, int n_total, int k_total) {
   __shared__ float a_tile[kTileK][kTileM + 4];
   __shared__ float w_tile[kTileK][kTileN + 4];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * kTileM, n0 = blockIdx.x * kTileN;
   const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
@@ -73,8 +73,8 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256)
 gemm_small_m_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w, const float* __restrict__ bias,
                     TOut* __restrict__ c, int m_total, int n_total, int k_total) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= n_total) return;
   const TIn* wrow = w + (size_t)warp * k_total;

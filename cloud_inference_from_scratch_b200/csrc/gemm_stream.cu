@@ -104,15 +104,14 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
     load_x(step);
   };
 
-  // The weights do not depend on the kernels before this one: the CTA requests its first weight
-  // tiles before waiting for them, so the weight stream overlaps the tail of earlier kernels.
-  // (Asking L2 for the whole weight slice at this point was tried and made the step slower: the
-  // attention kernel holds whole SMs, so the chain of waiting kernels cannot get deep enough.)
-  pdl_trigger();
+  // The weights do not depend on the kernel before this one: the CTA requests its first weight
+  // tiles before waiting for it, so the weight stream overlaps the tail of that kernel.
+  // (Asking L2 for the whole weight slice at this point was tried and made the step slower.)
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s)
     if (s < steps) load_w(s);
   pdl_wait();
+  pdl_trigger();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < steps) load_x(s);

@@ -128,8 +128,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   __shared__ __align__(8) uint64_t acc_bar;
   __shared__ uint32_t tmem_base_s;
 
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int a_row0 = blockIdx.x * BM;
   const int b_row0 = blockIdx.y * BN;

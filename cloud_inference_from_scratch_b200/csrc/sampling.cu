@@ -36,8 +36,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   __shared__ float seg_sum[kThreads];
   __shared__ float bcast[2];
   __shared__ int chosen;
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)r * vocab;
 
