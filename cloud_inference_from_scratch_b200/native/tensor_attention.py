@@ -61,6 +61,15 @@ class TensorAttention:
         import os
 
         self.use_tma = 0 if os.environ.get("CIE_DECODE_TMA", "1") == "0" else 1
+        # prompt portions on tcgen05 where the kernel exists: head size 64 or 128, no window,
+        # pages of a multiple of 16 tokens; everything else stays on the mma.sync kernel
+        self._prefill_tc = None
+        if head_dim in (64, 128) and os.environ.get("CIE_PREFILL_TC", "1") != "0":
+            tc = _Lib(load_library("attention_prefill_tc.cu", {"HEAD_DIM": head_dim}))
+            self._prefill_tc = tc.function(
+                "cie_attention_prefill_tc",
+                [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, v, v],
+            )
 
     @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int) -> int:
@@ -100,6 +109,15 @@ class TensorAttention:
             plan = {name: torch.from_numpy(array).to(ops.device) for name, array in tiles.items()}
         num_tiles = plan["tile_request"].shape[0]
         ops.launches += 1
+        if (self._prefill_tc is not None and window <= 0 and kv.page_size % 16 == 0
+                and qkv.shape[1] % 8 == 0 and out.shape[1] % 8 == 0):
+            self._prefill_tc(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
+                             kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
+                             plan["tile_request"].data_ptr(), plan["tile_q0"].data_ptr(), num_tiles,
+                             ctx.context_lens.data_ptr(), ctx.query_lens.data_ptr(),
+                             ctx.query_start.data_ptr(), q_heads, kv_heads, kv.page_size,
+                             heads_per_tile(group), scale, ops.error_word.data_ptr(), ops.stream)
+            return True
         self._prefill(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                       kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
                       plan["tile_request"].data_ptr(), plan["tile_q0"].data_ptr(), num_tiles,

@@ -519,3 +519,25 @@ def test_gemm_tcgen05_silu_epilogue(tensor_ops, m):
     xf = x.float().cpu()
     want = torch.nn.functional.silu(xf @ gate.float().cpu().t()) * (xf @ up.float().cpu().t())
     torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
+
+
+# ------------------------------------------------------------------ prompt attention on tcgen05
+@pytest.mark.parametrize("dim,page,q_heads,kv_heads", [
+    (128, 16, 16, 2), (128, 48, 7, 1), (64, 16, 14, 2), (64, 128, 3, 3), (128, 64, 40, 8), (64, 32, 24, 2),
+])
+def test_prefill_attention_tcgen05(ops, dim, page, q_heads, kv_heads):
+    """Prompt portions whose keys cross several 128-key tiles, with and without a cached prefix,
+    beside short ones; lengths around the tile and page edges."""
+    item = ops[torch.bfloat16]
+    item.require_attention(dim)
+    assert item._tensor_attention[dim]._prefill_tc is not None, "the tcgen05 prefill kernel was not loaded"
+    tensor_case(ops, dim, [0, 127, 128, 300, 0], [129, 2, 256, 77, 1], q_heads, kv_heads, dim, page, seed=11)
+    tensor_case(ops, dim, [1000, 0], [3, 640], q_heads, kv_heads, dim, page, seed=12)
+
+
+def test_prefill_attention_tcgen05_far_key(ops):
+    """The last query of a 300-token portion behind 1,700 cached keys is aligned with key 5, then
+    with key 1,663 (the last key of a tile): the output must be that key's value."""
+    tensor_case(ops, 128, [1700, 10], [300, 4], 16, 2, 128, 16, seed=13, plant=(0, 5, 4.0))
+    tensor_case(ops, 128, [1700, 10], [300, 4], 16, 2, 128, 16, seed=14, plant=(0, 1663, 4.0))
+    tensor_case(ops, 64, [0], [513], 4, 1, 64, 16, seed=15, plant=(0, 384, 4.0))
