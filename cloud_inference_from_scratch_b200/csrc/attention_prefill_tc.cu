@@ -303,42 +303,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   if (warp == 5) tmem_free<TMEM_COLS>(tmem);
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// Tensor map of one layer's key (or value) pool seen as a matrix [pages * kv_heads * page_size, D],
-// read in boxes of 16 rows x 64 columns with 128-byte swizzle.  Maps are kept by pool address.
-static bool pool_map(const void* pool, long long rows, CUtensorMap* out) {
-  struct Entry { const void* pool; long long rows; CUtensorMap map; };
-  static Entry cache[512];
-  static int used = 0;
-  for (int i = 0; i < used; ++i)
-    if (cache[i].pool == pool && cache[i].rows == rows) { *out = cache[i].map; return true; }
-  static EncodeTiled encode = nullptr;
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess ||
-        status != cudaDriverEntryPointSuccess)
-      return false;
-    encode = reinterpret_cast<EncodeTiled>(fn);
-  }
-  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
-  cuuint32_t box[2] = {64, 16};
-  cuuint32_t elem[2] = {1, 1};
-  CUtensorMap map;
-  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return false;
-  if (used == 512) used = 0;
-  cache[used++] = Entry{pool, rows, map};
-  *out = map;
-  return true;
-}
-
 }  // namespace cie
 
 using namespace cie;
@@ -372,7 +336,8 @@ extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, 
   a.scale_log2 = scale * 1.4426950408889634f; a.err = err;
   CUtensorMap k_map, v_map;
   const long long rows = (long long)num_pages * kv_heads * page_size;
-  if (!pool_map(k_pool, rows, &k_map) || !pool_map(v_pool, rows, &v_map))
+  // the pools as matrices [pages * kv_heads * page_size, D], read in boxes of 16 rows
+  if (!tensor_map_bf16(k_pool, rows, D, 16, &k_map) || !tensor_map_bf16(v_pool, rows, D, 16, &v_map))
     CIE_FAIL("attention_prefill_tc: cuTensorMapEncodeTiled failed");
   static bool configured = false;
   if (!configured) {

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <mutex>
+#include <unordered_map>
 
 namespace cie {
 namespace bw {
@@ -123,6 +125,60 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// ---- host side: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn encode = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess ||
+        status != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(fn);
+  }();
+  return encode;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] (cols a multiple of 8, base 16-byte
+// aligned) read in boxes of [box_rows, 64 columns] with 128-byte swizzle; what lies outside the
+// matrix reads as zero.  Maps are kept by (address, shape, box) for the life of the process.
+inline bool tensor_map_bf16(const void* ptr, long long rows, long long cols, int box_rows, CUtensorMap* out) {
+  struct Key {
+    const void* ptr; long long rows, cols; int box_rows;
+    bool operator==(const Key& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^
+             (std::hash<long long>()(k.cols) * 131) ^ (size_t)k.box_rows;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex lock;
+  const Key key{ptr, rows, cols, box_rows};
+  std::lock_guard<std::mutex> guard(lock);
+  auto found = cache.find(key);
+  if (found != cache.end()) { *out = found->second; return true; }
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUtensorMap map;
+  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return true;
 }
 
 }  // namespace bw

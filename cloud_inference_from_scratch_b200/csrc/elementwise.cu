@@ -58,8 +58,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
                                    const float* __restrict__ gain, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
-  pdl_wait();
+  // The one kernel that triggers BEFORE its wait: what follows a norm is a matrix product, and
+  // all that product does before its own wait is to ask for weights, which no kernel writes.  It
+  // may therefore start beside the kernel before this one and stream weights through its tail.
   pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * hidden;

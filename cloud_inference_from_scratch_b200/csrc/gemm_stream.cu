@@ -2,7 +2,9 @@
 //
 // With at most 64 tokens a projection is bound by reading W once from HBM, so the kernel is
 // built around the weight stream: a CTA owns BN weight rows and a slice of K, and pulls
-// [BN x 128] weight tiles through a four-stage cp.async pipeline while tensor cores
+// [BN x 128] weight tiles through a four-stage pipeline (two TMA tensor copies per tile with
+// 128-byte swizzle, completing on the stage's mbarrier; cp.async for a weight whose address or
+// row length TMA cannot take) while tensor cores
 // (mma.sync m16n8k16, bfloat16 in, float32 accumulate) multiply them with the matching slice
 // of x.  Weights are the 16-row operand (the roles of the two operands are swapped), tokens are
 // the 8-wide operand, so 8 tokens cost no more tensor work than 1.
@@ -10,23 +12,35 @@
 // partial sums are written as float32 [splits][M][N] and added up, in a fixed order, by the
 // kernel that consumes them (residual-add + RMSNorm, or rotary + cache write), which also adds
 // the bias.  Epilogues: bfloat16 or float32 output with bias; float32 partials; SiLU(gate) * up
-// when the weight holds gate and up rows interleaved in blocks of BN/2.
+// when the weight holds gate and up rows interleaved in blocks of BN/2; and the residual
+// epilogue: the CTAs that share weight rows form a thread-block cluster, add their K slices up
+// through distributed shared memory in a fixed order, add the sum into the float32 residual
+// stream and leave the sum of squares of each new row slice for the product that normalises next.
+//
+// With the gain of the norm that follows, that epilogue also writes bfloat16(new row * gain): the
+// un-normalised input of the next product, which multiplies its own result rows by
+// rstd = rsqrt(mean square + eps), formed from those sums of squares, in its epilogue.  One
+// rounding to bfloat16 either way, and no RMSNorm kernel in between.
 //
 // The reference runs these products through cuBLAS (zeeshan8281/cloud-inference-from-scratch
 // src/cloud_engine/model.py:100,134-136,217,227).
+#include "blackwell.cuh"
 #include "common.cuh"
+
+#include <cooperative_groups.h>
 
 CIE_DEFINE_LAST_ERROR()
 
 namespace cie {
 
+namespace cg = cooperative_groups;
 using bf16 = __nv_bfloat16;
 constexpr int BK = 128;
 constexpr int WROW = BK + 8;
 constexpr int STAGES = 4;
 constexpr int KSTEPS = BK / 16;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+using bw::smem_u32;
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
@@ -45,7 +59,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kOutBF16 = 0, kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3;
+constexpr int kOutBF16 = 0, kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3, kOutResidual = 4;
 
 struct StreamArgs {
   const bf16* x;       // [M, K]
@@ -55,15 +69,49 @@ struct StreamArgs {
   int m, n, k;
   int k_per_split;     // multiple of BK
   int mode;
+  int* err;            // error word for a wait that ran out (TMA variant), may be null
+  // row scale: with row_sq the result rows are multiplied by rstd[m] = rsqrt(sum over tiles of
+  // row_sq[m][tile] / K + eps) before bias, partial-sum output or activation (x then holds
+  // bfloat16(h * gain) of the rows h whose squares were summed)
+  const float* row_sq;   // [M, row_tiles] or null
+  int row_tiles;
+  float eps;
+  // mode 4: residual[m][n] += sum over the cluster's K slices (+ bias);
+  // sq[m][blockIdx.x] = sum of squares of the new residual[m][n0 .. n0 + BN)
+  float* residual;     // [M, N]
+  float* sq;           // [M, gridDim.x]
+  // mode 4, optional: scaled[m][n] = bfloat16(new residual[m][n] * next_gain[n])
+  bf16* scaled;        // [M, N] or null
+  const float* next_gain;
 };
 
-template <int MT, int BN>
-__global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a) {
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ int timeout_sink;   // takes the time-out bit when the caller gave no error word
+
+// Shared-memory layout.  cp.async variant: weight rows padded to WROW elements.  TMA variant: a
+// weight stage is two boxes of [BN rows x 64 columns] as the copy leaves them (rows of 128 bytes,
+// the 16-byte piece c of row r at position c ^ (r & 7)), stages 1024-byte aligned.
+template <int BN, bool TMA>
+constexpr int w_stage_elems() { return TMA ? BN * BK : BN * WROW; }
+
+template <int MT, int BN, bool TMA>
+__global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map,
+                                                              const StreamArgs a) {
   constexpr int THREADS = BN * 2;   // one warp per 16 weight rows
   constexpr int MP = MT * 8;        // padded token count
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* w_s = reinterpret_cast<bf16*>(smem_raw);            // [STAGES][BN][WROW]
-  bf16* x_s = w_s + STAGES * BN * WROW;                     // [STAGES][MP][WROW]
+  constexpr int WSTAGE = w_stage_elems<BN, TMA>();
+  constexpr int XSTAGE = MP * WROW * 2;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem_base = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
+                                 : smem_raw;
+  bf16* w_s = reinterpret_cast<bf16*>(smem_base);           // [STAGES][WSTAGE]
+  unsigned char* x_s = reinterpret_cast<unsigned char*>(w_s + STAGES * WSTAGE);   // [STAGES][XSTAGE]
+  __shared__ __align__(8) uint64_t full[STAGES];
+  __shared__ float rstd_s[MP];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * BN;
   const int k_begin = blockIdx.y * a.k_per_split;
@@ -77,26 +125,37 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
     int tile = step + rotate;
     if (tile >= steps) tile -= steps;
     const int k0 = k_begin + tile * BK;
-    bf16* wd = w_s + (step % STAGES) * BN * WROW;
+    bf16* wd = w_s + (step % STAGES) * WSTAGE;
+    if constexpr (TMA) {
+      // K slices end on a tile edge or at K itself, where the copy fills with zeros
+      if (tid == 0) {
+        bw::mbar_expect_tx(&full[step % STAGES], BN * BK * 2);
+        bw::tma_load_2d(wd, &w_map, &full[step % STAGES], k0, n0);
+        bw::tma_load_2d(wd + BN * 64, &w_map, &full[step % STAGES], k0 + 64, n0);
+      }
+    } else {
 #pragma unroll
-    for (int i = 0; i < (BN * 16) / THREADS; ++i) {   // BN rows x 16 pieces of 16 bytes
-      const int e = tid + i * THREADS;
-      const int r = e >> 4, c = e & 15;
-      const int row = n0 + r, col = k0 + c * 8;
-      const bool ok = row < a.n && col < k_end;
-      cp_async16(wd + r * WROW + c * 8, ok ? a.w + (size_t)row * a.k + col : a.w, ok);
+      for (int i = 0; i < (BN * 16) / THREADS; ++i) {   // BN rows x 16 pieces of 16 bytes
+        const int e = tid + i * THREADS;
+        const int r = e >> 4, c = e & 15;
+        const int row = n0 + r, col = k0 + c * 8;
+        const bool ok = row < a.n && col < k_end;
+        cp_async16(wd + r * WROW + c * 8, ok ? a.w + (size_t)row * a.k + col : a.w, ok);
+      }
     }
   };
   auto load_x = [&](int step) {
     int tile = step + rotate;
     if (tile >= steps) tile -= steps;
     const int k0 = k_begin + tile * BK;
-    bf16* xd = x_s + (step % STAGES) * MP * WROW;
-    for (int e = tid; e < MP * 16; e += THREADS) {
-      const int r = e >> 4, c = e & 15;
-      const int col = k0 + c * 8;
-      const bool ok = r < a.m && col < k_end;
-      cp_async16(xd + r * WROW + c * 8, ok ? a.x + (size_t)r * a.k + col : a.x, ok);
+    {
+      bf16* xd = reinterpret_cast<bf16*>(x_s + (step % STAGES) * XSTAGE);
+      for (int e = tid; e < MP * 16; e += THREADS) {
+        const int r = e >> 4, c = e & 15;
+        const int col = k0 + c * 8;
+        const bool ok = r < a.m && col < k_end;
+        cp_async16(xd + r * WROW + c * 8, ok ? a.x + (size_t)r * a.k + col : a.x, ok);
+      }
     }
   };
   auto load_stage = [&](int step) {
@@ -107,6 +166,13 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
   // The weights do not depend on the kernel before this one: the CTA requests its first weight
   // tiles before waiting for it, so the weight stream overlaps the tail of that kernel.
   // (Asking L2 for the whole weight slice at this point was tried and made the step slower.)
+  if constexpr (TMA) {
+    if (tid == 0) {
+      for (int s = 0; s < STAGES; ++s) bw::mbar_init(&full[s], 1);
+      bw::mbar_init_fence();
+    }
+    __syncthreads();
+  }
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s)
     if (s < steps) load_w(s);
@@ -117,6 +183,33 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
     if (s < steps) load_x(s);
     cp_async_commit();
   }
+  if (a.row_sq) {
+    // rstd of every token row from the partial sums of squares (used in the epilogue, behind barriers)
+    // (every load is issued before the first sum needs one: one trip to L2, not one per value)
+    constexpr int ROWS = MP / (THREADS / 32);
+    constexpr int PER_LANE = 8;   // 256 tiles = rows of 8192 without a second pass
+    float vals[ROWS][PER_LANE];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+      const int m = warp + i * (THREADS / 32);
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) {
+        const int t = lane + 32 * j;
+        vals[i][j] = (m < a.m && t < a.row_tiles) ? __ldg(a.row_sq + (size_t)m * a.row_tiles + t) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+      const int m = warp + i * (THREADS / 32);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) sum += vals[i][j];
+      if (m < a.m)
+        for (int t = lane + 32 * PER_LANE; t < a.row_tiles; t += 32) sum += a.row_sq[(size_t)m * a.row_tiles + t];
+      sum = warp_sum(sum);
+      if (lane == 0) rstd_s[m] = m < a.m ? rsqrtf(sum / (float)a.k + a.eps) : 0.f;
+    }
+  }
 
   float acc[MT][4];
 #pragma unroll
@@ -124,20 +217,34 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
 
   for (int it = 0; it < steps; ++it) {
     cp_async_wait<STAGES - 2>();
+    if constexpr (TMA) {
+      if (!bw::mbar_wait(&full[it % STAGES], (it / STAGES) & 1, a.err ? a.err : &timeout_sink)) break;
+    }
     __syncthreads();
     if (it + STAGES - 1 < steps) load_stage(it + STAGES - 1);
     cp_async_commit();
-    const bf16* wt = w_s + (it % STAGES) * BN * WROW + warp * 16 * WROW;
-    const bf16* xt = x_s + (it % STAGES) * MP * WROW;
+    const bf16* ws = w_s + (it % STAGES) * WSTAGE;
+    const unsigned char* xt_raw = x_s + (it % STAGES) * XSTAGE;
+    const int wr = warp * 16 + (lane & 15);
 #pragma unroll
     for (int kp = 0; kp < KSTEPS / 2; ++kp) {
       uint32_t a0[4], a1[4];
-      ldsm_x4(a0, wt + (lane & 15) * WROW + (2 * kp) * 16 + (lane >> 4) * 8);
-      ldsm_x4(a1, wt + (lane & 15) * WROW + (2 * kp + 1) * 16 + (lane >> 4) * 8);
+      if constexpr (TMA) {
+        // 16-byte piece c of row wr: box c / 8, position (c % 8) ^ (wr % 8) in the 128-byte row
+        const int c0 = (2 * kp) * 2 + (lane >> 4), c1 = c0 + 2;
+        ldsm_x4(a0, ws + (c0 >> 3) * (BN * 64) + wr * 64 + (((c0 & 7) ^ (wr & 7)) << 3));
+        ldsm_x4(a1, ws + (c1 >> 3) * (BN * 64) + wr * 64 + (((c1 & 7) ^ (wr & 7)) << 3));
+      } else {
+        ldsm_x4(a0, ws + wr * WROW + (2 * kp) * 16 + (lane >> 4) * 8);
+        ldsm_x4(a1, ws + wr * WROW + (2 * kp + 1) * 16 + (lane >> 4) * 8);
+      }
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         uint32_t b[4];  // tokens mt*8.., k = kp*32 + {0, 8, 16, 24}
-        ldsm_x4(b, xt + (mt * 8 + (lane & 7)) * WROW + kp * 32 + (lane >> 3) * 8);
+        {
+          const bf16* xt = reinterpret_cast<const bf16*>(xt_raw);
+          ldsm_x4(b, xt + (mt * 8 + (lane & 7)) * WROW + kp * 32 + (lane >> 3) * 8);
+        }
         mma_bf16(acc[mt], a0, b[0], b[1]);
         mma_bf16(acc[mt], a1, b[2], b[3]);
       }
@@ -147,17 +254,64 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
   __syncthreads();
 
   // ---- epilogue through shared memory: out_s[token][weight row]
-  float* out_s = reinterpret_cast<float*>(smem_raw);   // [MP][BN + 1]
+  float* out_s = reinterpret_cast<float*>(smem_base);  // [MP][BN + 1]
   const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
     const int m0 = mt * 8 + 2 * t4, r0 = warp * 16 + g;
-    out_s[m0 * (BN + 1) + r0] = acc[mt][0];
-    out_s[(m0 + 1) * (BN + 1) + r0] = acc[mt][1];
-    out_s[m0 * (BN + 1) + r0 + 8] = acc[mt][2];
-    out_s[(m0 + 1) * (BN + 1) + r0 + 8] = acc[mt][3];
+    const float s0 = a.row_sq ? rstd_s[m0] : 1.f, s1 = a.row_sq ? rstd_s[m0 + 1] : 1.f;
+    out_s[m0 * (BN + 1) + r0] = acc[mt][0] * s0;
+    out_s[(m0 + 1) * (BN + 1) + r0] = acc[mt][1] * s1;
+    out_s[m0 * (BN + 1) + r0 + 8] = acc[mt][2] * s0;
+    out_s[(m0 + 1) * (BN + 1) + r0 + 8] = acc[mt][3] * s1;
   }
   __syncthreads();
+  if (a.mode == kOutResidual) {
+    if constexpr (BN == 32) {
+      // the CTAs of the cluster hold the K slices of the same [M x 32] block; row m is finished by
+      // the CTA of rank m % size, whose first warp adds the slices in rank order
+      cg::cluster_group cluster = cg::this_cluster();
+      const int size = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+      // this CTA's rows are rank, rank + size, ...: warp w takes every (THREADS / 32)-th of them;
+      // what does not depend on the other CTAs is fetched before the cluster meets
+      const int col = n0 + lane;
+      const int first = rank + warp * size, stride = size * (THREADS / 32);
+      constexpr int MAX_ROWS = (MP + THREADS / 32 - 1) / (THREADS / 32);   // per warp, if size == 1
+      float old[MAX_ROWS];
+      const float bias = (a.bias && col < a.n) ? a.bias[col] : 0.f;
+      const float next_gain = (a.scaled && col < a.n) ? a.next_gain[col] : 0.f;
+#pragma unroll
+      for (int i = 0; i < MAX_ROWS; ++i) {
+        const int m = first + i * stride;
+        old[i] = (m < a.m && col < a.n) ? a.residual[(size_t)m * a.n + col] : 0.f;
+      }
+      cluster.sync();
+#pragma unroll
+      for (int i = 0; i < MAX_ROWS; ++i) {
+        const int m = first + i * stride;
+        if (m >= a.m) break;
+        // all remote loads are issued before the first addition (a cluster has at most 8 CTAs)
+        float part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          part[r] = r < size ? cluster.map_shared_rank(out_s, r)[m * (BN + 1) + lane] : 0.f;
+        float v = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) v += part[r];
+        float square = 0.f;
+        if (col < a.n) {
+          const float updated = old[i] + (v + bias);
+          a.residual[(size_t)m * a.n + col] = updated;
+          if (a.scaled) a.scaled[(size_t)m * a.n + col] = __float2bfloat16_rn(updated * next_gain);
+          square = updated * updated;
+        }
+        square = warp_sum(square);
+        if (lane == 0) a.sq[(size_t)m * gridDim.x + blockIdx.x] = square;
+      }
+      cluster.sync();   // nobody leaves while its shared memory may still be read
+    }
+    return;
+  }
   if (a.mode == kOutSiluMul) {
     constexpr int HALF = BN / 2;
     const int c0 = blockIdx.x * HALF, channels = a.n / 2;
@@ -185,42 +339,98 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const StreamArgs a)
   }
 }
 
-template <int MT, int BN>
-static int launch(const StreamArgs& a, int splits, cudaStream_t stream) {
+template <int MT, int BN, bool TMA>
+static int launch_variant(const CUtensorMap& w_map, const StreamArgs& a, int splits, cudaStream_t stream) {
   constexpr int MP = MT * 8;
-  constexpr size_t pipeline = (size_t)STAGES * (BN + MP) * WROW * sizeof(bf16);
+  constexpr size_t pipeline = (size_t)STAGES * (w_stage_elems<BN, TMA>() + MP * WROW) * sizeof(bf16);
   constexpr size_t staging = (size_t)MP * (BN + 1) * sizeof(float);
-  constexpr size_t smem = pipeline > staging ? pipeline : staging;
+  constexpr size_t smem = (pipeline > staging ? pipeline : staging) + (TMA ? 1024 : 0);
   static bool configured = false;
   if (!configured) {
-    cudaError_t status = cudaFuncSetAttribute(gemm_stream_kernel<MT, BN>,
+    cudaError_t status = cudaFuncSetAttribute(gemm_stream_kernel<MT, BN, TMA>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (status != cudaSuccess) CIE_FAIL("gemm_stream: shared memory %zu: %s", smem, cudaGetErrorString(status));
     configured = true;
   }
-  dim3 grid((a.n + BN - 1) / BN, splits);
-  CIE_LAUNCH("gemm_stream", gemm_stream_kernel<MT, BN>, grid, dim3(BN * 2), smem, stream, a);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((a.n + BN - 1) / BN, splits);
+  config.blockDim = dim3(BN * 2);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  if (pdl_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  if (a.mode == kOutResidual && splits > 1) {
+    // the K slices of one block of weight rows are one thread-block cluster
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = 1;
+    attributes[count].val.clusterDim.y = splits;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  cudaError_t status = cudaLaunchKernelEx(&config, gemm_stream_kernel<MT, BN, TMA>, w_map, a);
+  if (status != cudaSuccess) CIE_FAIL("gemm_stream: launch failed: %s", cudaGetErrorString(status));
   return 0;
+}
+
+// TMA needs the weight 16-byte aligned with rows of a multiple of 16 bytes (K % 8 == 0 is checked
+// by the caller); CIE_STREAM_TMA=0 in the environment keeps cp.async.
+template <int MT, int BN>
+static int launch(const StreamArgs& a, int splits, cudaStream_t stream) {
+  static const bool allowed = [] {
+    const char* value = getenv("CIE_STREAM_TMA");
+    return !(value && value[0] == '0');
+  }();
+  CUtensorMap w_map = {};
+  if (allowed && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0 && bw::tensor_map_bf16(a.w, a.n, a.k, BN, &w_map))
+    return launch_variant<MT, BN, true>(w_map, a, splits, stream);
+  return launch_variant<MT, BN, false>(w_map, a, splits, stream);
 }
 
 }  // namespace cie
 
 using namespace cie;
 
-// mode: 0 bf16 out, 1 float32 out, 2 float32 partials [splits][M][N] (bias ignored),
-// 3 SiLU(gate)*up with gate/up rows interleaved in blocks of block_rows/2 (splits must be 1).
+// The general entry point.
+//  input:  x (bfloat16 [M, K]).  With row_sq ([M, row_tiles] float32 sums of squares of the rows
+//          that x was made from) every result row m is multiplied by
+//          rsqrt(sum of row_sq[m] / K + eps) before anything else is done with it.
+//  output: mode 0 bf16 out, 1 float32 out, 2 float32 partials [splits][M][N] (bias ignored),
+//          3 SiLU(gate)*up with gate/up rows interleaved in blocks of block_rows/2 (one split),
+//          4 residual[M, N] += product (+ bias), sq[M, ceil(N / 32)] = sums of squares of the new
+//          rows per block of 32 columns and, with next_gain, scaled[M, N] = bfloat16(new row *
+//          next_gain); splits must be 1, 2, 4 or 8 (the size of a cluster), block_rows 32.
 // block_rows: weight rows per CTA, 32 or 64.
-extern "C" int cie_gemm_stream(const void* x, const void* w, const float* bias, void* out, int m,
-                               int n, int k, int splits, int mode, int block_rows, void* stream) {
+extern "C" int cie_gemm_stream_ex(const void* x, const float* row_sq, int row_tiles, float eps, const void* w,
+                                  const float* bias, void* out, float* residual, float* sq, void* scaled,
+                                  const float* next_gain, int m, int n, int k, int splits, int mode,
+                                  int block_rows, int* err, void* stream) {
   if (m <= 0 || n <= 0) return 0;
+  if (!x || !w) CIE_FAIL("gemm_stream: null operand");
   if (m > 64) CIE_FAIL("gemm_stream: takes at most 64 rows, got %d", m);
   if (k < 8 || k % 8) CIE_FAIL("gemm_stream: K must be a multiple of 8 (16-byte rows), got %d", k);
   if (splits < 1) CIE_FAIL("gemm_stream: splits %d", splits);
+  if (mode < 0 || mode > kOutResidual) CIE_FAIL("gemm_stream: mode %d", mode);
   if (mode == kOutSiluMul && (splits != 1 || n % 2)) CIE_FAIL("gemm_stream: the SiLU epilogue needs one split and an even N");
-  if (mode != kOutPartial && splits != 1) CIE_FAIL("gemm_stream: %d splits need the partial-sum output", splits);
+  if (mode == kOutResidual) {
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) CIE_FAIL("gemm_stream: the residual epilogue takes 1, 2, 4 or 8 splits, got %d", splits);
+    if (block_rows != 32 || !residual || !sq) CIE_FAIL("gemm_stream: the residual epilogue needs 32-row blocks, a residual and a place for the sums of squares");
+    if ((scaled != nullptr) != (next_gain != nullptr)) CIE_FAIL("gemm_stream: the scaled copy needs both its buffer and the gain");
+  } else if (mode != kOutPartial && splits != 1) {
+    CIE_FAIL("gemm_stream: %d splits need the partial-sum or the residual output", splits);
+  }
+  if (row_sq && row_tiles < 1) CIE_FAIL("gemm_stream: %d tiles of sums of squares", row_tiles);
   StreamArgs a;
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out;
-  a.m = m; a.n = n; a.k = k; a.mode = mode;
+  a.m = m; a.n = n; a.k = k; a.mode = mode; a.err = err;
+  a.row_sq = row_sq; a.row_tiles = row_tiles; a.eps = eps;
+  a.residual = residual; a.sq = sq; a.scaled = (bf16*)scaled; a.next_gain = next_gain;
   const int k_tiles = (k + BK - 1) / BK;
   a.k_per_split = ((k_tiles + splits - 1) / splits) * BK;
   cudaStream_t s = (cudaStream_t)stream;
@@ -238,6 +448,14 @@ extern "C" int cie_gemm_stream(const void* x, const void* w, const float* bias, 
     return launch<8, 64>(a, splits, s);
   }
   CIE_FAIL("gemm_stream: block_rows must be 32 or 64, got %d", block_rows);
+}
+
+// bfloat16 input, modes 0..3.
+extern "C" int cie_gemm_stream(const void* x, const void* w, const float* bias, void* out, int m,
+                               int n, int k, int splits, int mode, int block_rows, int* err, void* stream) {
+  if (mode == kOutResidual) CIE_FAIL("gemm_stream: the residual epilogue is reached through cie_gemm_stream_ex");
+  return cie_gemm_stream_ex(x, nullptr, 0, 0.f, w, bias, out, nullptr, nullptr, nullptr, nullptr, m, n, k, splits,
+                            mode, block_rows, err, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -299,7 +517,7 @@ extern "C" int cie_gemm_stream_noalloc(const void* x, const void* w, const float
   float* scratch = nullptr;
   if (cie::scratch_address(&scratch) != 0) return 1;
   // partial sums of the existing kernel go to the built-in scratch ...
-  if (cie_gemm_stream(x, w, nullptr, scratch, m, n, k, splits, kOutPartial, 32, stream) != 0) return 1;
+  if (cie_gemm_stream(x, w, nullptr, scratch, m, n, k, splits, kOutPartial, 32, nullptr, stream) != 0) return 1;
   // ... and are added up, with the bias, by one more kernel (launched without programmatic
   // overlap, so it starts after the product has finished)
   const size_t total = (size_t)m * n;

@@ -65,7 +65,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
       const int oi = __shfl_xor_sync(0xffffffffu, best_i, offset);
       if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
     }
-    if (lane == 0) { bcast[0] = best; chosen = best_i; }
+    // a row without any comparable value (all NaN) yields token 0 rather than an index outside the vocabulary
+    if (lane == 0) { bcast[0] = best; chosen = best_i == 0x7fffffff ? 0 : best_i; }
   }
   __syncthreads();
   const float temp = temperature ? temperature[r] : 0.f;
@@ -94,7 +95,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
       if (before + seg_sum[i] > target) break;
       if (i + 1 < kThreads) before += seg_sum[i];
     }
-    // walk the owner's segment; fall back to the last token with weight > 0
+    // walk the owner's segment; if rounding left the target unreached, take the argmax
     const int b = min(owner * seg, vocab), e = min(b + seg, vocab);
     float running = before;
     int pick = -1;

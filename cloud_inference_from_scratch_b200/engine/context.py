@@ -56,3 +56,7 @@ class StepContext:
     bindings: list[LayerBinding] = field(default_factory=list)
     all_decode: bool = False  # every request brings exactly one token
     extras: dict[Any, dict[str, Any]] = field(default_factory=dict)
+    # The float32 residual stream [T, H] when every norm of the model accepts an ``Accumulated``
+    # update, else None.  A mixer or feed-forward may hand it to ``ops.linear(..., residual=...)``
+    # for its last projection, whose kernel then adds the result into the stream itself.
+    residual_sink: Any = None

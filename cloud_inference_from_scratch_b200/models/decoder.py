@@ -14,6 +14,7 @@ from dataclasses import dataclass
 from typing import Any
 
 from ..config.spec import ModelSpec
+from ..native.ops import ResidualSink
 from ..parts.base import (
     Block,
     CacheSpec,
@@ -85,6 +86,10 @@ class DecoderModel:
                 )
             )
         self.final_norm: Norm = build_part("norm", spec.final_norm)
+        # a projection may add itself into the residual stream only if whoever normalises next
+        # understands that the sum is already there
+        norms = [self.final_norm] + [n for layer in self.layers for n in (layer.mixer_norm, layer.feed_forward_norm)]
+        self.norms_accept_accumulated = all(getattr(norm, "accepts_accumulated", False) for norm in norms)
         self.embedding: Any = None
         self.head: Any = None
         self.runtime: Any = None
@@ -150,8 +155,18 @@ class DecoderModel:
         spec = self.spec
         residual = rt.workspace.get("residual", ctx.num_tokens, spec.hidden_size, torch.float32)
         rt.ops.embedding(ctx.token_ids, self.embedding, residual)
+        sink = ResidualSink(residual) if self.norms_accept_accumulated else None
+        ctx.residual_sink = sink
         pending = None
         for index, entry in enumerate(spec.schedule):
+            if sink is not None:
+                # who normalises after this layer: the next layer's first norm, if its mixer can
+                # finish a pre-scaled norm; the final norm takes the plain kernel
+                sink.following_gain = None
+                if index + 1 < len(spec.schedule):
+                    following = self.layers[spec.schedule[index + 1].layer].block
+                    if getattr(following.mixer, "takes_normed_input", False) and hasattr(following.mixer_norm, "forward_lazy"):
+                        sink.following_gain = getattr(following.mixer_norm, "lazy_gain", None)
             pending = self.layers[entry.layer].block.forward(
                 residual, pending, ctx, ctx.bindings[index]
             )

@@ -11,6 +11,7 @@ kernel takes raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Any
 
@@ -44,6 +45,48 @@ class Partials:
         return (self.rows, self.width)
 
 
+class ResidualSink:
+    """The float32 residual stream [T, H] as a target: a projection handed this (``Ops.linear(...,
+    residual=sink)``) may add its result into ``tensor`` itself.  ``gain`` is the gain vector of the
+    norm that will read the stream next, when that norm can take its input pre-scaled (else None);
+    whoever arranges the layers sets it before each projection."""
+
+    def __init__(self, tensor: Any) -> None:
+        self.tensor = tensor
+        self.gain: Any = None
+        self.following_gain: Any = None   # for the last projection of the current layer
+
+
+class Accumulated:
+    """A projection that its own kernel has already added into the float32 residual stream.
+
+    ``sq`` holds, for every token row, the sums of squares of the new residual row per block of 32
+    columns ([rows, tiles] float32): a norm that follows needs no pass over the row to know its
+    mean square.  ``scaled`` (or None) is bfloat16(new row * ``gain``) for the norm whose gain
+    vector ``gain`` is.  A consumer that only wants the sum treats this as "nothing left to add"."""
+
+    def __init__(self, residual: Any, sq: Any, tiles: int, scaled: Any = None, gain: Any = None) -> None:
+        self.residual, self.sq, self.tiles, self.scaled, self.gain = residual, sq, tiles, scaled, gain
+
+    @property
+    def shape(self) -> tuple[int, ...]:
+        return tuple(self.residual.shape)
+
+
+class NormedInput:
+    """RMSNorm of the residual rows, not yet divided by the root mean square: ``accumulated.scaled``
+    holds bfloat16(row * gain) and the matrix product that takes this (``Ops.linear``,
+    ``Ops.gate_up``) multiplies its result rows by rstd, which it forms from ``accumulated.sq``.
+    ``materialize()`` runs the ordinary norm kernel and returns a plain tensor for anyone else."""
+
+    def __init__(self, accumulated: Accumulated, eps: float, materialize: Any) -> None:
+        self.accumulated, self.eps, self.materialize = accumulated, eps, materialize
+
+    @property
+    def shape(self) -> tuple[int, ...]:
+        return tuple(self.accumulated.scaled.shape)
+
+
 class GateUpWeight:
     """Stacked gate and up matrices [2I, H].  ``block`` == I: all gate rows, then all up rows.
     ``block`` < I: rows interleaved in blocks (``block`` gate rows, the matching ``block`` up
@@ -55,6 +98,9 @@ class GateUpWeight:
 
 SM_COUNT = 148
 STREAM_MAX_ROWS = 16   # more rows than this go to the tile kernels (tcgen05 or the library)
+# Up to this many rows a projection adds itself into the residual stream (cluster epilogue of the
+# streaming kernel); measured on B200, 9..16 rows are faster with partial sums and the norm kernel.
+FUSED_RESIDUAL_MAX_ROWS = 8
 
 
 class _Lib:
@@ -122,11 +168,16 @@ class Ops:
         self._tensor_gemm = None
         self._tensor_attention: dict[int, Any] = {}
         self._gemm_stream = None
+        self._gemm_stream_ex = None
+        self.fuse_norm = False
         self._partial_buffers: dict[str, Any] = {}
         self.scratch_frozen = False
         if self.code == BF16 and self.gemm_mode != "simt":
             st = _Lib(load_library("gemm_stream.cu"))
-            self._gemm_stream = st.function("cie_gemm_stream", [v, v, v, v, i, i, i, i, i, i, v])
+            self._gemm_stream = st.function("cie_gemm_stream", [v, v, v, v, i, i, i, i, i, i, v, v])
+            self._gemm_stream_ex = st.function(
+                "cie_gemm_stream_ex", [v, v, i, f, v, v, v, v, v, v, v, i, i, i, i, i, i, v, v])
+            self.fuse_norm = os.environ.get("CIE_FUSE_NORM", "1") != "0"
         if self.code == BF16 and self.gemm_mode == "tensor":
             from .tensor_gemm import TensorGemm
 
@@ -187,6 +238,8 @@ class Ops:
         """``update``: None, a tensor [T, H] of the compute dtype, or ``Partials``."""
         count, hidden = out.shape
         self.launches += 1
+        if isinstance(update, Accumulated):
+            update = None   # its kernel has added it already
         if isinstance(update, Partials) and update.splits == 0:
             update = self.resolve(update, None)
         if isinstance(update, Partials):
@@ -228,12 +281,27 @@ class Ops:
     def freeze_scratch(self) -> None:
         self.scratch_frozen = True
 
+    def _stream(self, x: Any, weight: Any, bias: Any, out: Any, m: int, n: int, k: int, splits: int,
+                mode: int, residual: Any = None, sq: Any = None, scaled: Any = None,
+                next_gain: Any = None) -> None:
+        """One launch of the streaming kernel; ``x`` is a tensor or a ``NormedInput``."""
+        self.launches += 1
+        row_sq, tiles, eps = None, 0, 0.0
+        if isinstance(x, NormedInput):
+            row_sq, tiles, eps, x = x.accumulated.sq, x.accumulated.tiles, x.eps, x.accumulated.scaled
+        self._gemm_stream_ex(_ptr(x), _ptr(row_sq), tiles, eps, _ptr(weight), _ptr(bias), _ptr(out),
+                             _ptr(residual), _ptr(sq), _ptr(scaled), _ptr(next_gain), m, n, k, splits,
+                             mode, 32, _ptr(self.error_word), self.stream)
+
     def linear(self, x: Any, weight: Any, bias: Any, out: Any, allow_partials: bool = False,
-               tag: str = "", defer_bias: bool = False) -> Any:
+               tag: str = "", defer_bias: bool = False, residual: Any = None) -> Any:
         """out[M, N] = x[M, K] @ weight[N, K]^T (+ bias); out is the compute dtype or float32.
 
-        Returns ``out``, or, when ``allow_partials`` and the product was cut along K, a
-        ``Partials`` that a consuming kernel adds up (then ``out`` was not written)."""
+        Returns ``out``; or, when ``allow_partials`` and the product was cut along K, a
+        ``Partials`` that a consuming kernel adds up (then ``out`` was not written); or, when the
+        caller names the ``ResidualSink`` its result is to be added to and the streaming kernel
+        takes the shape, an ``Accumulated`` (the sum is in the residual stream, ``out`` was not
+        written).  ``x`` may be a ``NormedInput``."""
         m, k = x.shape
         n = weight.shape[0]
         if weight.shape[1] != k or tuple(out.shape) != (m, n):
@@ -241,18 +309,31 @@ class Ops:
         if m == 0:
             return out
         plan = self.stream_plan(m, n, k, allow_partials) if self.code == BF16 else None
+        if plan is None and isinstance(x, NormedInput):
+            x = x.materialize()
         if plan is not None:
             block_rows, splits = plan
-            self.launches += 1
+            if residual is not None and self.fuse_norm and allow_partials and m <= FUSED_RESIDUAL_MAX_ROWS:
+                cluster = 1
+                while cluster * 2 <= splits:
+                    cluster *= 2
+                tiles = -(-n // 32)
+                sq = self.scratch("sq." + (tag or "linear"), m * tiles, reserve=STREAM_MAX_ROWS * tiles)
+                gain = residual.gain if n % 8 == 0 else None
+                scaled = None
+                if gain is not None:
+                    scaled = self.scratch("scaled." + (tag or "linear"), (m * n + 1) // 2,
+                                          reserve=STREAM_MAX_ROWS * n // 2)
+                    scaled = scaled.view(self.torch.bfloat16)[: m * n].view(m, n)
+                self._stream(x, weight, bias, None, m, n, k, cluster, 4, residual=residual.tensor, sq=sq,
+                             scaled=scaled, next_gain=gain)
+                return Accumulated(residual.tensor, sq, tiles, scaled, gain)
             if splits > 1:
                 scratch = self.scratch("partials." + (tag or "linear"), splits * m * n,
                                        reserve=splits * STREAM_MAX_ROWS * n)
-                self._gemm_stream(_ptr(x), _ptr(weight), None, _ptr(scratch), m, n, k, splits, 2,
-                                  block_rows, self.stream)
+                self._stream(x, weight, None, scratch, m, n, k, splits, 2)
                 return Partials(scratch, splits, m, n, bias)
-            mode = 1 if out.dtype == self.torch.float32 else 0
-            self._gemm_stream(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k, 1, mode,
-                              block_rows, self.stream)
+            self._stream(x, weight, bias, out, m, n, k, 1, 1 if out.dtype == self.torch.float32 else 0)
             return out
         if self._tensor_gemm is not None and self._tensor_gemm.run(x, weight, bias, out):
             return out
@@ -304,10 +385,10 @@ class Ops:
         if self.code == BF16 and weight.block == 16:
             plan = self.stream_plan(m, 2 * inter, k, False)
             if plan is not None:
-                self.launches += 1
-                self._gemm_stream(_ptr(x), _ptr(weight.weight), None, _ptr(hidden_out), m, 2 * inter,
-                                  k, 1, 3, 32, self.stream)
+                self._stream(x, weight.weight, None, hidden_out, m, 2 * inter, k, 1, 3)
                 return hidden_out
+        if isinstance(x, NormedInput):
+            x = x.materialize()
         both = workspace.get("swiglu.gate_up", m, 2 * inter, self.dtype)
         self.linear(x, weight.weight, None, both)
         self.silu_mul(both, hidden_out, weight.block)

@@ -88,6 +88,8 @@ class Attention(Mixer):
             self.position.bind({}, runtime)
         runtime.ops.require_attention(self.head_dim)
 
+    takes_normed_input = True   # x goes to ops.linear only
+
     def forward(self, x, ctx, binding):
         rt = self.runtime
         tokens = x.shape[0]
@@ -107,7 +109,8 @@ class Attention(Mixer):
             self.scale, self.window,
         )
         update = rt.workspace.get("mixer.update", tokens, self.hidden_size, rt.dtype)
-        return rt.ops.linear(mixed, self.w_o, None, update, allow_partials=True, tag="mixer.update")
+        return rt.ops.linear(mixed, self.w_o, None, update, allow_partials=True, tag="mixer.update",
+                             residual=getattr(ctx, "residual_sink", None))
 
 
 register_part("mixer", "attention", Attention, replace=True)

@@ -10,11 +10,32 @@ from __future__ import annotations
 from .base import Block, register_part
 
 
+def _normalise(norm, consumer, residual, pending, ctx):
+    """A consumer that declares ``takes_normed_input`` may get the norm un-computed (see
+    ``Norm.forward_lazy``); every other pairing runs the norm's kernel."""
+    lazy = getattr(norm, "forward_lazy", None)
+    if lazy is not None and getattr(consumer, "takes_normed_input", False):
+        return lazy(residual, pending, ctx)
+    return norm.forward(residual, pending, ctx)
+
+
+def _lazy_gain(norm, consumer):
+    """The gain a projection may pre-multiply with for ``norm``, if ``consumer`` can finish it."""
+    if getattr(consumer, "takes_normed_input", False) and hasattr(norm, "forward_lazy"):
+        return getattr(norm, "lazy_gain", None)
+    return None
+
+
 class PreNormResidual(Block):
     def forward(self, residual, pending, ctx, binding):
-        x = self.mixer_norm.forward(residual, pending, ctx)
+        sink = getattr(ctx, "residual_sink", None)
+        x = _normalise(self.mixer_norm, self.mixer, residual, pending, ctx)
+        if sink is not None:   # the mixer's sum is read next by this layer's second norm
+            sink.gain = _lazy_gain(self.feed_forward_norm, self.feed_forward)
         update = self.mixer.forward(x, ctx, binding)
-        x = self.feed_forward_norm.forward(residual, update, ctx)
+        x = _normalise(self.feed_forward_norm, self.feed_forward, residual, update, ctx)
+        if sink is not None:   # the feed-forward's sum by whoever comes after this layer
+            sink.gain = sink.following_gain
         return self.feed_forward.forward(x, ctx)
 
 

@@ -28,6 +28,8 @@ class SwiGLU(FeedForward):
         self.w_gate_up = runtime.ops.prepare_gate_up(tensors["gate_proj.weight"], tensors["up_proj.weight"])
         self.w_down = runtime.ops.prepare_weight(tensors["down_proj.weight"])
 
+    takes_normed_input = True   # x goes to ops.gate_up only
+
     def forward(self, x, ctx):
         rt = self.runtime
         tokens = x.shape[0]
@@ -35,7 +37,7 @@ class SwiGLU(FeedForward):
         rt.ops.gate_up(x, self.w_gate_up, hidden, rt.workspace)
         update = rt.workspace.get("feed_forward.update", tokens, self.hidden_size, rt.dtype)
         return rt.ops.linear(hidden, self.w_down, None, update, allow_partials=True,
-                             tag="feed_forward.update")
+                             tag="feed_forward.update", residual=getattr(ctx, "residual_sink", None))
 
 
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)

@@ -8,6 +8,7 @@ the same kernel, and the result is rounded once to the compute dtype.
 
 from __future__ import annotations
 
+from ..native.ops import Accumulated, NormedInput
 from .base import Norm, TensorSpec, register_part
 
 
@@ -23,6 +24,8 @@ class RMSNorm(Norm):
         self.runtime = runtime
         self.weight = tensors["weight"]
 
+    accepts_accumulated = True   # ``update`` may be an ``Accumulated``: the sum is already in the stream
+
     def forward(self, residual, update, ctx, rows=None):
         rt = self.runtime
         count = residual.shape[0] if rows is None else rows.shape[0]
@@ -30,6 +33,20 @@ class RMSNorm(Norm):
                                self.hidden_size, rt.dtype)
         rt.ops.add_rmsnorm(residual, update, self.weight, self.eps, out, rows)
         return out
+
+    @property
+    def lazy_gain(self):
+        """The gain vector a projection may pre-multiply the new residual rows with for this norm
+        (see ``forward_lazy``)."""
+        return self.weight
+
+    def forward_lazy(self, residual, update, ctx):
+        """For a consumer that finishes the norm itself (``takes_normed_input``): when the sum is
+        already in the stream, scaled by this norm's gain, and its sums of squares are known,
+        nothing runs here."""
+        if isinstance(update, Accumulated) and update.scaled is not None and update.gain is self.weight:
+            return NormedInput(update, self.eps, materialize=lambda: self.forward(residual, None, ctx))
+        return self.forward(residual, update, ctx)
 
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)

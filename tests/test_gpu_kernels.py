@@ -541,3 +541,77 @@ def test_prefill_attention_tcgen05_far_key(ops):
     tensor_case(ops, 128, [1700, 10], [300, 4], 16, 2, 128, 16, seed=13, plant=(0, 5, 4.0))
     tensor_case(ops, 128, [1700, 10], [300, 4], 16, 2, 128, 16, seed=14, plant=(0, 1663, 4.0))
     tensor_case(ops, 64, [0], [513], 4, 1, 64, 16, seed=15, plant=(0, 384, 4.0))
+
+
+# ------------------------------------------------------------------ residual epilogue and normed input
+@pytest.mark.parametrize("m", [1, 5, 8])
+@pytest.mark.parametrize("n,k", [(2048, 2048), (2048, 11008), (331, 96), (1000, 520)])
+def test_gemm_stream_adds_into_the_residual_and_feeds_the_next_product(ops, m, n, k):
+    """A projection adds itself into the float32 residual stream (its K slices are one cluster) and
+    leaves the sums of squares and the rows times the next norm's gain; the next product divides
+    its result rows by the root mean square."""
+    from cloud_inference_from_scratch_b200.engine.runtime import Workspace
+    from cloud_inference_from_scratch_b200.native.ops import Accumulated, NormedInput, ResidualSink
+
+    item = ops[torch.bfloat16]
+    x = rand(m, k, dtype=torch.bfloat16, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n)
+    bias = rand(n, seed=k)
+    before = rand(m, n, seed=5)
+    residual = before.clone()
+    gain = 1 + rand(n, scale=0.1, seed=4)
+    sink = ResidualSink(residual)
+    sink.gain = gain
+    out = torch.empty(m, n, dtype=torch.bfloat16).cuda()
+    got = item.linear(x, w, bias, out, allow_partials=True, tag=f"residual{n}x{k}", residual=sink)
+    assert isinstance(got, Accumulated) and got.residual is residual
+    want = before + plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).cuda()
+    scale = float(want.abs().max())
+    torch.testing.assert_close(residual, want, rtol=2e-3, atol=2e-3 * max(1.0, scale))
+    squares = got.sq[: m * got.tiles].view(m, got.tiles).sum(-1)
+    torch.testing.assert_close(squares, residual.pow(2).sum(-1), rtol=1e-4, atol=1e-4)
+    if n % 8:
+        assert got.scaled is None      # rows of the next product's input would not be 16-byte aligned
+        return
+    assert got.gain is gain
+    torch.testing.assert_close(got.scaled.float(), (residual * gain).to(torch.bfloat16).float(), rtol=0, atol=0)
+
+    # the same rows as the input of a product that finishes the RMSNorm itself
+    eps = 1e-5
+    lazy = NormedInput(got, eps, materialize=None)
+    normed = plain_model.rms_norm(residual.cpu(), gain.cpu(), eps)
+    w2 = rand(200, n, dtype=torch.bfloat16, scale=0.05, seed=7)
+    logits = torch.empty(m, 200, dtype=torch.float32).cuda()
+    assert item.linear(lazy, w2, None, logits) is logits
+    want2 = normed @ w2.float().cpu().t()
+    torch.testing.assert_close(logits.cpu(), want2, rtol=2e-2, atol=2e-2 * max(1.0, float(want2.abs().max()) / 4))
+    inter = 208
+    gate = rand(inter, n, dtype=torch.bfloat16, scale=0.05, seed=8)
+    up = rand(inter, n, dtype=torch.bfloat16, scale=0.05, seed=9)
+    hidden = torch.empty(m, inter, dtype=torch.bfloat16).cuda()
+    item.gate_up(lazy, item.prepare_gate_up(gate, up), hidden, Workspace("cuda:0"))
+    want3 = torch.nn.functional.silu(normed @ gate.float().cpu().t()) * (normed @ up.float().cpu().t())
+    torch.testing.assert_close(hidden.float().cpu(), want3, rtol=2e-2, atol=2e-2 * max(1.0, float(want3.abs().max()) / 4))
+    # and as partial sums for a consumer that adds them up
+    parts = item.linear(lazy, w2, None, torch.empty(m, 200, dtype=torch.bfloat16).cuda(), allow_partials=True, tag="lazy.parts")
+    total = torch.empty(m, 200, dtype=torch.float32).cuda()
+    torch.testing.assert_close(item.resolve(parts, total).float().cpu(), want2, rtol=2e-2,
+                               atol=2e-2 * max(1.0, float(want2.abs().max()) / 4))
+
+
+def test_a_projection_of_more_rows_leaves_the_sum_to_the_norm(ops):
+    """Above the row limit of the residual epilogue the same call returns partial sums (or the
+    product) and the residual is untouched."""
+    from cloud_inference_from_scratch_b200.native.ops import Accumulated, FUSED_RESIDUAL_MAX_ROWS, ResidualSink
+
+    item = ops[torch.bfloat16]
+    m, n, k = FUSED_RESIDUAL_MAX_ROWS + 1, 2048, 2048
+    x = rand(m, k, dtype=torch.bfloat16, seed=1)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=2)
+    residual = rand(m, n, seed=3)
+    before = residual.clone()
+    out = torch.empty(m, n, dtype=torch.bfloat16).cuda()
+    got = item.linear(x, w, None, out, allow_partials=True, tag="rows9", residual=ResidualSink(residual))
+    assert not isinstance(got, Accumulated)
+    torch.cuda.synchronize()
+    assert torch.equal(residual, before)

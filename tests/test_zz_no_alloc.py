@@ -25,7 +25,7 @@ def load():
     v, i = c_void_p, c_int
     lib.cie_gemm_stream_noalloc.argtypes = [v, v, v, v, i, i, i, i, v]
     lib.cie_gemm_stream_noalloc.restype = c_int
-    lib.cie_gemm_stream.argtypes = [v, v, v, v, i, i, i, i, i, i, v]
+    lib.cie_gemm_stream.argtypes = [v, v, v, v, i, i, i, i, i, i, v, v]
     lib.cie_gemm_stream.restype = c_int
     return lib
 
@@ -36,7 +36,7 @@ def regular(lib, x, w, bias, splits):
     n = w.shape[0]
     parts = torch.empty(splits, m, n, dtype=torch.float32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
-    status = lib.cie_gemm_stream(x.data_ptr(), w.data_ptr(), None, parts.data_ptr(), m, n, k, splits, 2, 32, stream)
+    status = lib.cie_gemm_stream(x.data_ptr(), w.data_ptr(), None, parts.data_ptr(), m, n, k, splits, 2, 32, None, stream)
     assert status == 0, lib.cie_last_error().decode()
     total = parts[0].clone()
     for s in range(1, splits):
