@@ -123,6 +123,18 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
 // The source row is either qkv itself (partial_splits == 0; then q_out == qkv and q is rotated
 // in place; a bias not yet added may be given) or float32 partial sums [splits][T][width] of the projection plus its bias
 // (partial_splits > 0; then the rotated q is written to q_out, rows of q_stride elements).
+//
+// paired != 0: the columns of every q and k head in the source are in the paired layout (the
+// weight rows were laid out so for the rotary epilogue of the streaming product): element d < rot
+// of a head stands at paired_column(d, rot), the rest (and v) where it always stands.  q_out must
+// then be another buffer than the source; what is written is in the natural order.
+__host__ __device__ __forceinline__ int paired_column(int d, int rot) {
+  // blocks of 32 columns: 16 elements of the first half of the rotary dims, then their 16 partners
+  const int half = rot / 2;
+  if (d >= rot) return d;
+  return d < half ? (d / 16) * 32 + d % 16 : ((d - half) / 16) * 32 + 16 + (d - half) % 16;
+}
+
 template <typename T>
 __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_splits,
                                      size_t partial_stride, const float* __restrict__ bias,
@@ -132,11 +144,13 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
                                      const int* __restrict__ table, int table_width, int num_pages,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const float* __restrict__ inv_freq, int q_heads, int kv_heads,
-                                     int dim, int rot, int page_size, int write_cache, int* err) {
+                                     int dim, int rot, int page_size, int write_cache, int paired,
+                                     int* err) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
   const int pos = positions[t];
+  const bool out_of_place = reinterpret_cast<const void*>(q_out) != src;
   const int width = (q_heads + 2 * kv_heads) * dim;
   const T* row_t = partial_splits == 0 ? reinterpret_cast<const T*>(src) + (size_t)t * width : nullptr;
   const float* row_p = partial_splits > 0 ? reinterpret_cast<const float*>(src) + (size_t)t * width : nullptr;
@@ -173,7 +187,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
     float s, c;
     sincosf((float)pos * inv_freq[j], &s, &c);
     for (int h = first_head; h < rot_heads; h += lanes_per_head_set) {
-      const float a = value(h * dim + j), b = value(h * dim + j + half);
+      const float a = value(h * dim + (paired ? paired_column(j, rot) : j));
+      const float b = value(h * dim + (paired ? paired_column(j + half, rot) : j + half));
       const T ra = from_float<T>(a * c - b * s), rb = from_float<T>(b * c + a * s);
       if (h < q_heads) {
         q_row[h * dim + j] = ra;
@@ -187,7 +202,7 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
   }
   // the part of q and k beyond the rotary dims passes through
   const int tail = dim - rot;
-  if (tail > 0 && (row_p || bias)) {
+  if (tail > 0 && (row_p || bias || out_of_place)) {
     for (int i = threadIdx.x; i < q_heads * tail; i += blockDim.x) {
       const int h = i / tail, d = rot + i % tail;
       q_row[h * dim + d] = from_float<T>(value(h * dim + d));
@@ -296,9 +311,11 @@ extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long 
                                  const int* request_of_token, const int* table, int table_width,
                                  int num_pages, void* k_pool, void* v_pool, const float* inv_freq,
                                  int tokens, int q_heads, int kv_heads, int dim, int rot,
-                                 int page_size, int write_cache, int dtype, int* err, void* stream) {
+                                 int page_size, int write_cache, int paired, int dtype, int* err,
+                                 void* stream) {
   if (tokens <= 0) return 0;
   if (rot % 2 || rot > dim || rot < 0) CIE_FAIL("rope_kv_write: rotary size %d does not fit head size %d", rot, dim);
+  if (paired && (rot % 32 || q_out == src)) CIE_FAIL("rope_kv_write: the paired layout needs a rotary size that is a multiple of 32 and a q buffer of its own");
   if (partial_splits > kMaxSplits) CIE_FAIL("rope_kv_write: at most %d partial sums, got %d", kMaxSplits, partial_splits);
   DISPATCH_DTYPE(dtype, "rope_kv_write", {
     const int work = (q_heads + kv_heads) * (rot / 2) > kv_heads * dim ? (q_heads + kv_heads) * (rot / 2) : kv_heads * dim;
@@ -308,7 +325,7 @@ extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long 
     CIE_LAUNCH("rope_kv_write", rope_kv_write_kernel<T>, dim3(tokens), dim3(threads), 0,
                (cudaStream_t)stream, src, partial_splits, (size_t)partial_stride, bias, (T*)q_out,
                q_stride, positions, request_of_token, table, table_width, num_pages, (T*)k_pool,
-               (T*)v_pool, inv_freq, q_heads, kv_heads, dim, rot, page_size, write_cache, err);
+               (T*)v_pool, inv_freq, q_heads, kv_heads, dim, rot, page_size, write_cache, paired, err);
   })
   return 0;
 }

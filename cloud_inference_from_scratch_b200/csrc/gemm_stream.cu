@@ -17,7 +17,12 @@
 // through distributed shared memory in a fixed order, add the sum into the float32 residual
 // stream and leave the sum of squares of each new row slice for the product that normalises next.
 //
-// With the gain of the norm that follows, that epilogue also writes bfloat16(new row * gain): the
+// The rotary epilogue works the same way for the stacked q/k/v projection of a decode step: the
+// cluster adds its K slices, then rotates q and k (weight rows of a head are laid out so that the
+// two elements of a rotary pair are 16 lanes apart in one CTA), writes q for the attention kernel
+// and k and v straight into their cache pages.
+//
+// With the gain of the norm that follows, the residual epilogue also writes bfloat16(new row * gain): the
 // un-normalised input of the next product, which multiplies its own result rows by
 // rstd = rsqrt(mean square + eps), formed from those sums of squares, in its epilogue.  One
 // rounding to bfloat16 either way, and no RMSNorm kernel in between.
@@ -59,7 +64,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kOutBF16 = 0, kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3, kOutResidual = 4;
+constexpr int kOutBF16 = 0, kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3, kOutResidual = 4, kOutRope = 5;
 
 struct StreamArgs {
   const bf16* x;       // [M, K]
@@ -83,6 +88,18 @@ struct StreamArgs {
   // mode 4, optional: scaled[m][n] = bfloat16(new residual[m][n] * next_gain[n])
   bf16* scaled;        // [M, N] or null
   const float* next_gain;
+  // mode 5: the product is the stacked q/k/v projection [M, (Hq + 2 Hkv) * D] of M tokens, q and k
+  // rows in the paired layout (see paired_column in elementwise.cu)
+  bf16* q_out;         // [M, q_stride]: rotated q, natural order
+  int q_stride;
+  const int* positions;          // [M]
+  const int* request_of_token;   // [M]
+  const int* table;              // [requests][table_width]
+  int table_width, num_pages;
+  bf16* k_pool;        // [pages][Hkv][page_size][D]
+  bf16* v_pool;
+  const float* inv_freq;         // [rot / 2]
+  int q_heads, kv_heads, dim, rot, page_size, write_cache;
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -312,6 +329,76 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
     }
     return;
   }
+  if (a.mode == kOutRope) {
+    if constexpr (BN == 32) {
+      cg::cluster_group cluster = cg::this_cluster();
+      const int size = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+      const int first = rank + warp * size, stride = size * (THREADS / 32);
+      constexpr int MAX_ROWS = (MP + THREADS / 32 - 1) / (THREADS / 32);
+      // the 32 columns of this CTA lie in one head (D is a multiple of 32)
+      const int q_width = a.q_heads * a.dim, kv_width = a.kv_heads * a.dim;
+      const int region = n0 < q_width ? 0 : n0 < q_width + kv_width ? 1 : 2;   // q, k, v
+      const int local = n0 - (region == 0 ? 0 : region == 1 ? q_width : q_width + kv_width);
+      const int head = local / a.dim, p0 = local % a.dim;
+      const int half = a.rot / 2;
+      const bool rotary = region < 2 && p0 < a.rot;
+      // natural position of this lane's element inside its head, and its rotary frequency
+      const int pair = (p0 >> 5) * 16 + (lane & 15);
+      const int d_out = rotary ? (lane < 16 ? pair : half + pair) : p0 + lane;
+      const float freq = rotary ? a.inv_freq[pair] : 0.f;
+      const float bias = a.bias ? a.bias[n0 + lane] : 0.f;
+      int pos[MAX_ROWS];
+      long long slot[MAX_ROWS];   // element offset of (page, head 0, slot in page, 0), or -1
+#pragma unroll
+      for (int i = 0; i < MAX_ROWS; ++i) {
+        const int m = first + i * stride;
+        pos[i] = 0;
+        slot[i] = -1;
+        if (m < a.m) {
+          pos[i] = a.positions[m];
+          if (region > 0 && a.write_cache) {
+            const int index = pos[i] / a.page_size;
+            const int page = index < a.table_width ? a.table[(size_t)a.request_of_token[m] * a.table_width + index] : -1;
+            if (page < 0 || page >= a.num_pages) {
+              if (lane == 0) atomicOr(a.err ? a.err : &timeout_sink, kErrBadPage);
+            } else {
+              slot[i] = ((long long)page * a.kv_heads * a.page_size + pos[i] % a.page_size) * a.dim;
+            }
+          }
+        }
+      }
+      cluster.sync();
+#pragma unroll
+      for (int i = 0; i < MAX_ROWS; ++i) {
+        const int m = first + i * stride;
+        if (m >= a.m) break;
+        float part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          part[r] = r < size ? cluster.map_shared_rank(out_s, r)[m * (BN + 1) + lane] : 0.f;
+        float v = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) v += part[r];
+        v += bias;
+        float result = v;
+        if (rotary) {
+          float sn, cs;
+          sincosf((float)pos[i] * freq, &sn, &cs);
+          const float other = __shfl_xor_sync(0xffffffffu, v, 16);
+          result = lane < 16 ? v * cs - other * sn : v * cs + other * sn;
+        }
+        const bf16 rounded = __float2bfloat16_rn(result);
+        if (region == 0) {
+          a.q_out[(size_t)m * a.q_stride + head * a.dim + d_out] = rounded;
+        } else if (slot[i] >= 0) {
+          bf16* pool = region == 1 ? a.k_pool : a.v_pool;
+          pool[slot[i] + (long long)head * a.page_size * a.dim + d_out] = rounded;
+        }
+      }
+      cluster.sync();
+    }
+    return;
+  }
   if (a.mode == kOutSiluMul) {
     constexpr int HALF = BN / 2;
     const int c0 = blockIdx.x * HALF, channels = a.n / 2;
@@ -364,7 +451,7 @@ static int launch_variant(const CUtensorMap& w_map, const StreamArgs& a, int spl
     attributes[count].val.programmaticStreamSerializationAllowed = 1;
     ++count;
   }
-  if (a.mode == kOutResidual && splits > 1) {
+  if ((a.mode == kOutResidual || a.mode == kOutRope) && splits > 1) {
     // the K slices of one block of weight rows are one thread-block cluster
     attributes[count].id = cudaLaunchAttributeClusterDimension;
     attributes[count].val.clusterDim.x = 1;
@@ -393,6 +480,26 @@ static int launch(const StreamArgs& a, int splits, cudaStream_t stream) {
   return launch_variant<MT, BN, false>(w_map, a, splits, stream);
 }
 
+// Cuts K into `splits` slices of whole tiles and picks the kernel for the row count.
+static int dispatch(StreamArgs& a, int splits, int block_rows, cudaStream_t s) {
+  const int k_tiles = (a.k + BK - 1) / BK;
+  a.k_per_split = ((k_tiles + splits - 1) / splits) * BK;
+  const int mt = a.m <= 8 ? 1 : a.m <= 16 ? 2 : a.m <= 32 ? 4 : 8;
+  if (block_rows == 32) {
+    if (mt == 1) return launch<1, 32>(a, splits, s);
+    if (mt == 2) return launch<2, 32>(a, splits, s);
+    if (mt == 4) return launch<4, 32>(a, splits, s);
+    return launch<8, 32>(a, splits, s);
+  }
+  if (block_rows == 64) {
+    if (mt == 1) return launch<1, 64>(a, splits, s);
+    if (mt == 2) return launch<2, 64>(a, splits, s);
+    if (mt == 4) return launch<4, 64>(a, splits, s);
+    return launch<8, 64>(a, splits, s);
+  }
+  CIE_FAIL("gemm_stream: block_rows must be 32 or 64, got %d", block_rows);
+}
+
 }  // namespace cie
 
 using namespace cie;
@@ -416,7 +523,7 @@ extern "C" int cie_gemm_stream_ex(const void* x, const float* row_sq, int row_ti
   if (m > 64) CIE_FAIL("gemm_stream: takes at most 64 rows, got %d", m);
   if (k < 8 || k % 8) CIE_FAIL("gemm_stream: K must be a multiple of 8 (16-byte rows), got %d", k);
   if (splits < 1) CIE_FAIL("gemm_stream: splits %d", splits);
-  if (mode < 0 || mode > kOutResidual) CIE_FAIL("gemm_stream: mode %d", mode);
+  if (mode < 0 || mode > kOutResidual) CIE_FAIL("gemm_stream: mode %d (the rotary epilogue has its own entry point)", mode);
   if (mode == kOutSiluMul && (splits != 1 || n % 2)) CIE_FAIL("gemm_stream: the SiLU epilogue needs one split and an even N");
   if (mode == kOutResidual) {
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) CIE_FAIL("gemm_stream: the residual epilogue takes 1, 2, 4 or 8 splits, got %d", splits);
@@ -426,28 +533,45 @@ extern "C" int cie_gemm_stream_ex(const void* x, const float* row_sq, int row_ti
     CIE_FAIL("gemm_stream: %d splits need the partial-sum or the residual output", splits);
   }
   if (row_sq && row_tiles < 1) CIE_FAIL("gemm_stream: %d tiles of sums of squares", row_tiles);
-  StreamArgs a;
+  StreamArgs a = {};
   a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias; a.out = out;
   a.m = m; a.n = n; a.k = k; a.mode = mode; a.err = err;
   a.row_sq = row_sq; a.row_tiles = row_tiles; a.eps = eps;
   a.residual = residual; a.sq = sq; a.scaled = (bf16*)scaled; a.next_gain = next_gain;
-  const int k_tiles = (k + BK - 1) / BK;
-  a.k_per_split = ((k_tiles + splits - 1) / splits) * BK;
-  cudaStream_t s = (cudaStream_t)stream;
-  const int mt = m <= 8 ? 1 : m <= 16 ? 2 : m <= 32 ? 4 : 8;
-  if (block_rows == 32) {
-    if (mt == 1) return launch<1, 32>(a, splits, s);
-    if (mt == 2) return launch<2, 32>(a, splits, s);
-    if (mt == 4) return launch<4, 32>(a, splits, s);
-    return launch<8, 32>(a, splits, s);
-  }
-  if (block_rows == 64) {
-    if (mt == 1) return launch<1, 64>(a, splits, s);
-    if (mt == 2) return launch<2, 64>(a, splits, s);
-    if (mt == 4) return launch<4, 64>(a, splits, s);
-    return launch<8, 64>(a, splits, s);
-  }
-  CIE_FAIL("gemm_stream: block_rows must be 32 or 64, got %d", block_rows);
+  return dispatch(a, splits, block_rows, (cudaStream_t)stream);
+}
+
+// The stacked q/k/v projection of at most 16 decode tokens with the rotary epilogue (mode 5): q is
+// written, rotated, to q_out [M, q_stride]; k (rotated) and v go to the token's slot of the cache
+// pages unless write_cache is 0.  The weight (and bias) rows of q and k heads are in the paired
+// layout; head size and rotary size are multiples of 32; splits is 1, 2, 4 or 8.
+extern "C" int cie_gemm_stream_rope(const void* x, const float* row_sq, int row_tiles, float eps, const void* w,
+                                    const float* bias, void* q_out, int q_stride, const int* positions,
+                                    const int* request_of_token, const int* table, int table_width,
+                                    int num_pages, void* k_pool, void* v_pool, const float* inv_freq, int m,
+                                    int q_heads, int kv_heads, int dim, int rot, int page_size,
+                                    int write_cache, int k, int splits, int* err, void* stream) {
+  if (m <= 0) return 0;
+  if (!x || !w || !q_out || !positions || !inv_freq) CIE_FAIL("gemm_stream_rope: null operand");
+  if (m > 16) CIE_FAIL("gemm_stream_rope: takes at most 16 rows, got %d", m);
+  if (k < 8 || k % 8) CIE_FAIL("gemm_stream_rope: K must be a multiple of 8, got %d", k);
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) CIE_FAIL("gemm_stream_rope: 1, 2, 4 or 8 splits, got %d", splits);
+  if (dim < 32 || dim % 32 || rot < 32 || rot % 32 || rot > dim)
+    CIE_FAIL("gemm_stream_rope: head size %d and rotary size %d must be multiples of 32", dim, rot);
+  if (q_heads < 1 || kv_heads < 1) CIE_FAIL("gemm_stream_rope: %d query and %d kv heads", q_heads, kv_heads);
+  if (write_cache && (!request_of_token || !table || !k_pool || !v_pool || page_size < 1))
+    CIE_FAIL("gemm_stream_rope: the cache write needs the block table and the pools");
+  if (row_sq && row_tiles < 1) CIE_FAIL("gemm_stream_rope: %d tiles of sums of squares", row_tiles);
+  StreamArgs a = {};
+  a.x = (const bf16*)x; a.w = (const bf16*)w; a.bias = bias;
+  a.m = m; a.n = (q_heads + 2 * kv_heads) * dim; a.k = k; a.mode = kOutRope; a.err = err;
+  a.row_sq = row_sq; a.row_tiles = row_tiles; a.eps = eps;
+  a.q_out = (bf16*)q_out; a.q_stride = q_stride; a.positions = positions; a.request_of_token = request_of_token;
+  a.table = table; a.table_width = table_width; a.num_pages = num_pages;
+  a.k_pool = (bf16*)k_pool; a.v_pool = (bf16*)v_pool; a.inv_freq = inv_freq;
+  a.q_heads = q_heads; a.kv_heads = kv_heads; a.dim = dim; a.rot = rot; a.page_size = page_size;
+  a.write_cache = write_cache;
+  return dispatch(a, splits, 32, (cudaStream_t)stream);
 }
 
 // bfloat16 input, modes 0..3.

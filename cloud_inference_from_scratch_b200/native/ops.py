@@ -154,7 +154,7 @@ class Ops:
         self._add_rmsnorm = ew.function("cie_add_rmsnorm", [v, v, i, ll, v, v, v, v, i, i, f, i, v])
         self._rope_kv_write = ew.function(
             "cie_rope_kv_write",
-            [v, i, ll, v, v, i, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, v, v],
+            [v, i, ll, v, v, i, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, i, v, v],
         )
         self._silu_mul = ew.function("cie_silu_mul", [v, v, i, i, i, i, v])
         gs = _Lib(load_library("gemm_simt.cu"))
@@ -169,6 +169,7 @@ class Ops:
         self._tensor_attention: dict[int, Any] = {}
         self._gemm_stream = None
         self._gemm_stream_ex = None
+        self._gemm_stream_rope = None
         self.fuse_norm = False
         self._partial_buffers: dict[str, Any] = {}
         self.scratch_frozen = False
@@ -177,6 +178,9 @@ class Ops:
             self._gemm_stream = st.function("cie_gemm_stream", [v, v, v, v, i, i, i, i, i, i, v, v])
             self._gemm_stream_ex = st.function(
                 "cie_gemm_stream_ex", [v, v, i, f, v, v, v, v, v, v, v, i, i, i, i, i, i, v, v])
+            self._gemm_stream_rope = st.function(
+                "cie_gemm_stream_rope",
+                [v, v, i, f, v, v, v, i, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, i, v, v])
             self.fuse_norm = os.environ.get("CIE_FUSE_NORM", "1") != "0"
         if self.code == BF16 and self.gemm_mode == "tensor":
             from .tensor_gemm import TensorGemm
@@ -407,10 +411,11 @@ class Ops:
 
     def rope_kv_write(self, qkv: Any, ctx: Any, kv: Any, position: Any, q_heads: int,
                       kv_heads: int, head_dim: int, write_cache: bool = True,
-                      q_buffer: Any = None) -> Any:
+                      q_buffer: Any = None, paired: bool = False) -> Any:
         """Rotates q and k, writes k and v into the pages; returns the tensor that holds the
         rotated q (head h of token t at [t, h * head_dim]).  ``qkv`` is a tensor (q is rotated in
-        place) or ``Partials`` (then q goes to ``q_buffer``)."""
+        place) or ``Partials`` (then q goes to ``q_buffer``).  ``paired``: the q and k columns of
+        ``qkv`` are in the paired layout of ``pair_rotary_rows``; q then always goes to ``q_buffer``."""
         rot = position.rotary_dim if position is not None else 0
         inv_freq = position.inv_freq if position is not None else None
         table = ctx.block_tables[kv.group]
@@ -427,13 +432,69 @@ class Ops:
             tokens = qkv.shape[0]
             src, splits, stride, bias = qkv, 0, 0, None
             target = qkv
+        if paired:
+            if q_buffer is None:
+                raise KernelError("rope_kv_write: the paired layout needs a q buffer")
+            target = q_buffer
         self._rope_kv_write(_ptr(src), splits, stride, _ptr(bias), _ptr(target), target.shape[1],
                             _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
                             table.shape[1], kv.num_pages, _ptr(kv.k), _ptr(kv.v), _ptr(inv_freq),
                             tokens, q_heads, kv_heads, head_dim, rot, kv.page_size,
-                            1 if write_cache else 0, self._code_of(target), _ptr(self.error_word),
-                            self.stream)
+                            1 if write_cache else 0, 1 if paired else 0, self._code_of(target),
+                            _ptr(self.error_word), self.stream)
         return target
+
+    # ------------------------------------------------------------------ rotary epilogue of the q/k/v product
+    def can_pair_rotary(self, head_dim: int, rotary_dim: int) -> bool:
+        """Whether the stacked q/k/v weight of an attention layer may be kept in the paired
+        layout, which lets a decode step rotate and store inside the projection's own kernel."""
+        return (self._gemm_stream_rope is not None and os.environ.get("CIE_FUSE_ROPE", "1") != "0"
+                and head_dim % 32 == 0 and rotary_dim % 32 == 0 and 32 <= rotary_dim <= head_dim)
+
+    def pair_rotary_rows(self, rows: Any, heads: int, head_dim: int, rotary_dim: int) -> Any:
+        """Rows [heads * head_dim, ...] of a q or k projection (weight or bias) in the paired
+        layout: inside every head, blocks of 16 rotary elements followed by their 16 partners."""
+        torch = self.torch
+        half = rotary_dim // 2
+        order = torch.empty(head_dim, dtype=torch.long)
+        for d in range(head_dim):
+            if d >= rotary_dim:
+                column = d
+            elif d < half:
+                column = (d // 16) * 32 + d % 16
+            else:
+                column = ((d - half) // 16) * 32 + 16 + (d - half) % 16
+            order[column] = d
+        index = (torch.arange(heads).view(-1, 1) * head_dim + order.view(1, -1)).reshape(-1).to(rows.device)
+        return rows.index_select(0, index).contiguous()
+
+    def qkv_rope(self, x: Any, weight: Any, bias: Any, ctx: Any, kv: Any, position: Any, q_heads: int,
+                 kv_heads: int, head_dim: int, write_cache: bool, q_buffer: Any) -> Any:
+        """The stacked q/k/v projection (paired layout) of a few decode tokens, rotated and stored
+        by the product's own kernel; returns ``q_buffer``, or None when the shape is not its kind
+        (the caller then runs the product and ``rope_kv_write(..., paired=True)``)."""
+        m, k = x.shape
+        n = weight.shape[0]
+        if (self._gemm_stream_rope is None or position is None or m > FUSED_RESIDUAL_MAX_ROWS
+                or self.stream_plan(m, n, k, True) is None
+                or not self.can_pair_rotary(head_dim, position.rotary_dim)):
+            return None
+        tiles, k_tiles = -(-n // 32), -(-k // 128)
+        splits = 8
+        while splits > 1 and (tiles * splits > 5 * SM_COUNT or k_tiles // splits < 2):
+            splits //= 2
+        row_sq, row_tiles, eps = None, 0, 0.0
+        if isinstance(x, NormedInput):
+            row_sq, row_tiles, eps, x = x.accumulated.sq, x.accumulated.tiles, x.eps, x.accumulated.scaled
+        table = ctx.block_tables[kv.group]
+        self.launches += 1
+        self._gemm_stream_rope(_ptr(x), _ptr(row_sq), row_tiles, eps, _ptr(weight), _ptr(bias),
+                               _ptr(q_buffer), q_buffer.shape[1], _ptr(ctx.positions),
+                               _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages,
+                               _ptr(kv.k), _ptr(kv.v), _ptr(position.inv_freq), m, q_heads, kv_heads,
+                               head_dim, position.rotary_dim, kv.page_size, 1 if write_cache else 0, k,
+                               splits, _ptr(self.error_word), self.stream)
+        return q_buffer
 
     def attention(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
                   head_dim: int, scale: float, window: int) -> None:

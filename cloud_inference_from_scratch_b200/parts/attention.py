@@ -75,14 +75,23 @@ class Attention(Mixer):
         import torch
 
         self.runtime = runtime
-        self.w_qkv = runtime.ops.prepare_weight(
-            torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]])
-        )
-        self.b_qkv = (
-            torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]).contiguous()
-            if self.qkv_bias
-            else None
-        )
+        ops = runtime.ops
+        # With a rotary encoding whose sizes allow it, the q and k rows are kept in the paired
+        # layout: a decode step then rotates and stores inside the projection's kernel, and the
+        # separate rotary kernel (prompt portions) reads the same layout.
+        rotary = self.position.rotary_dim if self.position is not None else 0
+        self.paired = bool(self.position is not None and getattr(ops, "can_pair_rotary", None)
+                           and ops.can_pair_rotary(self.head_dim, rotary))
+
+        def stacked(suffix):
+            q, k, v = (tensors[f"{name}_proj.{suffix}"] for name in "qkv")
+            if self.paired:
+                q = ops.pair_rotary_rows(q, self.num_heads, self.head_dim, rotary)
+                k = ops.pair_rotary_rows(k, self.num_kv_heads, self.head_dim, rotary)
+            return torch.cat([q, k, v]).contiguous()
+
+        self.w_qkv = ops.prepare_weight(stacked("weight"))
+        self.b_qkv = stacked("bias") if self.qkv_bias else None
         self.w_o = runtime.ops.prepare_weight(tensors["o_proj.weight"])
         if self.position is not None:
             self.position.bind({}, runtime)
@@ -93,16 +102,21 @@ class Attention(Mixer):
     def forward(self, x, ctx, binding):
         rt = self.runtime
         tokens = x.shape[0]
-        qkv = rt.workspace.get("attention.qkv", tokens, self.qkv_width, rt.dtype)
-        # for few tokens the projection may come back as partial sums that the next kernel adds up
-        qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, allow_partials=True, tag="attention.qkv",
-                            defer_bias=True)
         kv = binding.kv
-        q = rt.ops.rope_kv_write(
-            qkv, ctx, kv, self.position, self.num_heads, self.num_kv_heads, self.head_dim,
-            write_cache=binding.owns_cache,
-            q_buffer=rt.workspace.get("attention.q", tokens, self.q_width, rt.dtype),
-        )
+        q_buffer = rt.workspace.get("attention.q", tokens, self.q_width, rt.dtype)
+        q = None
+        if self.paired:   # a few decode tokens: projection, rotation and cache write in one kernel
+            q = rt.ops.qkv_rope(x, self.w_qkv, self.b_qkv, ctx, kv, self.position, self.num_heads,
+                                self.num_kv_heads, self.head_dim, binding.owns_cache, q_buffer)
+        if q is None:
+            qkv = rt.workspace.get("attention.qkv", tokens, self.qkv_width, rt.dtype)
+            # for few tokens the projection may come back as partial sums that the next kernel adds up
+            qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, allow_partials=True, tag="attention.qkv",
+                                defer_bias=True)
+            q = rt.ops.rope_kv_write(
+                qkv, ctx, kv, self.position, self.num_heads, self.num_kv_heads, self.head_dim,
+                write_cache=binding.owns_cache, q_buffer=q_buffer, paired=self.paired,
+            )
         mixed = rt.workspace.get("attention.out", tokens, self.q_width, rt.dtype)
         rt.ops.attention(
             q, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,

@@ -615,3 +615,115 @@ def test_a_projection_of_more_rows_leaves_the_sum_to_the_norm(ops):
     assert not isinstance(got, Accumulated)
     torch.cuda.synchronize()
     assert torch.equal(residual, before)
+
+
+# ------------------------------------------------------------------ rotary epilogue of the q/k/v product
+def paired_projection(item, q_heads, kv_heads, dim, rot, hidden, seed):
+    """A stacked q/k/v weight and bias, natural and in the paired layout."""
+    width = (q_heads + 2 * kv_heads) * dim
+    w = rand(width, hidden, dtype=torch.bfloat16, scale=0.03, seed=seed)
+    bias = rand(width, seed=seed + 1)
+    q_rows, k_rows = q_heads * dim, kv_heads * dim
+
+    def pair(t):
+        return torch.cat([item.pair_rotary_rows(t[:q_rows], q_heads, dim, rot),
+                          item.pair_rotary_rows(t[q_rows:q_rows + k_rows], kv_heads, dim, rot),
+                          t[q_rows + k_rows:]]).contiguous()
+
+    return w, bias, pair(w), pair(bias)
+
+
+def rotary_want(x, w, bias, positions, q_heads, kv_heads, dim, rot, theta):
+    tokens = x.shape[0]
+    full = plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).view(tokens, -1, dim)
+    cos, sin = plain_model.rope_tables(rot, positions.cpu().tolist(), theta)
+    return (plain_model.apply_rope(full[:, :q_heads], cos, sin),
+            plain_model.apply_rope(full[:, q_heads:q_heads + kv_heads], cos, sin),
+            full[:, q_heads + kv_heads:])
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,dim,rot,page", [(16, 2, 128, 128, 16), (6, 3, 64, 32, 8), (4, 4, 96, 64, 32)])
+@pytest.mark.parametrize("tokens", [1, 5, 8])
+def test_qkv_projection_rotates_and_stores_in_its_own_kernel(ops, q_heads, kv_heads, dim, rot, page, tokens):
+    """Decode tokens: q comes back rotated in the natural order, k and v land in the right slot of
+    the right page, nothing else in the pools changes; with write_cache off the pools stay as
+    they were.  The same paired weight through the separate rotary kernel gives the same."""
+    item = ops[torch.bfloat16]
+    hidden, theta = 1024, 1e6
+    assert item.can_pair_rotary(dim, rot)
+    w, bias, w_paired, bias_paired = paired_projection(item, q_heads, kv_heads, dim, rot, hidden, seed=tokens)
+    x = rand(tokens, hidden, dtype=torch.bfloat16, seed=9)
+    lengths = [1, 8, 16, 17, 301, 64, 33, 100][:tokens]
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32).cuda()
+    request = torch.arange(tokens, dtype=torch.int32).cuda()
+    k_pool, v_pool, table, _, total = paged_setup(lengths, page, kv_heads, dim, torch.bfloat16)
+    before_k, before_v = k_pool.clone(), v_pool.clone()
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).cuda()
+    position = SimpleNamespace(rotary_dim=rot, inv_freq=inv_freq)
+    ctx = SimpleNamespace(positions=positions, request_of_token=request, block_tables=[table])
+    kv = SimpleNamespace(group=0, k=k_pool, v=v_pool, num_pages=total, page_size=page)
+    want_q, want_k, want_v = rotary_want(x, w, bias, positions, q_heads, kv_heads, dim, rot, theta)
+
+    q_buffer = torch.zeros(tokens, q_heads * dim, dtype=torch.bfloat16).cuda()
+    got = item.qkv_rope(x, w_paired, bias_paired, ctx, kv, position, q_heads, kv_heads, dim, True, q_buffer)
+    assert got is q_buffer
+    torch.cuda.synchronize()
+    torch.testing.assert_close(q_buffer.float().cpu().view(tokens, q_heads, dim), want_q, rtol=2e-2, atol=2e-2)
+    touched = torch.zeros_like(k_pool, dtype=torch.bool)
+    for t in range(tokens):
+        pos = int(positions[t])
+        page_id = int(table[t, pos // page])
+        torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(v_pool[page_id, :, pos % page].float().cpu(), want_v[t], rtol=2e-2, atol=2e-2)
+        touched[page_id, :, pos % page] = True
+    assert torch.equal(k_pool[~touched], before_k[~touched])
+    assert torch.equal(v_pool[~touched], before_v[~touched])
+
+    # a layer that reads another layer's cache writes nothing
+    k2, v2 = before_k.clone(), before_v.clone()
+    kv2 = SimpleNamespace(group=0, k=k2, v=v2, num_pages=total, page_size=page)
+    q2 = torch.zeros_like(q_buffer)
+    item.qkv_rope(x, w_paired, bias_paired, ctx, kv2, position, q_heads, kv_heads, dim, False, q2)
+    torch.cuda.synchronize()
+    assert torch.equal(k2, before_k) and torch.equal(v2, before_v) and torch.equal(q2, q_buffer)
+
+    # the separate kernel on the same paired layout (as prompt portions use it)
+    k3, v3 = before_k.clone(), before_v.clone()
+    kv3 = SimpleNamespace(group=0, k=k3, v=v3, num_pages=total, page_size=page)
+    qkv = torch.empty(tokens, w.shape[0], dtype=torch.bfloat16).cuda()
+    qkv = item.linear(x, w_paired, bias_paired, qkv, allow_partials=True, tag="pairedrope", defer_bias=True)
+    q3 = item.rope_kv_write(qkv, ctx, kv3, position, q_heads, kv_heads, dim, q_buffer=torch.zeros_like(q_buffer),
+                            paired=True)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(q3.float().cpu().view(tokens, q_heads, dim), want_q, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(k3.float(), k_pool.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(v3.float(), v_pool.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_paired_rotary_kernel_on_a_prompt_portion(ops):
+    """Many tokens: the library product leaves q/k/v in the paired layout in the compute dtype with
+    the bias still to add; the rotary kernel reads it and writes q in the natural order."""
+    item = ops[torch.bfloat16]
+    q_heads, kv_heads, dim, rot, page, hidden, theta = 14, 2, 64, 64, 16, 896, 1e6
+    w, bias, w_paired, bias_paired = paired_projection(item, q_heads, kv_heads, dim, rot, hidden, seed=21)
+    tokens = 150
+    x = rand(tokens, hidden, dtype=torch.bfloat16, seed=22)
+    positions = torch.arange(40, 40 + tokens, dtype=torch.int32).cuda()
+    request = torch.zeros(tokens, dtype=torch.int32).cuda()
+    k_pool, v_pool, table, _, total = paged_setup([40 + tokens], page, kv_heads, dim, torch.bfloat16)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).cuda()
+    position = SimpleNamespace(rotary_dim=rot, inv_freq=inv_freq)
+    ctx = SimpleNamespace(positions=positions, request_of_token=request, block_tables=[table])
+    kv = SimpleNamespace(group=0, k=k_pool, v=v_pool, num_pages=total, page_size=page)
+    qkv = torch.empty(tokens, w.shape[0], dtype=torch.bfloat16).cuda()
+    qkv = item.linear(x, w_paired, bias_paired, qkv, allow_partials=True, tag="pairedprompt", defer_bias=True)
+    q = item.rope_kv_write(qkv, ctx, kv, position, q_heads, kv_heads, dim,
+                           q_buffer=torch.zeros(tokens, q_heads * dim, dtype=torch.bfloat16).cuda(), paired=True)
+    torch.cuda.synchronize()
+    want_q, want_k, want_v = rotary_want(x, w, bias, positions, q_heads, kv_heads, dim, rot, theta)
+    torch.testing.assert_close(q.float().cpu().view(tokens, q_heads, dim), want_q, rtol=2e-2, atol=2e-2)
+    for t in (0, 7, 149):
+        pos = int(positions[t])
+        page_id = int(table[0, pos // page])
+        torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(v_pool[page_id, :, pos % page].float().cpu(), want_v[t], rtol=2e-2, atol=2e-2)
