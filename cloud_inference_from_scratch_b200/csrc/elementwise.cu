@@ -116,6 +116,56 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const void* __r
   }
 }
 
+// The same for bfloat16 rows whose length is a multiple of 8, with a plain update or none: a thread
+// owns 8 neighbouring elements (two 16-byte loads of the residual, one of the update), keeps them
+// in registers across the reduction and writes them back the same way.  Up to 8192 elements a row.
+__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __nv_bfloat16* __restrict__ update,
+                                          const float* __restrict__ gain, __nv_bfloat16* __restrict__ out,
+                                          const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();   // see add_rmsnorm_kernel
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const int i = threadIdx.x * 8;
+  const bool active = i < hidden;
+  float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (active) {
+    const float4* res = reinterpret_cast<const float4*>(residual + (size_t)src * hidden + i);
+    const float4 lo = res[0], hi = res[1];
+    x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w; x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+    if (update) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(update + (size_t)src * hidden + i);
+      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 u = __bfloat1622float2(pairs[j]);
+        x[2 * j] += u.x;
+        x[2 * j + 1] += u.y;
+      }
+    }
+  }
+  float sumsq = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sumsq += x[j] * x[j];
+  const float total = block_sum(sumsq, scratch);
+  const float inv = rsqrtf(total / (float)hidden + eps);
+  if (!active) return;
+  if (update && !rows) {
+    float4* res = reinterpret_cast<float4*>(residual + (size_t)src * hidden + i);
+    res[0] = make_float4(x[0], x[1], x[2], x[3]);
+    res[1] = make_float4(x[4], x[5], x[6], x[7]);
+  }
+  const float4 g0 = *reinterpret_cast<const float4*>(gain + i), g1 = *reinterpret_cast<const float4*>(gain + i + 4);
+  const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+  uint4 packed;
+  __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    pairs[j] = __floats2bfloat162_rn(g[2 * j] * (x[2 * j] * inv), g[2 * j + 1] * (x[2 * j + 1] * inv));
+  *reinterpret_cast<uint4*>(out + (size_t)r * hidden + i) = packed;
+}
+
 // ---------------------------------------------------------------- rotary + paged KV write
 // qkv: [T, (Hq + 2 Hkv) * D], q heads first, then k heads, then v heads.  q is rotated in place.
 // k is rotated and written, v is copied, to pool[page][kv_head][pos % page][D] with
@@ -220,6 +270,125 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
   }
 }
 
+// The same for bfloat16 rows that are already summed (many tokens: the library product wrote them),
+// with rot a multiple of 16 and head size a multiple of 8: a thread owns 8 neighbouring rotary
+// pairs (16-byte loads of both halves), computes their sines and cosines once and walks over the
+// heads; values are copied 16 bytes at a time.  q_out may be the source itself only in the natural
+// layout (a thread reads both of its 16-byte pieces before it writes them).
+__global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ bias,
+                                            __nv_bfloat16* __restrict__ q_out, int q_stride,
+                                            const int* __restrict__ positions,
+                                            const int* __restrict__ request_of_token,
+                                            const int* __restrict__ table, int table_width, int num_pages,
+                                            __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
+                                            const float* __restrict__ inv_freq, int q_heads, int kv_heads,
+                                            int dim, int rot, int page_size, int write_cache, int paired,
+                                            int* err) {
+  pdl_wait();
+  pdl_trigger();
+  using bf16 = __nv_bfloat16;
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int width = (q_heads + 2 * kv_heads) * dim;
+  const bf16* row = src + (size_t)t * width;
+  bf16* q_row = q_out + (size_t)t * q_stride;
+  const bool out_of_place = q_out != src;
+  const int half = rot / 2;
+
+  long long slot_base = -1;
+  if (write_cache) {
+    const int request = request_of_token[t];
+    const int index = pos / page_size;
+    const int page = index < table_width ? table[(size_t)request * table_width + index] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, kErrBadPage);
+    } else {
+      slot_base = ((long long)page * kv_heads * page_size + pos % page_size) * dim;
+    }
+  }
+  const long long head_stride = (long long)page_size * dim;
+
+  auto load8 = [&](int column, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + column);
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(pairs[j]);
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+    if (bias) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += bias[column + j];
+    }
+  };
+  auto store8 = [&](bf16* dst, const float (&v)[8]) {
+    uint4 packed;
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pairs[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    *reinterpret_cast<uint4*>(dst) = packed;
+  };
+
+  // rotary pairs: chunk c holds pairs 8c .. 8c+7 of a head; a thread keeps one chunk and walks heads
+  const int chunks = half / 8;
+  const int rot_heads = q_heads + kv_heads;
+  if (chunks > 0) {
+    const int lanes = max(1, (int)blockDim.x / chunks);
+    if ((int)threadIdx.x < lanes * chunks) {
+      const int c = threadIdx.x % chunks, first_head = threadIdx.x / chunks;
+      float sn[8], cs[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sincosf((float)pos * inv_freq[c * 8 + j], &sn[j], &cs[j]);
+      // where the two halves of this chunk stand inside a head
+      const int col_a = paired ? paired_column(c * 8, rot) : c * 8;
+      const int col_b = paired ? paired_column(c * 8 + half, rot) : c * 8 + half;
+      for (int h = first_head; h < rot_heads; h += lanes) {
+        float a[8], b[8], ra[8], rb[8];
+        load8(h * dim + col_a, a);
+        load8(h * dim + col_b, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ra[j] = a[j] * cs[j] - b[j] * sn[j];
+          rb[j] = b[j] * cs[j] + a[j] * sn[j];
+        }
+        if (h < q_heads) {
+          store8(q_row + h * dim + c * 8, ra);
+          store8(q_row + h * dim + c * 8 + half, rb);
+        } else if (slot_base >= 0) {
+          bf16* dst = k_pool + slot_base + (long long)(h - q_heads) * head_stride;
+          store8(dst + c * 8, ra);
+          store8(dst + c * 8 + half, rb);
+        }
+      }
+    }
+  }
+  // what lies beyond the rotary dims passes through; values are copied
+  const int tail_chunks = (dim - rot) / 8;
+  if (tail_chunks > 0 && (bias || out_of_place)) {
+    for (int i = threadIdx.x; i < q_heads * tail_chunks; i += blockDim.x) {
+      const int h = i / tail_chunks, d = rot + (i % tail_chunks) * 8;
+      float v[8];
+      load8(h * dim + d, v);
+      store8(q_row + h * dim + d, v);
+    }
+  }
+  if (slot_base < 0) return;
+  for (int i = threadIdx.x; i < kv_heads * tail_chunks; i += blockDim.x) {
+    const int h = i / tail_chunks, d = rot + (i % tail_chunks) * 8;
+    float v[8];
+    load8((q_heads + h) * dim + d, v);
+    store8(k_pool + slot_base + h * head_stride + d, v);
+  }
+  const int value_chunks = dim / 8;
+  for (int i = threadIdx.x; i < kv_heads * value_chunks; i += blockDim.x) {
+    const int h = i / value_chunks, d = (i % value_chunks) * 8;
+    float v[8];
+    load8((q_heads + kv_heads + h) * dim + d, v);
+    store8(v_pool + slot_base + h * head_stride + d, v);
+  }
+}
+
 // ---------------------------------------------------------------- SiLU(gate) * up
 // gate_up: [T, 2 * inter] where channel c has its gate at column (c / block) * 2 * block + c % block
 // and its up value `block` columns further (block == inter: all gates first, then all ups).
@@ -261,7 +430,10 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-      o2[j] = __floats2bfloat162_rn((g.x / (1.f + expf(-g.x))) * u.x, (g.y / (1.f + expf(-g.y))) * u.y);
+      // the result is rounded to bfloat16: the fast exponential and division (a few ulp of
+      // float32) cost a third of the instructions of the exact ones, which bound this kernel
+      o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x,
+                                    __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
     }
     *reinterpret_cast<uint4*>(out + t * inter + c) = packed;
   }
@@ -298,6 +470,14 @@ extern "C" int cie_add_rmsnorm(float* residual, const void* update, int partial_
                                float eps, int dtype, void* stream) {
   if (count <= 0) return 0;
   if (partial_splits > kMaxSplits) CIE_FAIL("add_rmsnorm: at most %d partial sums, got %d", kMaxSplits, partial_splits);
+  if (dtype == kBFloat16 && partial_splits == 0 && !update_bias && hidden % 8 == 0 && hidden <= 8192 &&
+      ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(update) | reinterpret_cast<uintptr_t>(gain) |
+        reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    const int threads = (hidden / 8 + 31) / 32 * 32;
+    CIE_LAUNCH("add_rmsnorm", add_rmsnorm_bf16x8_kernel, dim3(count), dim3(threads), 0, (cudaStream_t)stream, residual,
+               (const __nv_bfloat16*)update, gain, (__nv_bfloat16*)out, rows, hidden, eps);
+    return 0;
+  }
   DISPATCH_DTYPE(dtype, "add_rmsnorm", {
     CIE_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, dim3(count), dim3(threads_for(hidden / 4)), 0,
                (cudaStream_t)stream, residual, update, partial_splits, (size_t)partial_stride,
@@ -317,6 +497,16 @@ extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long 
   if (rot % 2 || rot > dim || rot < 0) CIE_FAIL("rope_kv_write: rotary size %d does not fit head size %d", rot, dim);
   if (paired && (rot % 32 || q_out == src)) CIE_FAIL("rope_kv_write: the paired layout needs a rotary size that is a multiple of 32 and a q buffer of its own");
   if (partial_splits > kMaxSplits) CIE_FAIL("rope_kv_write: at most %d partial sums, got %d", kMaxSplits, partial_splits);
+  if (dtype == kBFloat16 && partial_splits == 0 && tokens > 64 && rot >= 16 && rot % 16 == 0 && dim % 8 == 0 &&
+      q_stride % 8 == 0 &&
+      ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pool) |
+        reinterpret_cast<uintptr_t>(v_pool)) & 15) == 0) {
+    CIE_LAUNCH("rope_kv_write", rope_kv_write_bf16x8_kernel, dim3(tokens), dim3(128), 0, (cudaStream_t)stream,
+               (const __nv_bfloat16*)src, bias, (__nv_bfloat16*)q_out, q_stride, positions, request_of_token, table,
+               table_width, num_pages, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, inv_freq, q_heads, kv_heads,
+               dim, rot, page_size, write_cache, paired, err);
+    return 0;
+  }
   DISPATCH_DTYPE(dtype, "rope_kv_write", {
     const int work = (q_heads + kv_heads) * (rot / 2) > kv_heads * dim ? (q_heads + kv_heads) * (rot / 2) : kv_heads * dim;
     // few tokens: spread one token over many threads; many tokens: fewer threads that each reuse

@@ -727,3 +727,39 @@ def test_paired_rotary_kernel_on_a_prompt_portion(ops):
         page_id = int(table[0, pos // page])
         torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(v_pool[page_id, :, pos % page].float().cpu(), want_v[t], rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dim,rot,page", [(128, 128, 16), (128, 64, 16), (48, 16, 4), (64, 32, 32)])
+def test_rope_kv_write_many_tokens_in_place(ops, dim, rot, page):
+    """More than 64 bfloat16 tokens take the 16-byte-wide kernel: q rotated in place (natural
+    layout), the part of a head beyond the rotary dims untouched, k and v in their slots."""
+    q_heads, kv_heads = 5, 2
+    starts, lens = [3, 0], [90, 33]
+    width = (q_heads + 2 * kv_heads) * dim
+    tokens = sum(lens)
+    qkv = rand(tokens, width, dtype=torch.bfloat16, seed=31)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).int().cuda()
+    request = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().cuda()
+    k_pool, v_pool, table, _, total = paged_setup([s + n for s, n in zip(starts, lens)], page, kv_heads, dim, torch.bfloat16)
+    theta = 10000.0
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).cuda()
+    ctx = SimpleNamespace(positions=positions, request_of_token=request, block_tables=[table])
+    kv = SimpleNamespace(group=0, k=k_pool, v=v_pool, num_pages=total, page_size=page)
+    original = qkv.clone()
+    got = ops[torch.bfloat16].rope_kv_write(qkv, ctx, kv, SimpleNamespace(rotary_dim=rot, inv_freq=inv_freq),
+                                            q_heads, kv_heads, dim)
+    assert got is qkv
+    torch.cuda.synchronize()
+    src = original.float().cpu().view(tokens, q_heads + 2 * kv_heads, dim)
+    cos, sin = plain_model.rope_tables(rot, positions.cpu().tolist(), theta)
+    want_q = plain_model.apply_rope(src[:, :q_heads], cos, sin)
+    want_k = plain_model.apply_rope(src[:, q_heads:q_heads + kv_heads], cos, sin)
+    out = qkv.float().cpu().view(tokens, q_heads + 2 * kv_heads, dim)
+    torch.testing.assert_close(out[:, :q_heads], want_q, **tol(torch.bfloat16))
+    assert torch.equal(out[:, :q_heads, rot:], src[:, :q_heads, rot:])
+    assert torch.equal(out[:, q_heads:], src[:, q_heads:])
+    for t in range(tokens):
+        r, pos = int(request[t]), int(positions[t])
+        page_id = int(table[r, pos // page])
+        torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], **tol(torch.bfloat16))
+        assert torch.equal(v_pool[page_id, :, pos % page].float().cpu(), src[t, q_heads + kv_heads:])
