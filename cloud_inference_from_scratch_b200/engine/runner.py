@@ -67,6 +67,8 @@ class EngineRunner:
         self.ops.error_word = self.result_dev[0:1]
         has_state = any(need.state is not None for need in core.model.cache_needs())
         self.use_graphs = bool(config.cuda_graph_decode) and not has_state
+        if self.use_graphs:
+            core.step.enable_graphs(config.max_model_len)
         self.table_width = -(-config.max_model_len // core.page_size)
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self._parity = 0
@@ -161,9 +163,8 @@ class EngineRunner:
             host, _, spans = step.prepare(entries)
         rows = len(sampled)
         host.extras["sampling"] = self._sampling_arrays(sampled, rows)
-        ctx = step.upload(host)
         self.ops.error_word = self.result_dev[0:1]
-        logits = self.core.model.forward(ctx)
+        ctx, logits = step.forward_host(host)
         with nvtx_range("ragged.kv.commit"):
             self.core.cache.commit_lengths({rid: end for rid, (_, end) in spans.items()})
         step.steps_run += 1

@@ -20,6 +20,7 @@ class Workspace:
         self.max_rows = int(max_rows)
         self._buffers: dict[tuple[str, int, Any], Any] = {}
         self.frozen = False
+        self.generation = 0   # counts buffers that were replaced by larger ones (their old address died)
 
     def get(self, tag: str, rows: int, width: int, dtype: Any) -> Any:
         import torch
@@ -27,11 +28,13 @@ class Workspace:
         key = (tag, int(width), dtype)
         buffer = self._buffers.get(key)
         if buffer is None or buffer.shape[0] < rows:
-            if self.frozen:
+            if self.frozen and buffer is not None:   # a new buffer harms no graph; a moved one would
                 raise RuntimeError(
                     f"workspace buffer {tag!r} would have to grow to {rows} rows while a CUDA "
                     "graph that uses it is alive"
                 )
+            if buffer is not None:
+                self.generation += 1
             capacity = max(rows, self.max_rows, 1)
             buffer = torch.empty((capacity, int(width)), dtype=dtype, device=self.device)
             self._buffers[key] = buffer

@@ -18,6 +18,8 @@ pads (engine.py:320-356).
 
 from __future__ import annotations
 
+from collections import OrderedDict
+
 from collections.abc import Hashable, Sequence
 from dataclasses import dataclass, field
 from typing import Any
@@ -120,6 +122,18 @@ class MetadataBuffer:
         ]
 
 
+class _StepGraph:
+    """One captured forward pass for one shape of step: its own metadata buffer, whose device
+    addresses the captured kernels hold, and the logits it leaves."""
+
+    def __init__(self, meta: MetadataBuffer, graph: Any, logits: Any, stamp: Any) -> None:
+        self.meta, self.graph, self.logits, self.stamp = meta, graph, logits, stamp
+
+
+MAX_STEP_GRAPHS = 8          # captured shapes kept (least recently used goes first)
+CAPTURE_AT_OCCURRENCE = 2    # a shape is captured when it is seen for the second time
+
+
 class StepFunction:
     def __init__(self, model: Any, runtime: Any, cache: CacheManager, pools: Any) -> None:
         self.model = model
@@ -133,6 +147,16 @@ class StepFunction:
         self.steps_run = 0
         self.tokens_run = 0
         self.h2d_bytes = 0
+        # CUDA graphs by shape of step (the lengths of the requests' portions, the number of
+        # wanted rows, the sizes of every metadata array): a prompt portion of a common length is
+        # many hundred kernel launches that the host would otherwise issue one by one, slower
+        # than the device runs them.  Off until ``enable_graphs`` is called.
+        self.graphs_enabled = False
+        self.fixed_table_width: int | None = None   # block-table columns of every step, if set
+        self._graphs: "OrderedDict[Any, _StepGraph]" = OrderedDict()
+        self._seen: dict[Any, int] = {}
+        self.graph_captures = 0
+        self.graph_replays = 0
 
     def _collect_planners(self) -> dict[Any, Any]:
         """Mixers may add integer work lists of their own to a step's metadata: a mixer with
@@ -143,6 +167,13 @@ class StepFunction:
             if key is not None and key not in planners:
                 planners[key] = layer.mixer
         return planners
+
+    def enable_graphs(self, max_model_len: int) -> None:
+        """Steps of a shape seen before run from a captured CUDA graph.  Block tables of such
+        steps always have the columns of the longest request the engine admits, so that the
+        shape does not depend on how long the requests have grown."""
+        self.graphs_enabled = True
+        self.fixed_table_width = -(-int(max_model_len) // self.cache.page_size)
 
     # ------------------------------------------------------------------ admission
     def admit(self, request_id: Hashable) -> int:
@@ -268,6 +299,8 @@ class StepFunction:
                 ) -> tuple[HostBatch, list[tuple[Hashable, int]], dict[Hashable, tuple[int, int]]]:
         """Everything that can fail on the host: checks the entries, grows the tables
         (``CacheCapacityFull`` leaves the cache untouched) and builds the host arrays."""
+        if table_width is None:
+            table_width = self.fixed_table_width
         host, rows, spans = self.build_host_batch(entries, table_width)
         self.cache.ensure_capacity_batch(spans)
         dirty = self.cache.take_dirty_slots()
@@ -276,12 +309,65 @@ class StepFunction:
         self._fill_tables(host, spans)
         return host, rows, spans
 
+    def _graph_key(self, host: HostBatch) -> Any:
+        extras = tuple((key, name, array.shape) for key, arrays in host.extras.items()
+                       for name, array in arrays.items())
+        return (tuple(host.query_lens.tolist()), int(host.logit_rows.shape[0]),
+                tuple(table.shape for table in host.tables), extras,
+                self.runtime.ops.error_word.data_ptr())
+
+    def _buffer_stamp(self) -> tuple[int, int]:
+        return (self.runtime.workspace.generation, self.runtime.ops.scratch_generation)
+
+    def forward_host(self, host: HostBatch) -> tuple[StepContext, Any]:
+        """Uploads the step's metadata and runs the model on it: from the captured graph of this
+        shape of step if there is one, else kernel by kernel (and, the second time a shape comes
+        by, capturing it).  Returns the context and the logits (None if no row was wanted)."""
+        if not self.graphs_enabled:
+            ctx = self.upload(host)
+            return ctx, self.model.forward(ctx)
+        key = self._graph_key(host)
+        held = self._graphs.get(key)
+        if held is not None and held.stamp != self._buffer_stamp():
+            # a workspace or scratch buffer has been replaced by a larger one since the capture:
+            # the graph holds the address of the old one
+            del self._graphs[key]
+            held = None
+        if held is not None:
+            self._graphs.move_to_end(key)
+            ctx = self.upload(host, held.meta)
+            held.graph.replay()
+            self.graph_replays += 1
+            return ctx, held.logits
+        seen = self._seen.get(key, 0) + 1
+        if len(self._seen) > 4096:
+            self._seen.clear()
+        self._seen[key] = seen
+        if seen < CAPTURE_AT_OCCURRENCE:
+            ctx = self.upload(host)
+            return ctx, self.model.forward(ctx)
+        import torch
+
+        meta = MetadataBuffer(self.runtime.device, words=1 << 10)
+        ctx = self.upload(host, meta)
+        torch.cuda.synchronize()
+        # the same shape ran kernel by kernel before, so every buffer it needs exists; should one be
+        # replaced later, the stamp tells (see above)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        graph.replay()
+        self.graph_captures += 1
+        self._graphs[key] = _StepGraph(meta, graph, logits, self._buffer_stamp())
+        while len(self._graphs) > MAX_STEP_GRAPHS:
+            self._graphs.popitem(last=False)
+        return ctx, logits
+
     def run(self, entries: Sequence[StepEntry]) -> StepResult:
         if not entries:
             return StepResult(None, [])
         host, rows, spans = self.prepare(entries)
-        ctx = self.upload(host)
-        logits = self.model.forward(ctx)
+        _, logits = self.forward_host(host)
         self.cache.commit_lengths({request_id: end for request_id, (_, end) in spans.items()})
         self.steps_run += 1
         self.tokens_run += host.num_tokens

@@ -173,6 +173,7 @@ class Ops:
         self.fuse_norm = False
         self._partial_buffers: dict[str, Any] = {}
         self.scratch_frozen = False
+        self.scratch_generation = 0   # counts scratch buffers replaced by larger ones
         if self.code == BF16 and self.gemm_mode != "simt":
             st = _Lib(load_library("gemm_stream.cu"))
             self._gemm_stream = st.function("cie_gemm_stream", [v, v, v, v, i, i, i, i, i, i, v, v])
@@ -278,6 +279,8 @@ class Ops:
                     f"scratch buffer {tag!r} would have to grow from {held.numel()} to {elements} "
                     "elements while a CUDA graph that uses it is alive"
                 )
+            if held is not None:
+                self.scratch_generation += 1
             held = torch.empty(max(elements, reserve, 1), dtype=torch.float32, device=self.device)
             self._partial_buffers[tag] = held
         return held

@@ -184,3 +184,29 @@ def test_trace_run_program(sharp_models, tmp_path, dtype):
                 row += 1
             position[entry["id"]] += len(entry["tokens"])
     check_against_plain(sharp_models.get("B", dtype), requests, got, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_steps_from_captured_graphs_give_the_same_logits(sharp_models, name, dtype):
+    """With graphs on, a shape of step that comes by again runs from its captured graph: the tail
+    of single tokens, the repeated portions and the mixed trace all repeat shapes while contexts,
+    pages and token ids change.  The logits must be those of the launches one by one, bit for bit."""
+    requests = make_requests(name)
+    for steps in (trace_tail(requests, 32), trace_portions(requests, sizes=(7, 7, 7, 2, 2, 16, 16, 5)),
+                  trace_mixed(requests, seed=3)):
+        tokens = peak_tokens(steps, PAGE_SIZE[name])
+        core = make_core(sharp_models.get(name, dtype), name, dtype, tokens)
+        core.step.enable_graphs(core.max_model_len)
+        graphed = replay(core, steps)
+        # launch by launch with block tables of the same width (the decode kernel cuts the keys of
+        # a request into as many parts as the table's width allows, and the order of a sum shows)
+        one_by_one = make_core(sharp_models.get(name, dtype), name, dtype, tokens)
+        one_by_one.step.fixed_table_width = core.step.fixed_table_width
+        plain = replay(one_by_one, steps)
+        assert core.step.graph_captures > 0 and core.step.graph_replays > 0
+        assert graphed.keys() == plain.keys()
+        for rid in plain:
+            assert graphed[rid].keys() == plain[rid].keys()
+            for position, want in plain[rid].items():
+                assert np.array_equal(graphed[rid][position], want), (rid, position)
