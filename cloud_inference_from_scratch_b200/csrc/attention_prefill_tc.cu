@@ -4,15 +4,18 @@
 // One CTA takes 128 query rows of ONE request and ONE kv head; a row is a (token, query head of the
 // group) pair, so the heads of a group share every key and value.  Keys go by in tiles of 128:
 //
-//   TMA warp      key/value pages -> shared memory, boxes of 16 keys x 64 columns with 128-byte
-//                 swizzle, two stages, one mbarrier per stage.
+//   TMA warp      key/value pages -> shared memory, one copy per 16 keys (a 4-dimensional box
+//                 that leaves every 8 keys as two swizzled 8 x 64 pieces side by side: few, large
+//                 copies, because the TMA unit's rate of copies bounds this kernel); two stages of keys and two of values, each with its own mbarriers, so
+//                 the keys of tile j+2 are on their way while the values of tile j are still in use.
 //   MMA thread    S = Q K^T (128 x 128, float32, in tensor memory, double buffered), then
 //                 O += P V (128 x HEAD_DIM, in tensor memory).  V is the N operand with N
 //                 contiguous, exactly as it lies in the cache; nothing is transposed.
 //   4 softmax     thread r owns row r: reads S from tensor memory, keeps the running maximum and
-//   warps         sum in float32, writes P as bfloat16 into shared memory in the swizzled layout
-//                 the tensor core reads, and rescales O in tensor memory when the maximum of some
-//                 row of its warp grew by more than 2^8 (the result does not depend on when).
+//   warps         sum in float32, writes P as bfloat16 into shared memory (two buffers) in the
+//                 swizzled layout the tensor core reads, and rescales O in tensor memory when the
+//                 maximum of some row of its warp grew by more than 2^8 (the result does not
+//                 depend on when).
 //
 // S of tile j+1 is computed while the softmax of tile j runs; O += P V of tile j runs while the
 // maximum of tile j+1 is searched.  Every wait is bounded (about two seconds, then an error bit).
@@ -38,17 +41,36 @@ constexpr int D = HEAD_DIM;
 static_assert(D == 64 || D == 128, "this kernel is built for head sizes 64 and 128");
 
 constexpr int BM = 128;                 // query rows per CTA (tensor-memory lanes)
-constexpr int BN = 128;                 // keys per tile
+#ifndef TC_BN
+#define TC_BN 128
+#endif
+#ifndef TC_STAGES
+#define TC_STAGES 2
+#endif
+constexpr int BN = TC_BN;               // keys per tile: 64 or 128
+static_assert(BN == 64 || BN == 128, "key tiles of 64 or 128");
 constexpr int HALVES = D / 64;          // 64-column sub-tiles of a row of Q, K or V
-constexpr int SUB_BYTES = 128 * 128;    // one sub-tile: 128 rows of 128 bytes
-constexpr int TILE_BYTES = HALVES * SUB_BYTES;
-constexpr int P_BYTES = 2 * SUB_BYTES;  // 128 rows x 128 keys
-constexpr int STAGES = 2;
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + P_BYTES + 1024;
+constexpr int SUB_BYTES = 128 * 128;    // a sub-tile of Q or P: 128 rows of 128 bytes (64 columns)
+constexpr int Q_BYTES = HALVES * SUB_BYTES;
+constexpr int GROUP_BYTES = HALVES * 1024;          // 8 keys of K or V: 8 x 64 left columns, then the right ones
+constexpr int BLOCK_BYTES = 2 * GROUP_BYTES;        // 16 keys: what one TMA copy brings
+constexpr int TILE_BYTES = (BN / 16) * BLOCK_BYTES; // one stage of keys (or of values)
+constexpr int P_BYTES = (BN / 64) * SUB_BYTES;      // 128 rows x BN keys
+constexpr int STAGES = TC_STAGES;
+constexpr int SMEM_BYTES = Q_BYTES + TILE_BYTES * 2 * STAGES + 2 * P_BYTES + 1024;   // P is double buffered
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 constexpr int THREADS = 192;            // 4 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr int TMEM_COLS = 512;          // S0 | S1 | O
 constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
+constexpr int TABLE_SLOTS = 256;       // block-table entries kept in shared memory (more are read from global memory)
 constexpr float kGrow = 8.f;            // rescale when a maximum moved by more than this (log2 units)
+
+// 2^x by the special-function unit alone (results below 2^-126 become 0; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct Args {
   const bf16* q;
@@ -77,11 +99,12 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = smem;
-  unsigned char* k_s = q_s + TILE_BYTES;             // [STAGES][TILE_BYTES]
+  unsigned char* k_s = q_s + Q_BYTES;                // [STAGES][TILE_BYTES]
   unsigned char* v_s = k_s + STAGES * TILE_BYTES;    // [STAGES][TILE_BYTES]
   unsigned char* p_s = v_s + STAGES * TILE_BYTES;
-  __shared__ __align__(8) uint64_t kv_full[STAGES], kv_empty[STAGES], s_full[2], p_full, pv_done;
+  __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], p_full, pv_done[2];
   __shared__ uint32_t tmem_slot;
+  __shared__ int pages_s[TABLE_SLOTS];   // the block-table entries this CTA's keys need
 
   pdl_wait();
   pdl_trigger();
@@ -96,12 +119,19 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   const int pos_lo = context + q0;
   const int valid_hi = context + q0 + ntok;          // keys [0, valid_hi) are visible to some row
   const int tiles = (valid_hi + BN - 1) / BN;
+  // CTAs that share keys walk them from different starting tiles (the running-maximum softmax does
+  // not care about the order), so that they do not all ask L2 for the same lines at the same time
+  const int first_tile = tiles > 0 ? (int)((blockIdx.x * 5u + blockIdx.y * 3u) % (unsigned)tiles) : 0;
+  auto tile_of = [&](int j) { const int t = j + first_tile; return t >= tiles ? t - tiles : t; };
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
     mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
     mbar_init(&p_full, 128);
-    mbar_init(&pv_done, 1);
+    mbar_init(&pv_done[0], 1); mbar_init(&pv_done[1], 1);
     mbar_init_fence();
   }
   if (warp == 5) tmem_alloc<TMEM_COLS>(&tmem_slot);
@@ -119,6 +149,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   }
   for (int idx = tid; idx < STAGES * TILE_BYTES / 16; idx += THREADS)
     reinterpret_cast<uint4*>(v_s)[idx] = make_uint4(0u, 0u, 0u, 0u);
+  {
+    const int needed = min((valid_hi + a.page_size - 1) / a.page_size, min(a.table_width, TABLE_SLOTS));
+    for (int idx = tid; idx < needed; idx += THREADS) pages_s[idx] = table_row[idx];
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -126,66 +160,84 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   const uint32_t tmem = tmem_slot;
 
   if (warp == 4) {
-    // ---- TMA producer: lane b fetches the b-th block of 16 keys of a tile
-    for (int j = 0; j < tiles; ++j) {
+    // ---- TMA producer: lane b fetches the b-th block of 16 keys of a tile.  Keys and values have
+    // rings of their own: a key stage is free again as soon as S of its tile is computed, long
+    // before the values of that tile have been used.
+    // The keys run one tile ahead of the values in this thread's order of waits: the keys of tile
+    // j+1 only need S of tile j-1 computed, the values of tile j need O += P V of tile j-2.
+    auto block_row = [&](int j) -> int {
+      const int key = tile_of(j) * BN + lane * 16;
+      const int index = key / a.page_size;
+      int page = index >= a.table_width ? -1 : index < TABLE_SLOTS ? pages_s[index] : table_row[index];
+      if (page < 0 || page >= a.num_pages) {
+        atomicOr(a.err, kErrBadPage);
+        page = 0;                     // the copy must still happen: the barrier counts its bytes
+      }
+      return (page * a.kv_heads + kvh) * a.page_size + key % a.page_size;
+    };
+    auto blocks_of = [&](int j) { return min(BN / 16, (valid_hi - tile_of(j) * BN + 15) / 16); };
+    auto load = [&](int j, unsigned char* ring, const CUtensorMap* map, uint64_t* full, uint64_t* empty) -> bool {
       const int s = j % STAGES;
-      if (j >= STAGES && !mbar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1, a.err)) break;
-      const int k0 = j * BN;
-      const int blocks = min(BN / 16, (valid_hi - k0 + 15) / 16);
-      if (lane == 0) mbar_expect_tx(&kv_full[s], (uint32_t)blocks * 2u * 16u * D * 2u);
+      const int blocks = blocks_of(j);
+      const int row = lane < blocks ? block_row(j) : 0;
+      if (j >= STAGES && !mbar_wait(&empty[s], ((j / STAGES) - 1) & 1, a.err)) return false;
+      if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)blocks * 16u * D * 2u);
       __syncwarp();
-      if (lane < blocks) {
-        const int key = k0 + lane * 16;
-        const int index = key / a.page_size;
-        int page = index < a.table_width ? table_row[index] : -1;
-        if (page < 0 || page >= a.num_pages) {
-          atomicOr(a.err, kErrBadPage);
-          page = 0;                     // the copy must still happen: the barrier counts its bytes
-        }
-        const int row = (page * a.kv_heads + kvh) * a.page_size + key % a.page_size;
-#pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-          tma_load_2d(k_s + s * TILE_BYTES + h * SUB_BYTES + lane * 2048, &k_map, &kv_full[s], h * 64, row);
-          tma_load_2d(v_s + s * TILE_BYTES + h * SUB_BYTES + lane * 2048, &v_map, &kv_full[s], h * 64, row);
-        }
+      if (lane < blocks) {   // one copy per block of 16 keys (they lie in one page)
+        if constexpr (HALVES == 2) tma_load_4d(ring + s * TILE_BYTES + lane * BLOCK_BYTES, map, &full[s], 0, 0, 0, row / 8);
+        else tma_load_3d(ring + s * TILE_BYTES + lane * BLOCK_BYTES, map, &full[s], 0, 0, row / 8);
       }
       __syncwarp();
+      return true;
+    };
+    bool alive = tiles > 0 && load(0, k_s, &k_map, k_full, k_empty);
+    for (int j = 0; j < tiles && alive; ++j) {
+      if (j + 1 < tiles) alive = load(j + 1, k_s, &k_map, k_full, k_empty);
+      if (alive) alive = load(j, v_s, &v_map, v_full, v_empty);
     }
   } else if (warp == 5) {
     if (lane == 0) {
       // ---- MMA issuer
       constexpr uint32_t idesc_qk = idesc_bf16(BM, BN);
       constexpr uint32_t idesc_pv = idesc_bf16(BM, D, true);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      // descriptors differ only in their address field (bits 0..13, in units of 16 bytes): one is
+      // built per operand and the others follow by adding to it
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s)), p_desc0 = smem_desc_sw128(smem_u32(p_s));
+      // keys: rows are keys, groups of 8 keys GROUP_BYTES apart, the right 64 columns 1 KB further;
+      // values: the N-contiguous operand, 64-column blocks 1 KB apart, groups of 8 keys GROUP_BYTES apart
+      const uint64_t k_desc0 = smem_desc_sw128(smem_u32(k_s), 16, GROUP_BYTES);
+      const uint64_t v_desc0 = smem_desc_sw128(smem_u32(v_s), 1024, GROUP_BYTES);
       auto issue_qk = [&](int j) -> bool {
         const int s = j % STAGES;
-        if (!mbar_wait(&kv_full[s], (j / STAGES) & 1, a.err)) return false;
+        if (!mbar_wait(&k_full[s], (j / STAGES) & 1, a.err)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(k_s + s * TILE_BYTES);
+        const uint64_t k_desc = k_desc0 + (uint64_t)((s * TILE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * SUB_BYTES + (kk & 3) * 32;
-          umma_bf16(tmem + COL_S + (j & 1) * BN, smem_desc_sw128(q_addr + off), smem_desc_sw128(k_addr + off),
-                    idesc_qk, kk > 0 ? 1u : 0u);
+          constexpr int unit = 16;
+          const uint32_t q_off = ((kk >> 2) * SUB_BYTES + (kk & 3) * 32) / unit, k_off = ((kk >> 2) * 1024 + (kk & 3) * 32) / unit;
+          umma_bf16(tmem + COL_S + (j & 1) * BN, q_desc + q_off, k_desc + k_off, idesc_qk, kk > 0 ? 1u : 0u);
         }
         tc_commit(&s_full[j & 1]);
+        tc_commit(&k_empty[s]);
         return true;
       };
       bool alive = issue_qk(0);
       for (int j = 0; j < tiles && alive; ++j) {
         if (j + 1 < tiles) alive = issue_qk(j + 1);
         if (!alive || !mbar_wait(&p_full, j & 1, a.err)) { alive = false; break; }
+        if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, a.err)) { alive = false; break; }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_s + (j % STAGES) * TILE_BYTES);
+        const uint64_t p_desc = p_desc0 + (uint64_t)(((j & 1) * P_BYTES) >> 4);
+        const uint64_t v_desc = v_desc0 + (uint64_t)(((j % STAGES) * TILE_BYTES) >> 4);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           // P: 16 keys further inside the swizzled row; V: 16 key rows further down
-          const uint64_t p_desc = smem_desc_sw128(p_addr + (kk >> 2) * SUB_BYTES + (kk & 3) * 32);
-          const uint64_t v_desc = smem_desc_sw128(v_addr + kk * 2048, SUB_BYTES);
-          umma_bf16(tmem + COL_O, p_desc, v_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16(tmem + COL_O, p_desc + (uint32_t)(((kk >> 2) * SUB_BYTES + (kk & 3) * 32) >> 4),
+                    v_desc + (uint32_t)((kk * BLOCK_BYTES) >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(&kv_empty[j % STAGES]);
-        tc_commit(&pv_done);
+        tc_commit(&v_empty[j % STAGES]);
+        tc_commit(&pv_done[j & 1]);
       }
     }
     __syncwarp();
@@ -201,25 +253,38 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
     for (int j = 0; j < tiles && alive; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, a.err)) { alive = false; break; }
       tc_fence_after();
-      const int k0 = j * BN;
+      const int k0 = tile_of(j) * BN;
       const int rel = pos - k0;                       // columns 0..rel of this tile are visible
       const bool masked = k0 + BN - 1 > pos_lo;       // the same for the whole CTA
       const uint32_t s_addr = tmem + lane_base + COL_S + (j & 1) * BN;
-      float mx = -INFINITY;
+      // the whole row of S comes into registers once; maxima and sums run as four independent
+      // chains (a thread has no other warp on its scheduler to hide a dependent chain behind)
+      uint32_t sraw[BN / 32][32];
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(s_addr + c * 32, raw);
-        tc_wait_ld();
+      for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, sraw[c]);
+      tc_wait_ld();
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (masked) {   // a tile on the diagonal: compare every column with the row's position
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float s = __uint_as_float(raw[i]);
-          mx = fmaxf(mx, (masked && c * 32 + i > rel) ? -INFINITY : s);
+        for (int c = 0; c < BN / 32; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c * 32 + i > rel) sraw[c][i] = 0xff800000u;   // -inf: stays out of maximum and sum
+            mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sraw[c][i]));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sraw[c][i]));
         }
       }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= a.scale_log2;
       const bool grow = mx > m_used + kGrow;          // false while the row has seen no key
-      if (j > 0 && !mbar_wait(&pv_done, (j - 1) & 1, a.err)) { alive = false; break; }
+      // this tile's P buffer was last read by O += P V of tile j-2
+      if (j > 1 && !mbar_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, a.err)) { alive = false; break; }
       if (__any_sync(0xffffffffu, grow)) {
         float alpha = 1.f;
         if (grow) {
@@ -228,6 +293,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
           l *= alpha;
         }
         if (j > 0) {
+          // O must be complete up to tile j-1 before it is rescaled
+          if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, a.err)) { alive = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 32; ++c) {
@@ -242,21 +309,16 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
         }
       }
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
-        uint32_t raw[32];
-        tmem_ld32(s_addr + c * 32, raw);
-        tc_wait_ld();
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(raw[i]), a.scale_log2, -m_eff));
-          float p1 = exp2f(fmaf(__uint_as_float(raw[i + 1]), a.scale_log2, -m_eff));
-          if (masked) {
-            if (c * 32 + i > rel) p0 = 0.f;
-            if (c * 32 + i + 1 > rel) p1 = 0.f;
-          }
-          l += p0 + p1;
+          // masked columns hold -inf since the first pass: 2^(-inf) is 0
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sraw[c][i]), a.scale_log2, -m_eff));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sraw[c][i + 1]), a.scale_log2, -m_eff));
+          l4[(i >> 1) & 3] += p0 + p1;
           __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pair);
         }
@@ -264,16 +326,17 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
 #pragma unroll
         for (int piece = 0; piece < 4; ++piece) {
           const int chunk = c * 4 + piece;
-          *reinterpret_cast<uint4*>(p_s + (chunk >> 3) * SUB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) =
+          *reinterpret_cast<uint4*>(p_s + (j & 1) * P_BYTES + (chunk >> 3) * SUB_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) =
               make_uint4(packed[piece * 4], packed[piece * 4 + 1], packed[piece * 4 + 2], packed[piece * 4 + 3]);
         }
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full);
     }
     // ---- write out
-    if (alive && tiles > 0 && mbar_wait(&pv_done, (tiles - 1) & 1, a.err)) {
+    if (alive && tiles > 0 && mbar_wait(&pv_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, a.err)) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = a.out + (size_t)(first_token + tok) * a.out_stride + (size_t)(kvh * a.group + hh) * D;
@@ -336,8 +399,8 @@ extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, 
   a.scale_log2 = scale * 1.4426950408889634f; a.err = err;
   CUtensorMap k_map, v_map;
   const long long rows = (long long)num_pages * kv_heads * page_size;
-  // the pools as matrices [pages * kv_heads * page_size, D], read in boxes of 16 rows
-  if (!tensor_map_bf16(k_pool, rows, D, 16, &k_map) || !tensor_map_bf16(v_pool, rows, D, 16, &v_map))
+  // the pools as matrices [pages * kv_heads * page_size, D], read in blocks of 16 whole rows
+  if (!tensor_map_bf16_row_blocks(k_pool, rows, D, 16, &k_map) || !tensor_map_bf16_row_blocks(v_pool, rows, D, 16, &v_map))
     CIE_FAIL("attention_prefill_tc: cuTensorMapEncodeTiled failed");
   static bool configured = false;
   if (!configured) {

@@ -53,6 +53,16 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 // Orders this thread's ordinary shared-memory writes before later reads or writes of the same
 // bytes by TMA or the tensor cores.
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -105,11 +115,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 //  * reduction dimension contiguous ("K-major", rows are M or N indices): `leading` is not used;
 //  * M/N dimension contiguous ("MN-major", rows are indices of the reduction dimension, 64
 //    M/N elements per row): `leading` is the distance in bytes between blocks of 64 M/N elements.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t leading = 16) {
+// `stride`: distance in bytes between groups of 8 rows (1024 when the groups follow each other).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t leading = 16, uint32_t stride = 1024) {
   uint64_t desc = 0;
   desc |= (uint64_t)((addr & 0x3FFFF) >> 4);
   desc |= (uint64_t)((leading >> 4) & 0x3FFF) << 16;
-  desc |= (uint64_t)(1024 >> 4) << 32;
+  desc |= (uint64_t)((stride >> 4) & 0x3FFF) << 32;
   desc |= (uint64_t)1 << 46;                   // descriptor version of sm_100
   desc |= (uint64_t)2 << 61;                   // SWIZZLE_128B
   return desc;
@@ -175,6 +186,57 @@ inline bool tensor_map_bf16(const void* ptr, long long rows, long long cols, int
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return false;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return true;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] (rows a multiple of 8, cols 64 or 128)
+// read in blocks of `block_rows` whole rows (a multiple of 8) by ONE copy each.  What a copy leaves
+// in shared memory is, for every group of 8 rows, first the 8 x 64 left columns (1 KB, 128-byte
+// swizzle) and then, if cols is 128, the 8 x 64 right columns: a layout the tensor core reads as a
+// swizzled operand whose groups of 8 rows are cols * 16 bytes apart.  The coordinates of a copy
+// are (0, 0, [0,] first row / 8).
+inline bool tensor_map_bf16_row_blocks(const void* ptr, long long rows, int cols, int block_rows, CUtensorMap* out) {
+  struct Key {
+    const void* ptr; long long rows; int cols, block_rows;
+    bool operator==(const Key& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && block_rows == o.block_rows; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^ ((size_t)k.cols * 131) ^ (size_t)k.block_rows;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex lock;
+  if ((cols != 64 && cols != 128) || rows % 8 || block_rows % 8 || block_rows < 8 || block_rows > 256 * 8) return false;
+  const Key key{ptr, rows, cols, block_rows};
+  std::lock_guard<std::mutex> guard(lock);
+  auto found = cache.find(key);
+  if (found != cache.end()) { *out = found->second; return true; }
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return false;
+  const cuuint64_t row_bytes = (cuuint64_t)cols * 2;
+  CUtensorMap map;
+  CUresult status;
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  if (cols == 128) {
+    cuuint64_t dims[4] = {64, 8, 2, (cuuint64_t)(rows / 8)};
+    cuuint64_t strides[3] = {row_bytes, 128, 8 * row_bytes};
+    cuuint32_t box[4] = {64, 8, 2, (cuuint32_t)(block_rows / 8)};
+    status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[3] = {64, 8, (cuuint64_t)(rows / 8)};
+    cuuint64_t strides[2] = {row_bytes, 8 * row_bytes};
+    cuuint32_t box[3] = {64, 8, (cuuint32_t)(block_rows / 8)};
+    status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (status != CUDA_SUCCESS) return false;
   if (cache.size() > 8192) cache.clear();
   cache.emplace(key, map);
   *out = map;

@@ -65,7 +65,11 @@ class TensorAttention:
         # pages of a multiple of 16 tokens; everything else stays on the mma.sync kernel
         self._prefill_tc = None
         if head_dim in (64, 128) and os.environ.get("CIE_PREFILL_TC", "1") != "0":
-            tc = _Lib(load_library("attention_prefill_tc.cu", {"HEAD_DIM": head_dim}))
+            defines = {"HEAD_DIM": head_dim}
+            for name in ("TC_BN", "TC_STAGES"):
+                if os.environ.get("CIE_" + name):
+                    defines[name] = int(os.environ["CIE_" + name])
+            tc = _Lib(load_library("attention_prefill_tc.cu", defines))
             self._prefill_tc = tc.function(
                 "cie_attention_prefill_tc",
                 [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, v, v],
