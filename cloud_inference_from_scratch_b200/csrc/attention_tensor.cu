@@ -14,6 +14,7 @@
 // Formula: zeeshan8281/cloud-inference-from-scratch src/cloud_engine/kernel.py:324-405 (one
 // program per query token and head, CUDA-core reductions, page size fixed at 16, head size
 // 64 or 128).  Here head sizes are the multiples of 16 up to 256, any page size and grouping.
+#include "blackwell.cuh"
 #include "common.cuh"
 
 #include <cooperative_groups.h>
@@ -137,9 +138,14 @@ __device__ __forceinline__ long long kv_offset(const Pools& pools, const int* ro
 // SW == false: rows of ROW elements (padded).  SW == true: the layout a TMA tensor copy with
 // 128-byte swizzle leaves: 16-row sub-tiles of 64 columns, 2 KB each, the 16-byte piece c of
 // row r stored at piece position c ^ (r & 7).
+// For head sizes 64 and 128 one TMA copy brings a whole 16-key tile (a 4-dimensional box, see
+// tensor_map_bf16_row_blocks): every 8 rows are two swizzled 8 x 64 pieces side by side.
+constexpr bool kBlockCopies = D == 64 || D == 128;
 template <bool SW>
 __device__ __forceinline__ const bf16* tile_ptr(const bf16* base, int row, int col) {
   if constexpr (!SW) return base + row * ROW + col;
+  else if constexpr (kBlockCopies)
+    return base + (row >> 3) * (D * 8) + (col >> 6) * 512 + (row & 7) * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
   else return base + (col >> 6) * 1024 + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
 }
 
@@ -571,10 +577,20 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
         const int row0 = (page * a.pools.kv_heads + kvh) * a.pools.page_size + within;
         uint64_t* bar = &bars[warp][slot];
         mbar_expect_tx(bar, (uint32_t)(2 * DN * D * sizeof(bf16)));
+        if constexpr (kBlockCopies) {
+          if constexpr (D == 128) {
+            bw::tma_load_4d(dst, &k_map, bar, 0, 0, 0, row0 / 8);
+            bw::tma_load_4d(dst + DN * D, &v_map, bar, 0, 0, 0, row0 / 8);
+          } else {
+            bw::tma_load_3d(dst, &k_map, bar, 0, 0, row0 / 8);
+            bw::tma_load_3d(dst + DN * D, &v_map, bar, 0, 0, row0 / 8);
+          }
+        } else {
 #pragma unroll
-        for (int sub = 0; sub < D / 64; ++sub) {
-          tma_load_2d(dst + sub * 1024, &k_map, bar, sub * 64, row0);
-          tma_load_2d(dst + DN * D + sub * 1024, &v_map, bar, sub * 64, row0);
+          for (int sub = 0; sub < D / 64; ++sub) {
+            tma_load_2d(dst + sub * 1024, &k_map, bar, sub * 64, row0);
+            tma_load_2d(dst + DN * D + sub * 1024, &v_map, bar, sub * 64, row0);
+          }
         }
       }
     } else {
@@ -887,7 +903,10 @@ extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int 
                    ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) == 0;
   if (tma) {
     const long long rows = (long long)num_pages * kv_heads * page_size;
-    if (!pool_map(k_pool, rows, &k_map) || !pool_map(v_pool, rows, &v_map))
+    const bool mapped = kBlockCopies
+        ? bw::tensor_map_bf16_row_blocks(k_pool, rows, D, 16, &k_map) && bw::tensor_map_bf16_row_blocks(v_pool, rows, D, 16, &v_map)
+        : pool_map(k_pool, rows, &k_map) && pool_map(v_pool, rows, &v_map);
+    if (!mapped)
       CIE_FAIL("attention_decode: cuTensorMapEncodeTiled failed");
     return launch_decode<true>(k_map, v_map, a, requests, (cudaStream_t)stream);
   }
