@@ -1,11 +1,10 @@
 """The reference arm of bench.py: the unmodified reference project, installed under baseline/_ref,
 driven through its own public API for the same metric and model shape.
 
-Install (once, offline; the source tree is read-only, so from a copy):
+Install (once, offline, from a writable copy of the reference's source tree):
 
-    cp -r /root/reference /tmp/refcopy
-    python -m pip install --no-index --no-build-isolation --find-links /opt/wheelhouse \
-        --target baseline/_ref /tmp/refcopy
+    python -m pip install --no-index --no-build-isolation --find-links <wheel folder> \
+        --target baseline/_ref <copy of the reference>
 
 What runs is the reference's stock path: ``cloud_engine.config.build_config("ragged", pinned, ...)``,
 ``cloud_engine.engine.InferenceEngine(config, model_dir)``, ``await engine.start()`` (its loader, its

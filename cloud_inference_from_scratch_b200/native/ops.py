@@ -139,7 +139,7 @@ class Ops:
             raise KernelError(f"compute dtype must be float32 or bfloat16, got {dtype}")
         self.dtype = dtype
         self.code = F32 if dtype == torch.float32 else BF16
-        self.gemm_mode = gemm or ("simt" if self.code == F32 else "cublas")
+        self.gemm_mode = gemm or ("simt" if self.code == F32 else os.environ.get("CIE_GEMM", "cublas"))
         if self.code == F32 and self.gemm_mode != "simt":
             raise KernelError("the 32-bit path multiplies on the CUDA cores only (gemm='simt')")
         if self.gemm_mode not in ("simt", "tensor", "cublas"):
