@@ -1,6 +1,6 @@
-// Weight-streaming matrix product for few rows (decode): out[M, N] = x[M, K] * W[N, K]^T, M <= 64.
+// Weight-streaming matrix product for few rows (decode): out[M, N] = x[M, K] * W[N, K]^T, M <= 16.
 //
-// With at most 64 tokens a projection is bound by reading W once from HBM, so the kernel is
+// With so few tokens a projection is bound by reading W once from HBM, so the kernel is
 // built around the weight stream: a CTA owns BN weight rows and a slice of K, and pulls
 // [BN x 128] weight tiles through a four-stage pipeline (two TMA tensor copies per tile with
 // 128-byte swizzle, completing on the stage's mbarrier; cp.async for a weight whose address or
@@ -64,7 +64,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-constexpr int kOutBF16 = 0, kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3, kOutResidual = 4, kOutRope = 5;
+[[maybe_unused]] constexpr int kOutBF16 = 0;
+constexpr int kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3, kOutResidual = 4, kOutRope = 5;
 
 struct StreamArgs {
   const bf16* x;       // [M, K]
@@ -484,20 +485,9 @@ static int launch(const StreamArgs& a, int splits, cudaStream_t stream) {
 static int dispatch(StreamArgs& a, int splits, int block_rows, cudaStream_t s) {
   const int k_tiles = (a.k + BK - 1) / BK;
   a.k_per_split = ((k_tiles + splits - 1) / splits) * BK;
-  const int mt = a.m <= 8 ? 1 : a.m <= 16 ? 2 : a.m <= 32 ? 4 : 8;
-  if (block_rows == 32) {
-    if (mt == 1) return launch<1, 32>(a, splits, s);
-    if (mt == 2) return launch<2, 32>(a, splits, s);
-    if (mt == 4) return launch<4, 32>(a, splits, s);
-    return launch<8, 32>(a, splits, s);
-  }
-  if (block_rows == 64) {
-    if (mt == 1) return launch<1, 64>(a, splits, s);
-    if (mt == 2) return launch<2, 64>(a, splits, s);
-    if (mt == 4) return launch<4, 64>(a, splits, s);
-    return launch<8, 64>(a, splits, s);
-  }
-  CIE_FAIL("gemm_stream: block_rows must be 32 or 64, got %d", block_rows);
+  if (block_rows != 32) CIE_FAIL("gemm_stream: weight rows per CTA must be 32, got %d", block_rows);
+  if (a.m <= 8) return launch<1, 32>(a, splits, s);
+  return launch<2, 32>(a, splits, s);
 }
 
 }  // namespace cie
@@ -513,14 +503,14 @@ using namespace cie;
 //          4 residual[M, N] += product (+ bias), sq[M, ceil(N / 32)] = sums of squares of the new
 //          rows per block of 32 columns and, with next_gain, scaled[M, N] = bfloat16(new row *
 //          next_gain); splits must be 1, 2, 4 or 8 (the size of a cluster), block_rows 32.
-// block_rows: weight rows per CTA, 32 or 64.
+// block_rows: weight rows per CTA; 32 is the one size built.
 extern "C" int cie_gemm_stream_ex(const void* x, const float* row_sq, int row_tiles, float eps, const void* w,
                                   const float* bias, void* out, float* residual, float* sq, void* scaled,
                                   const float* next_gain, int m, int n, int k, int splits, int mode,
                                   int block_rows, int* err, void* stream) {
   if (m <= 0 || n <= 0) return 0;
   if (!x || !w) CIE_FAIL("gemm_stream: null operand");
-  if (m > 64) CIE_FAIL("gemm_stream: takes at most 64 rows, got %d", m);
+  if (m > 16) CIE_FAIL("gemm_stream: takes at most 16 rows, got %d", m);
   if (k < 8 || k % 8) CIE_FAIL("gemm_stream: K must be a multiple of 8 (16-byte rows), got %d", k);
   if (splits < 1) CIE_FAIL("gemm_stream: splits %d", splits);
   if (mode < 0 || mode > kOutResidual) CIE_FAIL("gemm_stream: mode %d (the rotary epilogue has its own entry point)", mode);

@@ -131,7 +131,10 @@ class _StepGraph:
 
 
 MAX_STEP_GRAPHS = 8          # captured shapes kept (least recently used goes first)
-CAPTURE_AT_OCCURRENCE = 2    # a shape is captured when it is seen for the second time
+# A capture costs about two runs of the step plus the instantiation of the graph, and pays only
+# where the host issues launches more slowly than the device runs them: wait for a shape to prove
+# that it recurs.
+CAPTURE_AT_OCCURRENCE = 3    # a shape is captured when it is seen for the third time
 
 
 class StepFunction:
@@ -321,7 +324,7 @@ class StepFunction:
 
     def forward_host(self, host: HostBatch) -> tuple[StepContext, Any]:
         """Uploads the step's metadata and runs the model on it: from the captured graph of this
-        shape of step if there is one, else kernel by kernel (and, the second time a shape comes
+        shape of step if there is one, else kernel by kernel (and, the third time a shape comes
         by, capturing it).  Returns the context and the logits (None if no row was wanted)."""
         if not self.graphs_enabled:
             ctx = self.upload(host)

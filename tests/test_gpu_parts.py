@@ -360,3 +360,151 @@ def test_windowed_and_full_attention_in_one_model(dtype, name, tmp_path):
     assert core.cache.groups[window_group].allocator.allocations_total > per_group[window_group]
     assert core.cache.free_pages(0) == core.cache.total_pages(0)
     assert core.cache.free_pages(1) == core.cache.total_pages(1)
+
+
+# ------------------------------------------------------------------ a routed feed-forward and another position encoding
+def register_toy_routed():
+    """A model whose first layer has a feed-forward with top-1 routing over two experts and an
+    attention with linearly scaled rotary positions; both parts are defined here, not in the package."""
+    from cloud_inference_from_scratch_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from cloud_inference_from_scratch_b200.parts import FeedForward, PositionEncoding, TensorSpec, register_part
+
+    class TopOneExperts(FeedForward):
+        """update = expert_e(x) with e = argmax(router(x)) in float32; every expert is a SwiGLU."""
+
+        def __init__(self, hidden_size, intermediate_size, experts):
+            self.hidden_size, self.intermediate_size, self.experts = hidden_size, intermediate_size, experts
+
+        def tensor_specs(self):
+            specs = {"router.weight": TensorSpec((self.experts, self.hidden_size))}
+            for e in range(self.experts):
+                specs[f"experts.{e}.gate_proj.weight"] = TensorSpec((self.intermediate_size, self.hidden_size))
+                specs[f"experts.{e}.up_proj.weight"] = TensorSpec((self.intermediate_size, self.hidden_size))
+                specs[f"experts.{e}.down_proj.weight"] = TensorSpec((self.hidden_size, self.intermediate_size))
+            return specs
+
+        def bind(self, tensors, runtime):
+            self.runtime, self.tensors = runtime, tensors
+
+        def forward(self, x, ctx):
+            logits = x.float() @ self.tensors["router.weight"].float().t()      # router in float32
+            choice = logits.argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows]
+                gate = xe @ self.tensors[f"experts.{e}.gate_proj.weight"].t()
+                up = xe @ self.tensors[f"experts.{e}.up_proj.weight"].t()
+                hidden = (torch.nn.functional.silu(gate.float()) * up.float()).to(x.dtype)
+                out[rows] = hidden @ self.tensors[f"experts.{e}.down_proj.weight"].t()
+            return out
+
+    class RopeLinear(PositionEncoding):
+        """Rotate-half rotary with positions divided by ``factor``: the attention part and its
+        kernels only read ``rotary_dim`` and ``inv_freq``."""
+
+        def __init__(self, head_dim, theta, factor):
+            self.head_dim, self.rotary_dim, self.theta, self.factor = head_dim, head_dim, theta, factor
+
+        def bind(self, tensors, runtime):
+            exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
+            self.inv_freq = (1.0 / (self.theta ** exponent) / self.factor).to(runtime.device).contiguous()
+
+    register_part("feed_forward", "toy_top_one_experts", TopOneExperts, replace=True)
+    register_part("position", "toy_rope_linear", RopeLinear, replace=True)
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        hidden_size: int
+        intermediate_size: int
+        vocab_size: int
+        heads: int
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"], raw["heads"])
+
+        def to_dict(self):
+            return dict(architectures=["ToyRoutedForCausalLM"], model_type="toy_routed", hidden_size=self.hidden_size,
+                        intermediate_size=self.intermediate_size, vocab_size=self.vocab_size, heads=self.heads)
+
+    def spec(config):
+        eps = 1e-5
+        head_dim = config.hidden_size // config.heads
+        norm = dict(hidden_size=config.hidden_size, eps=eps)
+
+        def attention(position):
+            return PartSpec("attention", dict(hidden_size=config.hidden_size, num_heads=config.heads, num_kv_heads=1,
+                                              head_dim=head_dim, qkv_bias=False, position=position), prefix="self_attn.")
+
+        def layer(index, mixer, feed_forward):
+            return LayerSpec(prefix=f"model.layers.{index}.", block=PartSpec("prenorm_residual"), mixer=mixer,
+                             feed_forward=feed_forward, mixer_norm=PartSpec("rmsnorm", norm, prefix="input_layernorm."),
+                             feed_forward_norm=PartSpec("rmsnorm", norm, prefix="post_attention_layernorm."))
+
+        scaled = PartSpec("toy_rope_linear", dict(head_dim=head_dim, theta=1e4, factor=4.0))
+        plain_rope = PartSpec("rope_neox", dict(head_dim=head_dim, rotary_dim=head_dim, theta=1e4, max_positions=512))
+        routed = PartSpec("toy_top_one_experts", dict(hidden_size=config.hidden_size,
+                                                      intermediate_size=config.intermediate_size, experts=2), prefix="moe.")
+        dense = PartSpec("swiglu", dict(hidden_size=config.hidden_size, intermediate_size=config.intermediate_size), prefix="mlp.")
+        return ModelSpec(
+            architecture="ToyRoutedForCausalLM", vocab_size=config.vocab_size, hidden_size=config.hidden_size,
+            embedding_tensor="model.embed_tokens.weight",
+            layers=(layer(0, attention(scaled), routed), layer(1, attention(plain_rope), dense)),
+            schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=PartSpec("rmsnorm", norm),
+            final_norm_prefix="model.norm.", head_tensor="model.embed_tokens.weight", max_positions=512,
+        )
+
+    register_architecture("ToyRoutedForCausalLM", "toy_routed", RoutedConfig.from_dict, spec, replace=True)
+    return RoutedConfig(hidden_size=64, intermediate_size=80, vocab_size=257, heads=2)
+
+
+def toy_routed_plain_forward(folder, tokens):
+    _, w = plain_model.read_model_folder(folder)
+    eps = 1e-5
+    config = dict(num_attention_heads=2, num_key_value_heads=1, hidden_size=64, rope_theta=1e4)
+    positions = list(range(len(tokens)))
+    h = plain_model.embedding(w["model.embed_tokens.weight"], tokens)
+    x = plain_model.rms_norm(h, w["model.layers.0.input_layernorm.weight"], eps)
+    update, _ = plain_model.attention_layer(x, w, "model.layers.0.self_attn.", config, [p / 4.0 for p in positions])
+    h = h + update
+    x = plain_model.rms_norm(h, w["model.layers.0.post_attention_layernorm.weight"], eps)
+    choice = (x @ w["model.layers.0.moe.router.weight"].t()).argmax(-1)
+    routed = torch.zeros_like(x)
+    for e in range(2):
+        p = f"model.layers.0.moe.experts.{e}."
+        full = plain_model.swiglu(x, w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
+        routed[choice == e] = full[choice == e]
+    h = h + routed
+    x = plain_model.rms_norm(h, w["model.layers.1.input_layernorm.weight"], eps)
+    update, _ = plain_model.attention_layer(x, w, "model.layers.1.self_attn.", config, positions)
+    h = h + update
+    x = plain_model.rms_norm(h, w["model.layers.1.post_attention_layernorm.weight"], eps)
+    h = h + plain_model.swiglu(x, w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"],
+                               w["model.layers.1.mlp.down_proj.weight"])
+    return plain_model.rms_norm(h, w["model.norm.weight"], eps) @ w["model.embed_tokens.weight"].t(), choice
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    """Registered, built from a folder and stepped through every cutting without a change to the
+    package.  32-bit only: a router's argmax over near-equal logits would make a bfloat16 run and
+    the plain model pick different experts, which says nothing about the engine."""
+    from cloud_inference_from_scratch_b200.engine.core import build_core
+    from cloud_inference_from_scratch_b200.weights import write_random_model
+
+    config = register_toy_routed()
+    folder = write_random_model(tmp_path / "routed", config.to_dict(), 5)
+    core = build_core(folder, dtype="float32", page_size=8, num_pages=48, max_requests=4, max_model_len=128)
+    assert core.architecture == "ToyRoutedForCausalLM"
+    requests = {f"r{i}": random_tokens(257, n, 40 + i) for i, n in enumerate((33, 6, 50, 21))}
+    used = set()
+    for steps in (trace_whole(requests), trace_portions(requests), trace_mixed(requests, seed=2)):
+        got = replay(core, steps)
+        for rid, tokens in requests.items():
+            ref, choice = toy_routed_plain_forward(folder, tokens)
+            used.update(choice.tolist())
+            mine = np.stack([got[rid][p] for p in range(len(tokens))])
+            assert relative_error(mine, ref.numpy()) <= TOL["float32"], (rid, relative_error(mine, ref.numpy()))
+    assert used == {0, 1}      # both experts took tokens

@@ -193,7 +193,7 @@ def test_steps_from_captured_graphs_give_the_same_logits(sharp_models, name, dty
     of single tokens, the repeated portions and the mixed trace all repeat shapes while contexts,
     pages and token ids change.  The logits must be those of the launches one by one, bit for bit."""
     requests = make_requests(name)
-    for steps in (trace_tail(requests, 32), trace_portions(requests, sizes=(7, 7, 7, 2, 2, 16, 16, 5)),
+    for steps in (trace_tail(requests, 32), trace_portions(requests, sizes=(7, 7, 7, 7, 2, 2, 2, 16, 16, 16, 5)),
                   trace_mixed(requests, seed=3)):
         tokens = peak_tokens(steps, PAGE_SIZE[name])
         core = make_core(sharp_models.get(name, dtype), name, dtype, tokens)
