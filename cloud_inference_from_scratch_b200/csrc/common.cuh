@@ -69,10 +69,13 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // its own wait, every earlier one) has completed and its writes are visible.  Before the wait a
 // kernel may only do what does not depend on earlier kernels and writes nothing they read:
 // set-up and prefetching what earlier kernels do not write.  `pdl_trigger` lets the next kernel in
-// the stream start its own set-up.  Every kernel triggers AFTER its own wait: a kernel can then
-// overlap only the ONE kernel before it (whose own predecessors have all completed), which is
-// what the early loads of the streaming product and of decode attention rely on.  Without the
-// launch attribute both are no-ops.
+// the stream start its own set-up.  Kernels trigger AFTER their own wait: a kernel can then
+// overlap only the ONE kernel before it (whose own predecessors have all completed).  Two kinds of
+// kernel trigger first (the RMSNorm kernel and the streaming product with the residual epilogue),
+// because what follows them is a product whose early part only asks for weights; the kernel after
+// that one waits before it triggers, so never more than two kernels back are still running.
+// The early loads (weight tiles; key/value tiles of earlier steps) stay valid under that.
+// Without the launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -194,8 +194,13 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s)
     if (s < steps) load_w(s);
+  // A product with the residual epilogue lets the next kernel start already now, beside the kernel
+  // before this one: what follows is the next product, and before its own wait a kernel of this
+  // engine touches only what no kernel of the same step writes (weight tiles; key/value tiles of
+  // earlier steps).
+  if (a.mode == kOutResidual) pdl_trigger();
   pdl_wait();
-  pdl_trigger();
+  if (a.mode != kOutResidual) pdl_trigger();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < steps) load_x(s);
