@@ -4,12 +4,12 @@
 // One CTA takes 128 query rows of ONE request and ONE kv head; a row is a (token, query head of the
 // group) pair, so the heads of a group share every key and value.  Keys go by in tiles of 128:
 //
-//   TMA warp      key/value pages -> shared memory, one copy per 16 keys (a 4-dimensional box
+//   TMA warps     key/value pages -> shared memory, one copy per 16 keys (a 4-dimensional box
 //                 that leaves every 8 keys as two swizzled 8 x 64 pieces side by side: few, large
 //                 copies, because the TMA unit's rate of copies bounds this kernel); two stages of keys and two of values, each with its own mbarriers, so
 //                 the keys of tile j+2 are on their way while the values of tile j are still in use.
-//   MMA thread    S = Q K^T (128 x 128, float32, in tensor memory, double buffered), then
-//                 O += P V (128 x HEAD_DIM, in tensor memory).  V is the N operand with N
+//   MMA threads   one issues S = Q K^T (128 x 128, float32, in tensor memory, double buffered),
+//                 another O += P V (128 x HEAD_DIM, in tensor memory).  V is the N operand with N
 //                 contiguous, exactly as it lies in the cache; nothing is transposed.
 //   4 softmax     thread r owns row r: reads S from tensor memory, keeps the running maximum and
 //   warps         sum in float32, writes P as bfloat16 into shared memory (two buffers) in the
@@ -59,7 +59,20 @@ constexpr int P_BYTES = (BN / 64) * SUB_BYTES;      // 128 rows x BN keys
 constexpr int STAGES = TC_STAGES;
 constexpr int SMEM_BYTES = Q_BYTES + TILE_BYTES * 2 * STAGES + 2 * P_BYTES + 1024;   // P is double buffered
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
-constexpr int THREADS = 192;            // 4 softmax warps, 1 TMA warp, 1 MMA warp
+#ifndef TC_KEY_PRODUCERS
+#define TC_KEY_PRODUCERS 1
+#endif
+#ifndef TC_VALUE_PRODUCERS
+#define TC_VALUE_PRODUCERS 1
+#endif
+// TMA warps per ring: the copies of a tile are issued by several threads at once (one warp issuing
+// all of them was measured slower).  No more than 8 warps in all: the softmax threads keep a row
+// of S in registers and need the 255 a thread of a 256-thread CTA may have.
+constexpr int KEY_PRODUCERS = TC_KEY_PRODUCERS, VALUE_PRODUCERS = TC_VALUE_PRODUCERS;
+constexpr int MMA_WARP = 4;            // issues S = Q K^T (and owns the tensor-memory allocation)
+constexpr int PV_WARP = 5 + KEY_PRODUCERS + VALUE_PRODUCERS;   // issues O += P V
+constexpr int THREADS = (PV_WARP + 1) * 32;   // 4 softmax warps, two MMA warps, the TMA warps
+static_assert(THREADS <= 256, "at most 8 warps");
 constexpr int TMEM_COLS = 512;          // S0 | S1 | O
 constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
 constexpr int TABLE_SLOTS = 256;       // block-table entries kept in shared memory (more are read from global memory)
@@ -102,7 +115,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   unsigned char* k_s = q_s + Q_BYTES;                // [STAGES][TILE_BYTES]
   unsigned char* v_s = k_s + STAGES * TILE_BYTES;    // [STAGES][TILE_BYTES]
   unsigned char* p_s = v_s + STAGES * TILE_BYTES;
-  __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], p_full, pv_done[2];
+  __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], s_free[2], p_full, pv_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int pages_s[TABLE_SLOTS];   // the block-table entries this CTA's keys need
 
@@ -130,11 +143,12 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
+    mbar_init(&s_free[0], 128); mbar_init(&s_free[1], 128);
     mbar_init(&p_full, 128);
     mbar_init(&pv_done[0], 1); mbar_init(&pv_done[1], 1);
     mbar_init_fence();
   }
-  if (warp == 5) tmem_alloc<TMEM_COLS>(&tmem_slot);
+  if (warp == MMA_WARP) tmem_alloc<TMEM_COLS>(&tmem_slot);
 
   // ---- Q tile, swizzled by hand: row r is token r / hpt, head h0 + r % hpt of the group.
   // Value stages start as zeros: rows that no copy fills must not hold NaN or Inf bits.
@@ -159,14 +173,17 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
 
-  if (warp == 4) {
-    // ---- TMA producer: lane b fetches the b-th block of 16 keys of a tile.  Keys and values have
-    // rings of their own: a key stage is free again as soon as S of its tile is computed, long
-    // before the values of that tile have been used.
-    // The keys run one tile ahead of the values in this thread's order of waits: the keys of tile
-    // j+1 only need S of tile j-1 computed, the values of tile j need O += P V of tile j-2.
+  if (warp > MMA_WARP && warp < PV_WARP) {
+    // ---- TMA producers: some warps for the keys, some for the values; a lane fetches one
+    // block of 16 keys of a tile.  Keys and values have rings of their own: a key stage is free again
+    // as soon as S of its tile is computed, long before the values of that tile have been used.
+    const bool for_keys = warp - MMA_WARP - 1 < KEY_PRODUCERS;
+    const int sharers = for_keys ? KEY_PRODUCERS : VALUE_PRODUCERS;
+    const int part = for_keys ? warp - MMA_WARP - 1 : warp - MMA_WARP - 1 - KEY_PRODUCERS;   // which share of a tile's blocks
+    const int per_warp = (BN / 16 + sharers - 1) / sharers;
+    const int block = part * per_warp + lane;                    // this lane's block, if lane < per_warp
     auto block_row = [&](int j) -> int {
-      const int key = tile_of(j) * BN + lane * 16;
+      const int key = tile_of(j) * BN + block * 16;
       const int index = key / a.page_size;
       int page = index >= a.table_width ? -1 : index < TABLE_SLOTS ? pages_s[index] : table_row[index];
       if (page < 0 || page >= a.num_pages) {
@@ -179,37 +196,38 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
     auto load = [&](int j, unsigned char* ring, const CUtensorMap* map, uint64_t* full, uint64_t* empty) -> bool {
       const int s = j % STAGES;
       const int blocks = blocks_of(j);
-      const int row = lane < blocks ? block_row(j) : 0;
+      const bool mine = lane < per_warp && block < blocks;
+      const int row = mine ? block_row(j) : 0;
       if (j >= STAGES && !mbar_wait(&empty[s], ((j / STAGES) - 1) & 1, a.err)) return false;
-      if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)blocks * 16u * D * 2u);
+      // the first warp of the ring announces the bytes of the whole tile (a copy of another warp
+      // may complete before that: the phase still waits for this arrival)
+      if (part == 0 && lane == 0) mbar_expect_tx(&full[s], (uint32_t)blocks * 16u * D * 2u);
       __syncwarp();
-      if (lane < blocks) {   // one copy per block of 16 keys (they lie in one page)
-        if constexpr (HALVES == 2) tma_load_4d(ring + s * TILE_BYTES + lane * BLOCK_BYTES, map, &full[s], 0, 0, 0, row / 8);
-        else tma_load_3d(ring + s * TILE_BYTES + lane * BLOCK_BYTES, map, &full[s], 0, 0, row / 8);
+      if (mine) {   // one copy per block of 16 keys (they lie in one page)
+        if constexpr (HALVES == 2) tma_load_4d(ring + s * TILE_BYTES + block * BLOCK_BYTES, map, &full[s], 0, 0, 0, row / 8);
+        else tma_load_3d(ring + s * TILE_BYTES + block * BLOCK_BYTES, map, &full[s], 0, 0, row / 8);
       }
       __syncwarp();
       return true;
     };
-    bool alive = tiles > 0 && load(0, k_s, &k_map, k_full, k_empty);
-    for (int j = 0; j < tiles && alive; ++j) {
-      if (j + 1 < tiles) alive = load(j + 1, k_s, &k_map, k_full, k_empty);
-      if (alive) alive = load(j, v_s, &v_map, v_full, v_empty);
-    }
-  } else if (warp == 5) {
+    bool alive = true;
+    for (int j = 0; j < tiles && alive; ++j)
+      alive = for_keys ? load(j, k_s, &k_map, k_full, k_empty) : load(j, v_s, &v_map, v_full, v_empty);
+  } else if (warp == MMA_WARP) {
     if (lane == 0) {
-      // ---- MMA issuer
+      // ---- S = Q K^T, issued as far ahead as the two S buffers allow; the other products are
+      // issued by a thread of their own, so that neither waits behind the other's operands
       constexpr uint32_t idesc_qk = idesc_bf16(BM, BN);
-      constexpr uint32_t idesc_pv = idesc_bf16(BM, D, true);
       // descriptors differ only in their address field (bits 0..13, in units of 16 bytes): one is
       // built per operand and the others follow by adding to it
-      const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s)), p_desc0 = smem_desc_sw128(smem_u32(p_s));
-      // keys: rows are keys, groups of 8 keys GROUP_BYTES apart, the right 64 columns 1 KB further;
-      // values: the N-contiguous operand, 64-column blocks 1 KB apart, groups of 8 keys GROUP_BYTES apart
+      const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s));
+      // keys: rows are keys, groups of 8 keys GROUP_BYTES apart, the right 64 columns 1 KB further
       const uint64_t k_desc0 = smem_desc_sw128(smem_u32(k_s), 16, GROUP_BYTES);
-      const uint64_t v_desc0 = smem_desc_sw128(smem_u32(v_s), 1024, GROUP_BYTES);
-      auto issue_qk = [&](int j) -> bool {
+      for (int j = 0; j < tiles; ++j) {
         const int s = j % STAGES;
-        if (!mbar_wait(&k_full[s], (j / STAGES) & 1, a.err)) return false;
+        // the softmax threads have taken S of tile j-2 out of this buffer
+        if (j > 1 && !mbar_wait(&s_free[j & 1], ((j >> 1) - 1) & 1, a.err)) break;
+        if (!mbar_wait(&k_full[s], (j / STAGES) & 1, a.err)) break;
         tc_fence_after();
         const uint64_t k_desc = k_desc0 + (uint64_t)((s * TILE_BYTES) >> 4);
 #pragma unroll
@@ -220,13 +238,19 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
         }
         tc_commit(&s_full[j & 1]);
         tc_commit(&k_empty[s]);
-        return true;
-      };
-      bool alive = issue_qk(0);
-      for (int j = 0; j < tiles && alive; ++j) {
-        if (j + 1 < tiles) alive = issue_qk(j + 1);
-        if (!alive || !mbar_wait(&p_full, j & 1, a.err)) { alive = false; break; }
-        if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, a.err)) { alive = false; break; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == PV_WARP) {
+    if (lane == 0) {
+      // ---- O += P V
+      constexpr uint32_t idesc_pv = idesc_bf16(BM, D, true);
+      const uint64_t p_desc0 = smem_desc_sw128(smem_u32(p_s));
+      // values: the N-contiguous operand, 64-column blocks 1 KB apart, groups of 8 keys GROUP_BYTES apart
+      const uint64_t v_desc0 = smem_desc_sw128(smem_u32(v_s), 1024, GROUP_BYTES);
+      for (int j = 0; j < tiles; ++j) {
+        if (!mbar_wait(&p_full, j & 1, a.err)) break;
+        if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, a.err)) break;
         tc_fence_after();
         const uint64_t p_desc = p_desc0 + (uint64_t)(((j & 1) * P_BYTES) >> 4);
         const uint64_t v_desc = v_desc0 + (uint64_t)(((j % STAGES) * TILE_BYTES) >> 4);
@@ -263,6 +287,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld32(s_addr + c * 32, sraw[c]);
       tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s_free[j & 1]);   // the buffer may take S of tile j+2
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (masked) {   // a tile on the diagonal: compare every column with the row's position
 #pragma unroll
@@ -363,7 +389,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_free<TMEM_COLS>(tmem);
+  if (warp == MMA_WARP) tmem_free<TMEM_COLS>(tmem);
 }
 
 }  // namespace cie

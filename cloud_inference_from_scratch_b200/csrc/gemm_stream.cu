@@ -110,6 +110,35 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __device__ int timeout_sink;   // takes the time-out bit when the caller gave no error word
 
+// rstd[m] = rsqrt(sum of row_sq[m][0 .. row_tiles) / K + eps) for the MP token rows, warp w taking
+// rows w, w + warps, ...; a lane loads PER_LANE values per row at once (tiles beyond 32 * PER_LANE in
+// a loop of their own).
+template <int MP, int THREADS, int PER_LANE>
+__device__ __forceinline__ void row_rstd(const StreamArgs& a, float* rstd_s, int warp, int lane) {
+  constexpr int WARPS = THREADS / 32, ROWS = MP / WARPS;
+  float vals[ROWS][PER_LANE];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int m = warp + i * WARPS;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+      const int t = lane + 32 * j;
+      vals[i][j] = (m < a.m && t < a.row_tiles) ? __ldg(a.row_sq + (size_t)m * a.row_tiles + t) : 0.f;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int m = warp + i * WARPS;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) sum += vals[i][j];
+    if (m < a.m)
+      for (int t = lane + 32 * PER_LANE; t < a.row_tiles; t += 32) sum += a.row_sq[(size_t)m * a.row_tiles + t];
+    sum = warp_sum(sum);
+    if (lane == 0) rstd_s[m] = m < a.m ? rsqrtf(sum / (float)a.k + a.eps) : 0.f;
+  }
+}
+
 // Shared-memory layout.  cp.async variant: weight rows padded to WROW elements.  TMA variant: a
 // weight stage is two boxes of [BN rows x 64 columns] as the copy leaves them (rows of 128 bytes,
 // the 16-byte piece c of row r at position c ^ (r & 7)), stages 1024-byte aligned.
@@ -207,31 +236,11 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
     cp_async_commit();
   }
   if (a.row_sq) {
-    // rstd of every token row from the partial sums of squares (used in the epilogue, behind barriers)
-    // (every load is issued before the first sum needs one: one trip to L2, not one per value)
-    constexpr int ROWS = MP / (THREADS / 32);
-    constexpr int PER_LANE = 8;   // 256 tiles = rows of 8192 without a second pass
-    float vals[ROWS][PER_LANE];
-#pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-      const int m = warp + i * (THREADS / 32);
-#pragma unroll
-      for (int j = 0; j < PER_LANE; ++j) {
-        const int t = lane + 32 * j;
-        vals[i][j] = (m < a.m && t < a.row_tiles) ? __ldg(a.row_sq + (size_t)m * a.row_tiles + t) : 0.f;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-      const int m = warp + i * (THREADS / 32);
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < PER_LANE; ++j) sum += vals[i][j];
-      if (m < a.m)
-        for (int t = lane + 32 * PER_LANE; t < a.row_tiles; t += 32) sum += a.row_sq[(size_t)m * a.row_tiles + t];
-      sum = warp_sum(sum);
-      if (lane == 0) rstd_s[m] = m < a.m ? rsqrtf(sum / (float)a.k + a.eps) : 0.f;
-    }
+    // rstd of every token row from the partial sums of squares (used in the epilogue, behind
+    // barriers); every load is issued before the first sum needs one
+    if (a.row_tiles <= 64) row_rstd<MP, THREADS, 2>(a, rstd_s, warp, lane);
+    else if (a.row_tiles <= 128) row_rstd<MP, THREADS, 4>(a, rstd_s, warp, lane);
+    else row_rstd<MP, THREADS, 8>(a, rstd_s, warp, lane);
   }
 
   float acc[MT][4];

@@ -66,7 +66,7 @@ class TensorAttention:
         self._prefill_tc = None
         if head_dim in (64, 128) and os.environ.get("CIE_PREFILL_TC", "1") != "0":
             defines = {"HEAD_DIM": head_dim}
-            for name in ("TC_BN", "TC_STAGES"):
+            for name in ("TC_BN", "TC_STAGES", "TC_KEY_PRODUCERS", "TC_VALUE_PRODUCERS"):
                 if os.environ.get("CIE_" + name):
                     defines[name] = int(os.environ["CIE_" + name])
             tc = _Lib(load_library("attention_prefill_tc.cu", defines))
