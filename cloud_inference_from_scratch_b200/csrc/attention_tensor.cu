@@ -1,15 +1,18 @@
 // Tensor-core attention over the paged cache for bfloat16, one head size per build (-DHEAD_DIM).
 //
 //  * prefill_kernel: ragged causal attention of prompt portions (cached prefix + the portion
-//    itself).  One CTA takes a tile of query rows of ONE request and ONE kv head; a row is a
-//    (token, query head of the group) pair, so the heads of a group share every K/V load.
-//    K/V tiles of 64 keys are gathered row by row from the pages with cp.async (any page
-//    size), double buffered; QK^T and PV run on mma.sync m16n8k16 with float32 accumulators
-//    and a float32 running-maximum softmax.
-//  * decode_kernel + combine_kernel: one query token per request.  The keys of a request are
-//    split over CTAs (grid.x) and, inside a CTA, over 4 warps that each stream 16-key tiles
-//    through a private double buffer; partial (max, sum, output) triples are merged in shared
-//    memory, then across CTAs by combine_kernel through a float32 scratch buffer.
+//    itself) on mma.sync, for what the tcgen05 kernel (attention_prefill_tc.cu) does not take:
+//    head sizes other than 64 and 128, windows, pages that are no multiple of 16 tokens.  One CTA
+//    takes a tile of 128 query rows of ONE request and ONE kv head; a row is a (token, query head
+//    of the group) pair, so the heads of a group share every K/V load.  K/V tiles of 64 keys are
+//    gathered row by row from the pages with bulk asynchronous copies (any page size), double
+//    buffered; QK^T and PV run on mma.sync m16n8k16 with float32 accumulators and a float32
+//    running-maximum softmax.
+//  * decode_kernel: one query token per request.  The keys of a request are split over the CTAs
+//    of a thread-block cluster and, inside a CTA, over 12 warps that each stream 16-key tiles
+//    through private stages (TMA tensor copies where pages, head size and window allow, else
+//    cp.async); partial (max, sum, output) triples are merged in shared memory, then across the
+//    cluster through distributed shared memory.
 //
 // Formula: zeeshan8281/cloud-inference-from-scratch src/cloud_engine/kernel.py:324-405 (one
 // program per query token and head, CUDA-core reductions, page size fixed at 16, head size
@@ -32,18 +35,19 @@ namespace cie {
 
 namespace cg = cooperative_groups;
 using bf16 = __nv_bfloat16;
+using bw::mbar_expect_tx;
+using bw::mbar_init;
+using bw::mbar_wait;
+using bw::smem_u32;
+using bw::tma_load_2d;
 constexpr int D = HEAD_DIM;
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
 constexpr int ROW = D + 8;          // shared-memory row in elements: odd number of 16-byte units
 constexpr int CHUNKS = D / 8;       // 16-byte pieces of a row
 constexpr int KSTEPS = D / 16;
 constexpr int NTILES_D = D / 8;
-constexpr int kErrTimeout = 8;
 constexpr uint32_t ROW_BYTES = D * sizeof(__nv_bfloat16);
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros, nothing is read
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
@@ -52,32 +56,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// ---- bulk asynchronous copies (TMA without a tensor map) completing on an mbarrier
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up (error bit, false) after about two seconds.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > 4000000000ll) {
-      atomicOr(err, kErrTimeout);
-      return false;
-    }
-  }
-  return true;
-}
 __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -500,11 +478,6 @@ __device__ __forceinline__ void load_kv_tile_warp(const DecodeArgs& a, const int
   }
 }
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
 
 // kTma == false: keys and values come through the load/store unit (cp.async), any page size and
 // window.  kTma == true: each 16-key tile is fetched by one lane with D/64 tensor copies per
@@ -767,43 +740,6 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
 }
 
 // ------------------------------------------------------------------------------------ tensor maps
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                CUtensorMapFloatOOBfill);
-
-// Tensor map of one layer's key (or value) pool seen as a matrix [pages * kv_heads * page_size, D],
-// read in boxes of 16 rows x 64 columns with 128-byte swizzle.  Maps are kept by pool address.
-static bool pool_map(const void* pool, long long rows, CUtensorMap* out) {
-  struct Entry { const void* pool; long long rows; CUtensorMap map; };
-  static Entry cache[512];
-  static int used = 0;
-  for (int i = 0; i < used; ++i)
-    if (cache[i].pool == pool && cache[i].rows == rows) { *out = cache[i].map; return true; }
-  static EncodeTiled encode = nullptr;
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess ||
-        status != cudaDriverEntryPointSuccess)
-      return false;
-    encode = reinterpret_cast<EncodeTiled>(fn);
-  }
-  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(bf16)};
-  cuuint32_t box[2] = {64, 16};
-  cuuint32_t elem[2] = {1, 1};
-  CUtensorMap map;
-  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, elem,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return false;
-  if (used == 512) used = 0;
-  cache[used++] = Entry{pool, rows, map};
-  *out = map;
-  return true;
-}
-
 }  // namespace cie
 
 using namespace cie;
@@ -905,7 +841,7 @@ extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int 
     const long long rows = (long long)num_pages * kv_heads * page_size;
     const bool mapped = kBlockCopies
         ? bw::tensor_map_bf16_row_blocks(k_pool, rows, D, 16, &k_map) && bw::tensor_map_bf16_row_blocks(v_pool, rows, D, 16, &v_map)
-        : pool_map(k_pool, rows, &k_map) && pool_map(v_pool, rows, &v_map);
+        : bw::tensor_map_bf16(k_pool, rows, D, 16, &k_map) && bw::tensor_map_bf16(v_pool, rows, D, 16, &v_map);
     if (!mapped)
       CIE_FAIL("attention_decode: cuTensorMapEncodeTiled failed");
     return launch_decode<true>(k_map, v_map, a, requests, (cudaStream_t)stream);

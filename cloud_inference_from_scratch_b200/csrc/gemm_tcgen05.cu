@@ -17,19 +17,15 @@
 //
 // The reference runs these products through cuBLAS (zeeshan8281/cloud-inference-from-scratch
 // src/cloud_engine/model.py:100,134-136,217,227).
+#include "blackwell.cuh"
 #include "common.cuh"
-
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
 
 CIE_DEFINE_LAST_ERROR()
 
 namespace cie {
 
+using namespace bw;
 using bf16 = __nv_bfloat16;
-constexpr int kErrTimeout = 8;
 
 constexpr int BM = 128;              // rows of the A operand per tile (UMMA M)
 constexpr int BK = 64;               // K per stage: 64 bf16 = 128 bytes = one swizzle row
@@ -38,61 +34,8 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;
 
 constexpr int kOutBF16 = 0, kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: false (and an error bit) if the phase did not complete within ~2 s of cycles.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long start = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - start > 4000000000ll) {
-      atomicOr(err, kErrTimeout);
-      return false;
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t desc = 0;
-  desc |= (uint64_t)((addr & 0x3FFFF) >> 4);   // start address
-  desc |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major)
-  desc |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
-  desc |= (uint64_t)1 << 46;                   // descriptor version of sm_100
-  desc |= (uint64_t)2 << 61;                   // SWIZZLE_128B
-  return desc;
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -143,16 +86,15 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&acc_bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 0) {
     __syncwarp();
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    tmem_alloc<TMEM_COLS>(&tmem_base_s);
   }
-  tcgen05_fence_before();
+  tc_fence_before();
   __syncthreads();
-  tcgen05_fence_after();
+  tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
   if (warp == 0) {
@@ -173,30 +115,30 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      constexpr uint32_t idesc = idesc_bf16(BM, BN);
       bool alive = true;
       for (int kt = 0; kt < k_tiles && alive; ++kt) {
         const int s = kt % STAGES;
         const uint32_t phase = (kt / STAGES) & 1;
         if (!mbar_wait(&full_bar[s], phase, a.err)) { alive = false; break; }
-        tcgen05_fence_after();
+        tc_fence_after();
         const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-        const uint64_t a_desc = smem_desc(a_addr), b_desc = smem_desc(a_addr + A_STAGE_BYTES);
+        const uint64_t a_desc = smem_desc_sw128(a_addr), b_desc = smem_desc_sw128(a_addr + A_STAGE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
           // advancing 16 elements (32 bytes) inside the swizzled row: +2 in 16-byte units
           umma_bf16(tmem_base, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (kt > 0 || kk > 0) ? 1u : 0u);
         }
-        tcgen05_commit(&empty_bar[s]);
+        tc_commit(&empty_bar[s]);
       }
-      tcgen05_commit(&acc_bar);
+      tc_commit(&acc_bar);
     }
     __syncwarp();
   }
 
   // ---- epilogue: warp w reads tensor-memory lanes 32w .. 32w+31 (rows of the A operand)
   const bool ready = k_tiles > 0 ? mbar_wait(&acc_bar, 0, a.err) : true;
-  tcgen05_fence_after();
+  tc_fence_after();
   const int a_row = a_row0 + warp * 32 + lane;
   if (ready) {
 #pragma unroll 1
@@ -277,68 +219,14 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     // a wait ran out: give copies that may still be in flight time to land before leaving
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   }
-  tcgen05_fence_before();
+  tc_fence_before();
   __syncthreads();
   if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    tmem_free<TMEM_COLS>(tmem_base);
   }
 }
 
 // ------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_tiled() {
-  static EncodeTiled fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult status;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
-        status == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiled>(ptr);
-  }
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr;
-  int rows, cols, box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ ((size_t)k.box_rows << 20);
-  }
-};
-
-// Tensor map of a row-major bfloat16 matrix [rows, cols] read in boxes of [box_rows, 64] with
-// 128-byte swizzle; parts of a box outside the matrix read as zero.
-static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  static std::mutex lock;
-  const MapKey key{ptr, rows, cols, box_rows};
-  std::lock_guard<std::mutex> guard(lock);
-  auto found = cache.find(key);
-  if (found != cache.end()) { *out = found->second; return true; }
-  EncodeTiled encode = encode_tiled();
-  if (!encode) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(bf16)};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUtensorMap map;
-  CUresult status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
-                           box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (status != CUDA_SUCCESS) return false;
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, map);
-  *out = map;
-  return true;
-}
-
 template <int BN, int STAGES>
 static int launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcArgs& a, dim3 grid, cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (A_STAGE_BYTES + BN * BK * 2) + 1024;
@@ -379,13 +267,13 @@ extern "C" int cie_gemm_tcgen05(const void* x, const void* w, const float* bias,
   CUtensorMap map_a, map_b;
   if (swapped) {
     const int bn = m <= 16 ? 16 : m <= 32 ? 32 : 64;
-    if (!tensor_map(w, n, k, BM, &map_a) || !tensor_map(x, m, k, bn, &map_b)) CIE_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed");
+    if (!tensor_map_bf16(w, n, k, BM, &map_a) || !tensor_map_bf16(x, m, k, bn, &map_b)) CIE_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed");
     dim3 grid((n + BM - 1) / BM, 1, splits);
     if (bn == 16) return launch<16, 8>(map_a, map_b, a, grid, s);
     if (bn == 32) return launch<32, 8>(map_a, map_b, a, grid, s);
     return launch<64, 6>(map_a, map_b, a, grid, s);
   }
-  if (!tensor_map(x, m, k, BM, &map_a) || !tensor_map(w, n, k, 128, &map_b)) CIE_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed");
+  if (!tensor_map_bf16(x, m, k, BM, &map_a) || !tensor_map_bf16(w, n, k, 128, &map_b)) CIE_FAIL("gemm_tcgen05: cuTensorMapEncodeTiled failed");
   dim3 grid((m + BM - 1) / BM, (n + 127) / 128, 1);
   return launch<128, 3>(map_a, map_b, a, grid, s);
 }
