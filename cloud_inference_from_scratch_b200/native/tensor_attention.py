@@ -1,9 +1,11 @@
-"""Python side of the tensor-core attention kernels (csrc/attention_tensor.cu), one build per head size.
+"""Python side of the tensor-core attention kernels (csrc/attention_tensor.cu and
+csrc/attention_prefill_tc.cu), one build per head size.
 
-``plan`` turns a step's request lengths into the tile list of the prefill kernel (on the host,
+``plan`` turns a step's request lengths into the tile list of the prefill kernels (on the host,
 with numpy; it rides in the step's single metadata copy).  ``run`` picks the kernel: a step in
-which every request brings exactly one token goes to the split-key decode kernel, any other
-step to the prefill kernel.
+which every request brings exactly one token goes to the split-key decode kernel; any other
+step to the tcgen05 prefill kernel where it exists (head size 64 or 128, no window, pages of a
+multiple of 16 tokens), else to the mma.sync prefill kernel.
 """
 
 from __future__ import annotations
