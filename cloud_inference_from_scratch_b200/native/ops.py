@@ -166,6 +166,11 @@ class Ops:
         )
         self._sample = None   # sampling.cu is built when something is first sampled
         self._tensor_gemm = None
+        self._fold_gemm_held = None
+        # from this many rows on, projections fold the residual add / the norm / the activation
+        # into the persistent tcgen05 kernel instead of running library products and separate
+        # kernels (0: never)
+        self.fold_rows = int(os.environ.get("CIE_FOLD_ROWS", "0"))
         self._tensor_attention: dict[int, Any] = {}
         self._gemm_stream = None
         self._gemm_stream_ex = None
@@ -316,6 +321,10 @@ class Ops:
         if m == 0:
             return out
         plan = self.stream_plan(m, n, k, allow_partials) if self.code == BF16 else None
+        if plan is None and self.code == BF16 and self.fold_rows and m >= self.fold_rows:
+            done = self._linear_folded(x, weight, bias, out, m, n, k, allow_partials, tag, residual)
+            if done is not None:
+                return done
         if plan is None and isinstance(x, NormedInput):
             x = x.materialize()
         if plan is not None:
@@ -354,6 +363,40 @@ class Ops:
         self._gemm_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k, self._code_of(x),
                         self._code_of(out), 0 if self.code == F32 else 1, self.stream)
         return out
+
+    def _fold_gemm(self) -> Any:
+        if self._tensor_gemm is not None:
+            return self._tensor_gemm
+        if self._fold_gemm_held is None:
+            from .tensor_gemm import TensorGemm
+
+            self._fold_gemm_held = TensorGemm(self)
+        return self._fold_gemm_held
+
+    def _linear_folded(self, x: Any, weight: Any, bias: Any, out: Any, m: int, n: int, k: int,
+                       allow_partials: bool, tag: str, residual: Any) -> Any:
+        """Many rows on the persistent tcgen05 kernel where that saves a whole pass over the
+        activations: a projection that adds itself into the residual stream, or a product whose
+        input rows are still to be divided by their root mean square.  None: not its case."""
+        gemm = self._fold_gemm()
+        if k % 8 or weight.data_ptr() % 16:
+            return None
+        if isinstance(x, NormedInput):
+            acc = x.accumulated
+            gemm.launch_fused(acc.scaled, weight, bias, out, 1 if out.dtype == self.torch.float32 else 0,
+                              row_sq=acc.sq, row_tiles=acc.tiles, eps=x.eps)
+            return out
+        if residual is not None and allow_partials and self.fuse_norm and x.data_ptr() % 16 == 0:
+            tiles = -(-n // 32)
+            sq = self.scratch("sq.rows." + (tag or "linear"), m * tiles)
+            gain = residual.gain if n % 8 == 0 else None
+            scaled = None
+            if gain is not None:
+                scaled = self.scratch("scaled.rows." + (tag or "linear"), (m * n + 1) // 2)
+                scaled = scaled.view(self.torch.bfloat16)[: m * n].view(m, n)
+            gemm.launch_fused(x, weight, bias, None, 4, residual=residual.tensor, sq=sq, scaled=scaled, next_gain=gain)
+            return Accumulated(residual.tensor, sq, tiles, scaled, gain)
+        return None
 
     def resolve(self, value: Any, out: Any) -> Any:
         """A plain tensor for a part that cannot consume ``Partials`` itself."""
@@ -394,6 +437,12 @@ class Ops:
             if plan is not None:
                 self._stream(x, weight.weight, None, hidden_out, m, 2 * inter, k, 1, 3)
                 return hidden_out
+        if (isinstance(x, NormedInput) and self.code == BF16 and weight.block == 16 and self.fold_rows
+                and m >= self.fold_rows and k % 8 == 0):
+            acc = x.accumulated
+            self._fold_gemm().launch_fused(acc.scaled, weight.weight, None, hidden_out, 3, row_sq=acc.sq,
+                                              row_tiles=acc.tiles, eps=x.eps)
+            return hidden_out
         if isinstance(x, NormedInput):
             x = x.materialize()
         both = workspace.get("swiglu.gate_up", m, 2 * inter, self.dtype)

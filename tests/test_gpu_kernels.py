@@ -763,3 +763,49 @@ def test_rope_kv_write_many_tokens_in_place(ops, dim, rot, page):
         page_id = int(table[r, pos // page])
         torch.testing.assert_close(k_pool[page_id, :, pos % page].float().cpu(), want_k[t], **tol(torch.bfloat16))
         assert torch.equal(v_pool[page_id, :, pos % page].float().cpu(), src[t, q_heads + kv_heads:])
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 2048, 2048), (300, 1000, 520), (129, 331 * 32, 96)])
+def test_gemm_tcgen05_persistent_folds_norm_activation_and_residual(tensor_ops, m, n, k):
+    """More than 64 rows: the residual epilogue leaves new residual rows, their sums of squares and
+    the rows times a gain; the next product scales its result rows by rstd, with a plain output and
+    with SiLU(gate) * up."""
+    item = tensor_ops
+    gemm = item._tensor_gemm
+    x = rand(m, k, dtype=torch.bfloat16, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n)
+    bias = rand(n, seed=3)
+    before = rand(m, n, seed=5)
+    residual = before.clone()
+    gain = 1 + rand(n, scale=0.1, seed=4)
+    tiles = -(-n // 32)
+    sq = torch.full((m, tiles), float("nan"), dtype=torch.float32).cuda()
+    scaled = torch.full((m, n), float("nan"), dtype=torch.bfloat16).cuda() if n % 8 == 0 else None
+    gemm.launch_fused(x, w, bias, None, 4, residual=residual, sq=sq, scaled=scaled,
+                      next_gain=gain if scaled is not None else None)
+    item.check_errors()
+    want = before + plain_model.linear(x.float().cpu(), w.float().cpu(), bias.cpu()).cuda()
+    top = max(1.0, float(want.abs().max()))
+    torch.testing.assert_close(residual, want, rtol=2e-3, atol=2e-3 * top)
+    torch.testing.assert_close(sq.sum(-1), residual.pow(2).sum(-1), rtol=1e-4, atol=1e-4)
+    if scaled is None:
+        return
+    torch.testing.assert_close(scaled.float(), (residual * gain).to(torch.bfloat16).float(), rtol=0, atol=0)
+    eps = 1e-5
+    normed = plain_model.rms_norm(residual.cpu(), gain.cpu(), eps)
+    w2 = rand(416, n, dtype=torch.bfloat16, scale=0.05, seed=7)
+    out = torch.full((m, 416), float("nan"), dtype=torch.float32).cuda()
+    gemm.launch_fused(scaled, w2, None, out, 1, row_sq=sq, row_tiles=tiles, eps=eps)
+    item.check_errors()
+    want2 = normed @ w2.float().cpu().t()
+    torch.testing.assert_close(out.cpu(), want2, rtol=2e-2, atol=2e-2 * max(1.0, float(want2.abs().max()) / 4))
+    inter = 208
+    gate = rand(inter, n, dtype=torch.bfloat16, scale=0.05, seed=8)
+    up = rand(inter, n, dtype=torch.bfloat16, scale=0.05, seed=9)
+    stacked = item.prepare_gate_up(gate, up)
+    assert stacked.block == 16
+    hidden = torch.full((m, inter), float("nan"), dtype=torch.bfloat16).cuda()
+    gemm.launch_fused(scaled, stacked.weight, None, hidden, 3, row_sq=sq, row_tiles=tiles, eps=eps)
+    item.check_errors()
+    want3 = torch.nn.functional.silu(normed @ gate.float().cpu().t()) * (normed @ up.float().cpu().t())
+    torch.testing.assert_close(hidden.float().cpu(), want3, rtol=2e-2, atol=2e-2 * max(1.0, float(want3.abs().max()) / 4))
