@@ -42,7 +42,10 @@ namespace cg = cooperative_groups;
 using bf16 = __nv_bfloat16;
 constexpr int BK = 128;
 constexpr int WROW = BK + 8;
-constexpr int STAGES = 4;
+// Pipeline depth: four stages for up to 8 tokens; three for 9..16, whose larger x tiles would
+// otherwise cost an SM one resident CTA (and a wide product a second wave).
+template <int MT>
+constexpr int stages_for() { return MT == 1 ? 4 : 3; }
 constexpr int KSTEPS = BK / 16;
 
 using bw::smem_u32;
@@ -152,6 +155,7 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
   constexpr int MP = MT * 8;        // padded token count
   constexpr int WSTAGE = w_stage_elems<BN, TMA>();
   constexpr int XSTAGE = MP * WROW * 2;
+  constexpr int STAGES = stages_for<MT>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem_base = TMA ? reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
                                  : smem_raw;
@@ -444,7 +448,7 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
 template <int MT, int BN, bool TMA>
 static int launch_variant(const CUtensorMap& w_map, const StreamArgs& a, int splits, cudaStream_t stream) {
   constexpr int MP = MT * 8;
-  constexpr size_t pipeline = (size_t)STAGES * (w_stage_elems<BN, TMA>() + MP * WROW) * sizeof(bf16);
+  constexpr size_t pipeline = (size_t)stages_for<MT>() * (w_stage_elems<BN, TMA>() + MP * WROW) * sizeof(bf16);
   constexpr size_t staging = (size_t)MP * (BN + 1) * sizeof(float);
   constexpr size_t smem = (pipeline > staging ? pipeline : staging) + (TMA ? 1024 : 0);
   static bool configured = false;

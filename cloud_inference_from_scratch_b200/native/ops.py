@@ -98,9 +98,9 @@ class GateUpWeight:
 
 SM_COUNT = 148
 STREAM_MAX_ROWS = 16   # more rows than this go to the tile kernels (tcgen05 or the library)
-# Up to this many rows a projection adds itself into the residual stream (cluster epilogue of the
-# streaming kernel); measured on B200, 9..16 rows are faster with partial sums and the norm kernel.
-FUSED_RESIDUAL_MAX_ROWS = 8
+# Up to this many rows a projection adds itself into the residual stream, or rotates and stores
+# q/k/v (cluster epilogues of the streaming kernel): every row count that kernel takes.
+FUSED_RESIDUAL_MAX_ROWS = STREAM_MAX_ROWS
 
 
 class _Lib:

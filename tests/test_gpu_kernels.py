@@ -544,7 +544,7 @@ def test_prefill_attention_tcgen05_far_key(ops):
 
 
 # ------------------------------------------------------------------ residual epilogue and normed input
-@pytest.mark.parametrize("m", [1, 5, 8])
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
 @pytest.mark.parametrize("n,k", [(2048, 2048), (2048, 11008), (331, 96), (1000, 520)])
 def test_gemm_stream_adds_into_the_residual_and_feeds_the_next_product(ops, m, n, k):
     """A projection adds itself into the float32 residual stream (its K slices are one cluster) and
@@ -643,7 +643,7 @@ def rotary_want(x, w, bias, positions, q_heads, kv_heads, dim, rot, theta):
 
 
 @pytest.mark.parametrize("q_heads,kv_heads,dim,rot,page", [(16, 2, 128, 128, 16), (6, 3, 64, 32, 8), (4, 4, 96, 64, 32)])
-@pytest.mark.parametrize("tokens", [1, 5, 8])
+@pytest.mark.parametrize("tokens", [1, 5, 8, 11, 16])
 def test_qkv_projection_rotates_and_stores_in_its_own_kernel(ops, q_heads, kv_heads, dim, rot, page, tokens):
     """Decode tokens: q comes back rotated in the natural order, k and v land in the right slot of
     the right page, nothing else in the pools changes; with write_cache off the pools stay as
@@ -653,7 +653,7 @@ def test_qkv_projection_rotates_and_stores_in_its_own_kernel(ops, q_heads, kv_he
     assert item.can_pair_rotary(dim, rot)
     w, bias, w_paired, bias_paired = paired_projection(item, q_heads, kv_heads, dim, rot, hidden, seed=tokens)
     x = rand(tokens, hidden, dtype=torch.bfloat16, seed=9)
-    lengths = [1, 8, 16, 17, 301, 64, 33, 100][:tokens]
+    lengths = [1, 8, 16, 17, 301, 64, 33, 100, 2, 129, 48, 257, 31, 32, 5, 77][:tokens]
     positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32).cuda()
     request = torch.arange(tokens, dtype=torch.int32).cuda()
     k_pool, v_pool, table, _, total = paged_setup(lengths, page, kv_heads, dim, torch.bfloat16)
