@@ -4,7 +4,9 @@
 // One CTA takes 128 query rows of ONE request and ONE kv head; a row is a (token, query head of the
 // group) pair, so the heads of a group share every key and value.  Keys go by in tiles of 128:
 //
-//   TMA warps     key/value pages -> shared memory, one copy per 16 keys (a 4-dimensional box
+//   TMA warps     key/value pages -> shared memory: one copy per tile where the tile's pages follow
+//                 each other in the pool (a 5-dimensional box over consecutive pages of one kv
+//                 head), else one copy per 16 keys (a 4-dimensional box
 //                 that leaves every 8 keys as two swizzled 8 x 64 pieces side by side: few, large
 //                 copies, because the TMA unit's rate of copies bounds this kernel); two stages of keys and two of values, each with its own mbarriers, so
 //                 the keys of tile j+2 are on their way while the values of tile j are still in use.
@@ -104,10 +106,14 @@ struct Args {
   int group, hpt, tpt, head_chunks;
   float scale_log2;
   int* err;
+  // one copy per tile when the pages of a tile follow each other in the pool (0: never):
+  int run_pages;           // pages a tile spans (1 if a page holds several tiles)
 };
 
 __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                  const __grid_constant__ CUtensorMap v_map,
+                                                                 const __grid_constant__ CUtensorMap k_run_map,
+                                                                 const __grid_constant__ CUtensorMap v_run_map,
                                                                  const Args a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -193,12 +199,38 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
       return (page * a.kv_heads + kvh) * a.page_size + key % a.page_size;
     };
     auto blocks_of = [&](int j) { return min(BN / 16, (valid_hi - tile_of(j) * BN + 15) / 16); };
-    auto load = [&](int j, unsigned char* ring, const CUtensorMap* map, uint64_t* full, uint64_t* empty) -> bool {
+    auto page_at = [&](int key) -> int {
+      const int index = key / a.page_size;
+      return index >= a.table_width ? -1 : index < TABLE_SLOTS ? pages_s[index] : table_row[index];
+    };
+    auto load = [&](int j, unsigned char* ring, const CUtensorMap* map, const CUtensorMap* run_map, uint64_t* full,
+                    uint64_t* empty) -> bool {
       const int s = j % STAGES;
       const int blocks = blocks_of(j);
-      const bool mine = lane < per_warp && block < blocks;
+      const int k0 = tile_of(j) * BN;
+      // Do the pages of this tile follow each other in the pool?  Then one copy brings the tile.
+      bool run = a.run_pages > 0;
+      int first_page = 0;
+      if (run) {
+        const int page = lane < blocks ? page_at(k0 + lane * 16) : 0;
+        first_page = __shfl_sync(0xffffffffu, page, 0);
+        const bool follows = lane >= blocks || page == first_page + (lane * 16) / a.page_size;
+        run = __all_sync(0xffffffffu, follows) && first_page >= 0 && first_page < a.num_pages;
+      }
+      const bool mine = !run && lane < per_warp && block < blocks;
       const int row = mine ? block_row(j) : 0;
       if (j >= STAGES && !mbar_wait(&empty[s], ((j / STAGES) - 1) & 1, a.err)) return false;
+      if (run) {
+        if (part == 0 && lane == 0) {
+          // the whole box counts, also where it reaches past the keys in use or past the pool's end
+          mbar_expect_tx(&full[s], TILE_BYTES);
+          const int group = kvh * (a.page_size / 8) + (k0 % a.page_size) / 8;
+          if constexpr (HALVES == 2) tma_load_5d(ring + s * TILE_BYTES, run_map, &full[s], 0, 0, 0, group, first_page);
+          else tma_load_4d(ring + s * TILE_BYTES, run_map, &full[s], 0, 0, group, first_page);
+        }
+        __syncwarp();
+        return true;
+      }
       // the first warp of the ring announces the bytes of the whole tile (a copy of another warp
       // may complete before that: the phase still waits for this arrival)
       if (part == 0 && lane == 0) mbar_expect_tx(&full[s], (uint32_t)blocks * 16u * D * 2u);
@@ -212,7 +244,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
     };
     bool alive = true;
     for (int j = 0; j < tiles && alive; ++j)
-      alive = for_keys ? load(j, k_s, &k_map, k_full, k_empty) : load(j, v_s, &v_map, v_full, v_empty);
+      alive = for_keys ? load(j, k_s, &k_map, &k_run_map, k_full, k_empty) : load(j, v_s, &v_map, &v_run_map, v_full, v_empty);
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
       // ---- S = Q K^T, issued as far ahead as the two S buffers allow; the other products are
@@ -428,6 +460,21 @@ extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, 
   // the pools as matrices [pages * kv_heads * page_size, D], read in blocks of 16 whole rows
   if (!tensor_map_bf16_row_blocks(k_pool, rows, D, 16, &k_map) || !tensor_map_bf16_row_blocks(v_pool, rows, D, 16, &v_map))
     CIE_FAIL("attention_prefill_tc: cuTensorMapEncodeTiled failed");
+  // copies of whole tiles, for tiles whose pages follow each other in the pool
+  CUtensorMap k_run = k_map, v_run = v_map;
+  a.run_pages = 0;
+  {
+    int run_pages = 0, groups = 0;
+    if (page_size <= BN && BN % page_size == 0) { run_pages = BN / page_size; groups = page_size / 8; }
+    else if (page_size > BN && page_size % BN == 0) { run_pages = 1; groups = BN / 8; }
+    static const bool allowed = [] {
+      const char* value = getenv("CIE_TC_RUNS");
+      return !(value && value[0] == '0');
+    }();
+    if (allowed && run_pages > 0 && tensor_map_bf16_page_runs(k_pool, num_pages, kv_heads, page_size, D, groups, run_pages, &k_run) &&
+        tensor_map_bf16_page_runs(v_pool, num_pages, kv_heads, page_size, D, groups, run_pages, &v_run))
+      a.run_pages = run_pages;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t status = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -435,6 +482,6 @@ extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, 
     configured = true;
   }
   dim3 grid(num_tiles, kv_heads * a.head_chunks);
-  CIE_LAUNCH("attention_prefill_tc", prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, k_map, v_map, a);
+  CIE_LAUNCH("attention_prefill_tc", prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a);
   return 0;
 }

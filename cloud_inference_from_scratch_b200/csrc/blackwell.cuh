@@ -63,6 +63,11 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z, int w, int v) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(v) : "memory");
+}
 // Orders this thread's ordinary shared-memory writes before later reads or writes of the same
 // bytes by TMA or the tensor cores.
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -233,6 +238,64 @@ inline bool tensor_map_bf16_row_blocks(const void* ptr, long long rows, int cols
     cuuint64_t strides[2] = {row_bytes, 8 * row_bytes};
     cuuint32_t box[3] = {64, 8, (cuuint32_t)(block_rows / 8)};
     status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (status != CUDA_SUCCESS) return false;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, map);
+  *out = map;
+  return true;
+}
+
+// Tensor map of a paged key (or value) pool [pages][kv_heads][page_size][cols] (bfloat16, cols 64 or
+// 128, page_size a multiple of 8) for copies that span `run_pages` consecutive pages of ONE kv head,
+// `groups` groups of 8 rows from each: what a copy leaves in shared memory is the layout of
+// tensor_map_bf16_row_blocks (per 8 rows the left 8 x 64 columns, then the right ones), page after
+// page.  Coordinates of a copy: (0, 0, [0,] kv_head * page_size / 8 + first group in the page, first page).
+inline bool tensor_map_bf16_page_runs(const void* ptr, long long num_pages, int kv_heads, int page_size, int cols,
+                                      int groups, int run_pages, CUtensorMap* out) {
+  struct Key {
+    const void* ptr; long long pages; int heads, page, cols, groups, run;
+    bool operator==(const Key& o) const {
+      return ptr == o.ptr && pages == o.pages && heads == o.heads && page == o.page && cols == o.cols &&
+             groups == o.groups && run == o.run;
+    }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.pages) * 31) ^ ((size_t)k.heads * 131) ^
+             ((size_t)k.page * 1031) ^ ((size_t)k.cols * 7) ^ ((size_t)k.groups * 8191) ^ ((size_t)k.run * 65537);
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex lock;
+  if ((cols != 64 && cols != 128) || page_size % 8 || groups < 1 || groups > 256 || run_pages < 1 || run_pages > 256 ||
+      groups > page_size / 8)
+    return false;
+  const Key key{ptr, num_pages, kv_heads, page_size, cols, groups, run_pages};
+  std::lock_guard<std::mutex> guard(lock);
+  auto found = cache.find(key);
+  if (found != cache.end()) { *out = found->second; return true; }
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) return false;
+  const cuuint64_t row_bytes = (cuuint64_t)cols * 2;
+  const cuuint64_t groups_per_page = (cuuint64_t)kv_heads * (page_size / 8);
+  CUtensorMap map;
+  CUresult status;
+  cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+  if (cols == 128) {
+    cuuint64_t dims[5] = {64, 8, 2, groups_per_page, (cuuint64_t)num_pages};
+    cuuint64_t strides[4] = {row_bytes, 128, 8 * row_bytes, groups_per_page * 8 * row_bytes};
+    cuuint32_t box[5] = {64, 8, 2, (cuuint32_t)groups, (cuuint32_t)run_pages};
+    status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[4] = {64, 8, groups_per_page, (cuuint64_t)num_pages};
+    cuuint64_t strides[3] = {row_bytes, 8 * row_bytes, groups_per_page * 8 * row_bytes};
+    cuuint32_t box[4] = {64, 8, (cuuint32_t)groups, (cuuint32_t)run_pages};
+    status = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }

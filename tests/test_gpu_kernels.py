@@ -69,12 +69,20 @@ def test_add_rmsnorm(ops, dtype, hidden):
     torch.testing.assert_close(out3.float(), expect[rows.long()], **tol(dtype))
 
 
-def paged_setup(lengths, page, heads, dim, dtype, seed=0, extra_pages=3):
-    """Random keys/values scattered over a shuffled page pool; returns pools, tables, dense copies."""
+def paged_setup(lengths, page, heads, dim, dtype, seed=0, extra_pages=3, pages="shuffled"):
+    """Random keys/values scattered over a page pool; returns pools, tables, dense copies.
+    ``pages``: "shuffled" (every page anywhere), "consecutive" (a request's pages follow each other,
+    as a fresh allocator hands them out) or "runs" (consecutive except that every fifth page is
+    swapped with its neighbour)."""
     generator = torch.Generator().manual_seed(seed)
     pages_per = [-(-n // page) for n in lengths]
     total = sum(pages_per) + extra_pages
     order = torch.randperm(total, generator=generator).tolist()
+    if pages != "shuffled":
+        order = list(range(total))
+        if pages == "runs":
+            for i in range(4, total - 1, 5):
+                order[i], order[i + 1] = order[i + 1], order[i]
     width = max(pages_per) + 1
     table = torch.full((len(lengths), width), -1, dtype=torch.int32)
     k_pool = torch.zeros(total, heads, page, dim)
@@ -197,9 +205,9 @@ def test_silu_mul(ops, dtype):
 
 
 def attention_case(ops, dtype, contexts, query_lens, q_heads, kv_heads, dim, page, window=0, seed=0,
-                   plant=None, fn="attention_generic"):
+                   plant=None, fn="attention_generic", pages="shuffled"):
     lengths = [c + q for c, q in zip(contexts, query_lens)]
-    k_pool, v_pool, table, dense, total = paged_setup(lengths, page, kv_heads, dim, dtype, seed=seed)
+    k_pool, v_pool, table, dense, total = paged_setup(lengths, page, kv_heads, dim, dtype, seed=seed, pages=pages)
     tokens = sum(query_lens)
     q = rand(tokens, q_heads * dim, dtype=dtype, seed=seed + 1)
     if plant is not None:   # make one far key the only one that matters for the last query
@@ -809,3 +817,14 @@ def test_gemm_tcgen05_persistent_folds_norm_activation_and_residual(tensor_ops, 
     item.check_errors()
     want3 = torch.nn.functional.silu(normed @ gate.float().cpu().t()) * (normed @ up.float().cpu().t())
     torch.testing.assert_close(hidden.float().cpu(), want3, rtol=2e-2, atol=2e-2 * max(1.0, float(want3.abs().max()) / 4))
+
+
+@pytest.mark.parametrize("pages", ["consecutive", "runs"])
+@pytest.mark.parametrize("dim,page,q_heads,kv_heads", [(128, 16, 16, 2), (64, 16, 14, 2), (128, 64, 8, 8), (64, 256, 4, 1), (128, 32, 7, 1)])
+def test_prefill_attention_tcgen05_with_pages_in_a_row(ops, dim, page, q_heads, kv_heads, pages):
+    """Where the pages of a 128-key tile follow each other in the pool the kernel fetches the tile
+    with one copy (also past the keys in use and past the pool's end); where they do not, page by
+    page.  Both in one launch: some tiles of "runs" are in a row, some are not."""
+    tensor_case(ops, dim, [0, 127, 128, 300, 0], [129, 2, 256, 77, 1], q_heads, kv_heads, dim, page, seed=21, pages=pages)
+    tensor_case(ops, dim, [1000, 0], [3, 640], q_heads, kv_heads, dim, page, seed=22, pages=pages)
+    tensor_case(ops, dim, [1700, 10], [300, 4], q_heads, kv_heads, dim, page, seed=23, plant=(0, 1663, 4.0), pages=pages)
