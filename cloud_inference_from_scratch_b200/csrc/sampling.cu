@@ -24,13 +24,58 @@ __device__ __forceinline__ float uniform_from_key(unsigned long long x) {
   return (float)(x >> 40) * (1.0f / 16777216.0f);
 }
 
+constexpr int kSlices = 16;          // CTAs that search one row's maximum
+constexpr int kSliceThreads = 256;
+
+// First pass over the logits, spread over kSlices CTAs a row (one CTA reading a whole row of a
+// large vocabulary is bound by what one SM can take in): slice s of row r leaves its maximum and
+// the lowest index that holds it in partial_v / partial_i [r][s].
+__global__ void __launch_bounds__(kSliceThreads)
+slice_max_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ partial_v,
+                 int* __restrict__ partial_i) {
+  __shared__ float red_v[kSliceThreads / 32];
+  __shared__ int red_i[kSliceThreads / 32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.y, s = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* row = logits + (size_t)r * vocab;
+  const int per = (vocab + kSlices - 1) / kSlices;
+  const int begin = min(s * per, vocab), end = min(begin + per, vocab);
+  float best = -FLT_MAX;
+  int best_i = 0x7fffffff;
+  for (int i = begin + tid; i < end; i += kSliceThreads) {
+    const float v = row[i];
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, offset);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, offset);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  if (lane == 0) { red_v[warp] = best; red_i[warp] = best_i; }
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < kSliceThreads / 32 ? red_v[lane] : -FLT_MAX;
+    best_i = lane < kSliceThreads / 32 ? red_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, offset);
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) { partial_v[r * kSlices + s] = best; partial_i[r * kSlices + s] = best_i; }
+  }
+}
+
 // One block per row.  temperature[r] == 0: argmax.  Else: token = first index whose inclusive
 // cumulative weight exp((logit - max)/T) exceeds u * total; each thread owns one contiguous
 // segment of the vocabulary, segment sums are scanned in thread order, so the result is a pure
 // function of the row, the temperature and the key.
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
-              const unsigned long long* __restrict__ keys, int* __restrict__ out) {
+              const unsigned long long* __restrict__ keys, int* __restrict__ out,
+              const float* __restrict__ partial_v, const int* __restrict__ partial_i) {
   __shared__ float red_v[kThreads / 32];
   __shared__ int red_i[kThreads / 32];
   __shared__ float seg_sum[kThreads];
@@ -41,12 +86,16 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)r * vocab;
 
-  // ---- maximum and its lowest index
+  // ---- maximum and its lowest index: from the slices' maxima if a first pass left them
   float best = -FLT_MAX;
   int best_i = 0x7fffffff;
-  for (int i = tid; i < vocab; i += kThreads) {
-    const float v = row[i];
-    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  if (partial_v) {
+    if (tid < kSlices) { best = partial_v[r * kSlices + tid]; best_i = partial_i[r * kSlices + tid]; }
+  } else {
+    for (int i = tid; i < vocab; i += kThreads) {
+      const float v = row[i];
+      if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
   }
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) {
@@ -112,13 +161,25 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 
 using namespace cie;
 
-// temperature may be null (all rows greedy); keys may be null only then.
+extern "C" int cie_sample_slices() { return kSlices; }
+
+// temperature may be null (all rows greedy); keys may be null only then.  scratch: room for
+// rows * cie_sample_slices() floats and as many ints, or null (then one CTA a row finds the
+// maximum itself, which is slow for a large vocabulary).
 extern "C" int cie_sample(const float* logits, int rows, int vocab, const float* temperature,
-                          const unsigned long long* keys, int* out, void* stream) {
+                          const unsigned long long* keys, int* out, void* scratch, void* stream) {
   if (rows <= 0) return 0;
   if (vocab < 1) CIE_FAIL("sample: vocabulary size %d", vocab);
   if (temperature && !keys) CIE_FAIL("sample: temperature rows need draw keys");
+  float* partial_v = nullptr;
+  int* partial_i = nullptr;
+  if (scratch && vocab >= 4096) {
+    partial_v = reinterpret_cast<float*>(scratch);
+    partial_i = reinterpret_cast<int*>(partial_v + (size_t)rows * kSlices);
+    CIE_LAUNCH("sample", slice_max_kernel, dim3(kSlices, rows), dim3(kSliceThreads), 0, (cudaStream_t)stream,
+               logits, vocab, partial_v, partial_i);
+  }
   CIE_LAUNCH("sample", sample_kernel, dim3(rows), dim3(kThreads), 0, (cudaStream_t)stream, logits,
-             vocab, temperature, keys, out);
+             vocab, temperature, keys, out, (const float*)partial_v, (const int*)partial_i);
   return 0;
 }

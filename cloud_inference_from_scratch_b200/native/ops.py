@@ -578,6 +578,10 @@ class Ops:
         rows, vocab = logits.shape
         if self._sample is None:
             v, i = c_void_p, c_int
-            self._sample = _Lib(load_library("sampling.cu")).function("cie_sample", [v, i, i, v, v, v, v])
-        self.launches += 1
-        self._sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(keys), _ptr(out), self.stream)
+            lib = _Lib(load_library("sampling.cu"))
+            self._sample = lib.function("cie_sample", [v, i, i, v, v, v, v, v])
+            self._sample_slices = int(lib.handle.cie_sample_slices())
+        # the row maxima are searched by several CTAs a row first (two launches)
+        scratch = self.scratch("sample.maxima", 2 * rows * self._sample_slices, reserve=2 * 1024 * self._sample_slices)
+        self.launches += 2 if vocab >= 4096 else 1
+        self._sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(keys), _ptr(out), _ptr(scratch), self.stream)
