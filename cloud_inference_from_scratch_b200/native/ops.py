@@ -532,8 +532,10 @@ class Ops:
                 or not self.can_pair_rotary(head_dim, position.rotary_dim)):
             return None
         tiles, k_tiles = -(-n // 32), -(-k // 128)
+        # K slices per block of weight rows (the size of a cluster): about two and a half CTAs an SM
+        # was measured best for this small product (its successor, attention, cannot start beside it)
         splits = 8
-        while splits > 1 and (tiles * splits > 5 * SM_COUNT or k_tiles // splits < 2):
+        while splits > 1 and (2 * tiles * splits > 5 * SM_COUNT or k_tiles // splits < 2):
             splits //= 2
         row_sq, row_tiles, eps = None, 0, 0.0
         if isinstance(x, NormedInput):
