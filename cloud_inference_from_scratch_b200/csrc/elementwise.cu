@@ -271,10 +271,12 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int partial_s
 }
 
 // The same for bfloat16 rows that are already summed (many tokens: the library product wrote them),
-// with rot a multiple of 16 and head size a multiple of 8: a thread owns 8 neighbouring rotary
-// pairs (16-byte loads of both halves), computes their sines and cosines once and walks over the
-// heads; values are copied 16 bytes at a time.  q_out may be the source itself only in the natural
-// layout (a thread reads both of its 16-byte pieces before it writes them).
+// with rot a multiple of 16 and head size a multiple of 8.  The work of a token is a list of
+// 16-byte items: 8 neighbouring rotary pairs of a q or k head (both halves), then 8 passed-through
+// columns of q, of k and of v.  A thread asks for its first item's bytes before anything else, so
+// that their way from memory overlaps the position's: position -> sines and cosines (once per
+// block, in shared memory) -> rotation.  q_out may be the source itself only in the natural layout
+// (an item is read by the one thread that writes it, before it writes).
 __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ src, const float* __restrict__ bias,
                                             __nv_bfloat16* __restrict__ q_out, int q_stride,
                                             const int* __restrict__ positions,
@@ -284,17 +286,79 @@ __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ sr
                                             const float* __restrict__ inv_freq, int q_heads, int kv_heads,
                                             int dim, int rot, int page_size, int write_cache, int paired,
                                             int* err) {
+  extern __shared__ float trig[];  // sines of the rot / 2 pairs, then their cosines
   pdl_wait();
   pdl_trigger();
   using bf16 = __nv_bfloat16;
   const int t = blockIdx.x;
-  const int pos = positions[t];
   const int width = (q_heads + 2 * kv_heads) * dim;
   const bf16* row = src + (size_t)t * width;
   bf16* q_row = q_out + (size_t)t * q_stride;
   const bool out_of_place = q_out != src;
   const int half = rot / 2;
+  const int chunks = half / 8, tail_chunks = (dim - rot) / 8, value_chunks = dim / 8;
+  const int rot_items = (q_heads + kv_heads) * chunks;
+  const int q_tail_items = bias || out_of_place ? q_heads * tail_chunks : 0;
+  const int k_tail_items = kv_heads * tail_chunks;
+  const int items = rot_items + q_tail_items + k_tail_items + kv_heads * value_chunks;
 
+  // where an item's bytes stand in the source row: column of its first (or only) piece and of
+  // its partner piece (-1: none)
+  auto place = [&](int i, int& col_a, int& col_b) {
+    col_b = -1;
+    if (i < rot_items) {
+      const int h = i / chunks, c = i % chunks;
+      col_a = h * dim + (paired ? paired_column(c * 8, rot) : c * 8);
+      col_b = h * dim + (paired ? paired_column(c * 8 + half, rot) : c * 8 + half);
+      return;
+    }
+    i -= rot_items;
+    if (i < q_tail_items) {
+      col_a = (i / tail_chunks) * dim + rot + (i % tail_chunks) * 8;
+      return;
+    }
+    i -= q_tail_items;
+    if (i < k_tail_items) {
+      col_a = (q_heads + i / tail_chunks) * dim + rot + (i % tail_chunks) * 8;
+      return;
+    }
+    i -= k_tail_items;
+    col_a = (q_heads + kv_heads + i / value_chunks) * dim + (i % value_chunks) * 8;
+  };
+  auto fetch = [&](int i, uint4& a, uint4& b) {
+    int col_a, col_b;
+    place(i, col_a, col_b);
+    a = *reinterpret_cast<const uint4*>(row + col_a);
+    if (col_b >= 0) b = *reinterpret_cast<const uint4*>(row + col_b);
+  };
+  auto widen = [&](const uint4& raw, int column, float (&v)[8]) {
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(pairs[j]);
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
+    if (bias) {
+      const float4 lo = *reinterpret_cast<const float4*>(bias + column);
+      const float4 hi = *reinterpret_cast<const float4*>(bias + column + 4);
+      v[0] += lo.x, v[1] += lo.y, v[2] += lo.z, v[3] += lo.w;
+      v[4] += hi.x, v[5] += hi.y, v[6] += hi.z, v[7] += hi.w;
+    }
+  };
+  auto store8 = [&](bf16* dst, const float (&v)[8]) {
+    uint4 packed;
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pairs[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    *reinterpret_cast<uint4*>(dst) = packed;
+  };
+
+  int item = threadIdx.x;
+  uint4 raw_a = make_uint4(0, 0, 0, 0), raw_b = raw_a;
+  if (item < items) fetch(item, raw_a, raw_b);
+
+  const int pos = positions[t];
   long long slot_base = -1;
   if (write_cache) {
     const int request = request_of_token[t];
@@ -307,85 +371,53 @@ __global__ void rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ sr
     }
   }
   const long long head_stride = (long long)page_size * dim;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &trig[j], &trig[half + j]);
+  __syncthreads();
 
-  auto load8 = [&](int column, float (&v)[8]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(row + column);
-    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  while (item < items) {
+    const int next = item + blockDim.x;
+    uint4 next_a = raw_a, next_b = raw_b;
+    if (next < items) fetch(next, next_a, next_b);
+    int col_a, col_b;
+    place(item, col_a, col_b);
+    float a[8];
+    widen(raw_a, col_a, a);
+    if (item < rot_items) {
+      const int h = item / chunks, c = item % chunks;
+      float b[8], ra[8], rb[8];
+      widen(raw_b, col_b, b);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(pairs[j]);
-      v[2 * j] = f.x;
-      v[2 * j + 1] = f.y;
-    }
-    if (bias) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] += bias[column + j];
-    }
-  };
-  auto store8 = [&](bf16* dst, const float (&v)[8]) {
-    uint4 packed;
-    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) pairs[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-    *reinterpret_cast<uint4*>(dst) = packed;
-  };
-
-  // rotary pairs: chunk c holds pairs 8c .. 8c+7 of a head; a thread keeps one chunk and walks heads
-  const int chunks = half / 8;
-  const int rot_heads = q_heads + kv_heads;
-  if (chunks > 0) {
-    const int lanes = max(1, (int)blockDim.x / chunks);
-    if ((int)threadIdx.x < lanes * chunks) {
-      const int c = threadIdx.x % chunks, first_head = threadIdx.x / chunks;
-      float sn[8], cs[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sincosf((float)pos * inv_freq[c * 8 + j], &sn[j], &cs[j]);
-      // where the two halves of this chunk stand inside a head
-      const int col_a = paired ? paired_column(c * 8, rot) : c * 8;
-      const int col_b = paired ? paired_column(c * 8 + half, rot) : c * 8 + half;
-      for (int h = first_head; h < rot_heads; h += lanes) {
-        float a[8], b[8], ra[8], rb[8];
-        load8(h * dim + col_a, a);
-        load8(h * dim + col_b, b);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ra[j] = a[j] * cs[j] - b[j] * sn[j];
-          rb[j] = b[j] * cs[j] + a[j] * sn[j];
-        }
-        if (h < q_heads) {
-          store8(q_row + h * dim + c * 8, ra);
-          store8(q_row + h * dim + c * 8 + half, rb);
-        } else if (slot_base >= 0) {
-          bf16* dst = k_pool + slot_base + (long long)(h - q_heads) * head_stride;
-          store8(dst + c * 8, ra);
-          store8(dst + c * 8 + half, rb);
+      for (int j = 0; j < 8; ++j) {
+        const float sn = trig[c * 8 + j], cs = trig[half + c * 8 + j];
+        ra[j] = a[j] * cs - b[j] * sn;
+        rb[j] = b[j] * cs + a[j] * sn;
+      }
+      bf16* dst = h < q_heads ? q_row + h * dim
+                  : slot_base >= 0 ? k_pool + slot_base + (long long)(h - q_heads) * head_stride
+                                   : nullptr;
+      if (dst) {
+        store8(dst + c * 8, ra);
+        store8(dst + c * 8 + half, rb);
+      }
+    } else {
+      int i = item - rot_items;
+      bf16* dst = nullptr;
+      if (i < q_tail_items) {
+        dst = q_row + (i / tail_chunks) * dim + rot + (i % tail_chunks) * 8;
+      } else if (slot_base >= 0) {
+        i -= q_tail_items;
+        if (i < k_tail_items) {
+          dst = k_pool + slot_base + (i / tail_chunks) * head_stride + rot + (i % tail_chunks) * 8;
+        } else {
+          i -= k_tail_items;
+          dst = v_pool + slot_base + (i / value_chunks) * head_stride + (i % value_chunks) * 8;
         }
       }
+      if (dst) store8(dst, a);
     }
-  }
-  // what lies beyond the rotary dims passes through; values are copied
-  const int tail_chunks = (dim - rot) / 8;
-  if (tail_chunks > 0 && (bias || out_of_place)) {
-    for (int i = threadIdx.x; i < q_heads * tail_chunks; i += blockDim.x) {
-      const int h = i / tail_chunks, d = rot + (i % tail_chunks) * 8;
-      float v[8];
-      load8(h * dim + d, v);
-      store8(q_row + h * dim + d, v);
-    }
-  }
-  if (slot_base < 0) return;
-  for (int i = threadIdx.x; i < kv_heads * tail_chunks; i += blockDim.x) {
-    const int h = i / tail_chunks, d = rot + (i % tail_chunks) * 8;
-    float v[8];
-    load8((q_heads + h) * dim + d, v);
-    store8(k_pool + slot_base + h * head_stride + d, v);
-  }
-  const int value_chunks = dim / 8;
-  for (int i = threadIdx.x; i < kv_heads * value_chunks; i += blockDim.x) {
-    const int h = i / value_chunks, d = (i % value_chunks) * 8;
-    float v[8];
-    load8((q_heads + kv_heads + h) * dim + d, v);
-    store8(v_pool + slot_base + h * head_stride + d, v);
+    item = next;
+    raw_a = next_a;
+    raw_b = next_b;
   }
 }
 
@@ -500,11 +532,13 @@ extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long 
   if (dtype == kBFloat16 && partial_splits == 0 && tokens > 64 && rot >= 16 && rot % 16 == 0 && dim % 8 == 0 &&
       q_stride % 8 == 0 &&
       ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pool) |
-        reinterpret_cast<uintptr_t>(v_pool)) & 15) == 0) {
-    CIE_LAUNCH("rope_kv_write", rope_kv_write_bf16x8_kernel, dim3(tokens), dim3(128), 0, (cudaStream_t)stream,
-               (const __nv_bfloat16*)src, bias, (__nv_bfloat16*)q_out, q_stride, positions, request_of_token, table,
-               table_width, num_pages, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, inv_freq, q_heads, kv_heads,
-               dim, rot, page_size, write_cache, paired, err);
+        reinterpret_cast<uintptr_t>(v_pool) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0) {
+    const int items = (q_heads + kv_heads) * (rot / 16) + (q_heads + kv_heads) * ((dim - rot) / 8) + kv_heads * (dim / 8);
+    const int threads = items >= 256 ? 256 : (items + 31) / 32 * 32;
+    CIE_LAUNCH("rope_kv_write", rope_kv_write_bf16x8_kernel, dim3(tokens), dim3(threads), rot * sizeof(float),
+               (cudaStream_t)stream, (const __nv_bfloat16*)src, bias, (__nv_bfloat16*)q_out, q_stride, positions,
+               request_of_token, table, table_width, num_pages, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+               inv_freq, q_heads, kv_heads, dim, rot, page_size, write_cache, paired, err);
     return 0;
   }
   DISPATCH_DTYPE(dtype, "rope_kv_write", {
