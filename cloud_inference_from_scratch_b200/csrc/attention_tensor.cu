@@ -416,12 +416,17 @@ struct DecodeArgs {
   int head_chunks;          // ceil(group / 16)
   int page_shift;           // log2(page_size), or -1 if it is not a power of two
   int splits;               // CTAs per cluster: 1, 2, 4 or 8
+  int chunks;               // clusters that may share a request's keys (1 .. DECODE_MAX_CHUNKS)
+  int chunk_keys;           // a request uses only as many of them as leave every CTA this many keys
+  float* partials;          // chunks > 1: [unit][chunk][16][D + 2] shares of the clusters
+  int* counters;            // chunks > 1: [unit] CTAs that have delivered; zero between launches
   float scale_log2;
   int window;
   int q_heads;
   int* err;
 };
 
+constexpr int DECODE_MAX_CHUNKS = 16;
 constexpr int DECODE_PAGE_SLOTS = 1024;   // block-table entries of a CTA's key range kept in shared memory
 
 // Stages per warp: all but one are in flight while one is multiplied.
@@ -479,6 +484,41 @@ __device__ __forceinline__ void load_kv_tile_warp(const DecodeArgs& a, const int
 }
 
 
+// Several clusters per request: the CTA that delivered last adds up the clusters' shares
+// ([chunk][16][D + 2] floats: unnormalised output, maximum, sum) and writes the output rows.
+// Kept out of line so that it costs the kernel's main loop no registers.
+__device__ __noinline__ void merge_chunks(const float* unit_partials, int chunks, bf16* out_rows, int rows,
+                                          int tid) {
+  // out_rows: the first of this unit's head rows in the output; rows: how many of the 16 exist
+  for (int idx = tid; idx < 16 * D; idx += DECODE_WARPS * 32) {
+    const int r = idx / D, d = idx % D;
+    if (r >= rows) continue;
+    float ms[DECODE_MAX_CHUNKS], ls[DECODE_MAX_CHUNKS], os[DECODE_MAX_CHUNKS];
+#pragma unroll
+    for (int c = 0; c < DECODE_MAX_CHUNKS; ++c) {
+      if (c < chunks) {
+        const float* share = unit_partials + (size_t)(c * 16 + r) * (D + 2);
+        ms[c] = __ldcg(share + D);
+        ls[c] = __ldcg(share + D + 1);
+        os[c] = __ldcg(share + d);
+      } else {
+        ms[c] = -INFINITY; ls[c] = 0.f; os[c] = 0.f;
+      }
+    }
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < DECODE_MAX_CHUNKS; ++c) m_all = fmaxf(m_all, ms[c]);
+    float sum = 0.f, acc = 0.f;
+#pragma unroll
+    for (int c = 0; c < DECODE_MAX_CHUNKS; ++c) {
+      const float f = (ms[c] == -INFINITY) ? 0.f : exp2f(ms[c] - m_all);
+      sum += ls[c] * f;
+      acc += os[c] * f;
+    }
+    out_rows[(size_t)r * D + d] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+  }
+}
+
 // kTma == false: keys and values come through the load/store unit (cp.async), any page size and
 // window.  kTma == true: each 16-key tile is fetched by one lane with D/64 tensor copies per
 // matrix (boxes of 16 rows x 64 columns, 128-byte swizzle) that complete on the stage's mbarrier;
@@ -514,7 +554,13 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
   const int* table_row = a.pools.table + (size_t)request * a.pools.table_width;
   const int length = a.context_lens[request] + 1;
   const int first = (a.window > 0 && length > a.window) ? length - a.window : 0;
-  const int per_split = (((length - first + a.splits - 1) / a.splits) + DN - 1) / DN * DN;
+  // how many of the launched clusters this request needs: the launch is sized for the longest
+  // context the tables can hold, the request may be far shorter; the others leave at once
+  int chunks = a.chunks;
+  if (chunks > 1) chunks = max(1, min(chunks, (length - first) / (a.splits * a.chunk_keys)));
+  if ((int)blockIdx.x / a.splits >= chunks) return;
+  const int ranges = a.splits * chunks;   // blockIdx.x counts key ranges; a cluster holds neighbours
+  const int per_split = (((length - first + ranges - 1) / ranges) + DN - 1) / DN * DN;
   const int begin = first + split * per_split;
   const int end = min(length, begin + per_split);
 
@@ -691,7 +737,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
       part_s[r * (D + 2) + D + 1] = acc;
     }
   }
-  if (a.splits == 1) {
+  if (a.splits == 1 && chunks == 1) {
     __syncthreads();
     for (int idx = tid; idx < 16 * D; idx += DECODE_WARPS * 32) {
       const int r = idx / D, d = idx % D;
@@ -705,9 +751,16 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
   // ---- the CTAs of a cluster hold the splits of one (request, kv head, head chunk): after a
   // cluster barrier each CTA merges some of the 16 head rows, reading its peers' shares through
   // distributed shared memory.  No scratch in global memory, no second kernel.
+  // With several clusters per request (long contexts at small batches) a cluster's merged rows
+  // go to global memory instead, unnormalised, and whichever CTA of the request delivers last
+  // (a ticket from an atomic counter: nobody waits for anybody) merges the clusters.
   cg::cluster_group cluster = cg::this_cluster();
   cluster.sync();
   const int rank = (int)cluster.block_rank();
+  const bool chunked = chunks > 1;
+  const int unit = request * gridDim.y + blockIdx.y;
+  float* unit_partials = chunked ? a.partials + (size_t)unit * a.chunks * 16 * (D + 2) : nullptr;
+  float* my_partials = chunked ? unit_partials + (size_t)(blockIdx.x / a.splits) * 16 * (D + 2) : nullptr;
   for (int idx = tid; idx < 16 * D; idx += DECODE_WARPS * 32) {
     const int r = idx / D, d = idx % D;
     if (r % a.splits != rank || h0 + r >= a.group) continue;
@@ -733,10 +786,29 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
       sum += ls[c] * f;
       acc += os[c] * f;
     }
-    a.out[(size_t)request * a.out_stride + (size_t)(kvh * a.group + h0 + r) * D + d] =
-        __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+    if (!chunked) {
+      a.out[(size_t)request * a.out_stride + (size_t)(kvh * a.group + h0 + r) * D + d] =
+          __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+    } else {
+      my_partials[r * (D + 2) + d] = acc;
+      if (d == 0) {
+        my_partials[r * (D + 2) + D] = m_all;
+        my_partials[r * (D + 2) + D + 1] = sum;
+      }
+    }
   }
   cluster.sync();   // nobody leaves while a peer may still read its share
+  if (!chunked) return;
+  __shared__ int last_s;
+  __threadfence();   // this thread's shares are visible before the ticket is drawn
+  __syncthreads();
+  if (tid == 0) last_s = atomicAdd(&a.counters[unit], 1) == a.splits * chunks - 1;
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  merge_chunks(unit_partials, chunks, a.out + (size_t)request * a.out_stride + (size_t)(kvh * a.group + h0) * D,
+               a.group - h0, tid);
+  if (tid == 0) a.counters[unit] = 0;   // ready for the next launch
 }
 
 // ------------------------------------------------------------------------------------ tensor maps
@@ -780,6 +852,10 @@ extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int
 }
 
 // splits: CTAs that share the keys of one request (a thread-block cluster): 1, 2, 4 or 8.
+// chunks: clusters launched per request (1 .. 16); a request uses as many of them as leave each
+// of its CTAs `chunk_keys` keys.  More than one needs `partials`, float32
+// [requests * kv_heads * ceil(group / 16)][chunks][16][head size + 2], and `counters`, one int per
+// (request, kv head, 16 heads) that is zero before the first launch (the kernel leaves it zero).
 // use_tma: 1 lets the kernel fetch keys and values with tensor copies where the shapes allow it
 // (pages of a multiple of 16 tokens, head size a multiple of 64, no window); 0 keeps cp.async.
 template <bool kTma>
@@ -793,7 +869,7 @@ static int launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, con
     configured = true;
   }
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(a.splits, a.pools.kv_heads * a.head_chunks, requests);
+  config.gridDim = dim3(a.splits * a.chunks, a.pools.kv_heads * a.head_chunks, requests);
   config.blockDim = dim3(DECODE_WARPS * 32);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
@@ -820,17 +896,19 @@ extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int 
                                     const void* k_pool, const void* v_pool, const int* table,
                                     int table_width, int num_pages, const int* context_lens,
                                     int requests, int q_heads, int kv_heads, int page_size,
-                                    int splits, float scale, int window, int use_tma, int* err,
-                                    void* stream) {
+                                    int splits, int chunks, int chunk_keys, float* partials, int* counters, float scale,
+                                    int window, int use_tma, int* err, void* stream) {
   if (requests <= 0) return 0;
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_decode: %d query heads over %d kv heads", q_heads, kv_heads);
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) CIE_FAIL("attention_decode: splits must be 1, 2, 4 or 8, got %d", splits);
   if (q_stride % 8) CIE_FAIL("attention_decode: row stride must keep 16-byte alignment");
+  if (chunks < 1 || chunks > DECODE_MAX_CHUNKS) CIE_FAIL("attention_decode: 1 to %d clusters per request, got %d", DECODE_MAX_CHUNKS, chunks);
+  if (chunks > 1 && (!partials || !counters || chunk_keys < 1)) CIE_FAIL("attention_decode: several clusters per request need scratch memory and a least number of keys per CTA");
   DecodeArgs a;
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
   a.pools = Pools{(const bf16*)k_pool, (const bf16*)v_pool, table, table_width, num_pages, kv_heads, page_size};
   a.context_lens = context_lens; a.group = q_heads / kv_heads; a.head_chunks = (a.group + 15) / 16;
-  a.splits = splits; a.scale_log2 = scale * kLog2e; a.window = window; a.q_heads = q_heads; a.err = err;
+  a.splits = splits; a.chunks = chunks; a.chunk_keys = chunk_keys; a.partials = partials; a.counters = counters; a.scale_log2 = scale * kLog2e; a.window = window; a.q_heads = q_heads; a.err = err;
   a.page_shift = -1;
   for (int shift = 0; shift < 31; ++shift)
     if ((1 << shift) == page_size) a.page_shift = shift;

@@ -529,7 +529,7 @@ extern "C" int cie_rope_kv_write(const void* src, int partial_splits, long long 
   if (rot % 2 || rot > dim || rot < 0) CIE_FAIL("rope_kv_write: rotary size %d does not fit head size %d", rot, dim);
   if (paired && (rot % 32 || q_out == src)) CIE_FAIL("rope_kv_write: the paired layout needs a rotary size that is a multiple of 32 and a q buffer of its own");
   if (partial_splits > kMaxSplits) CIE_FAIL("rope_kv_write: at most %d partial sums, got %d", kMaxSplits, partial_splits);
-  if (dtype == kBFloat16 && partial_splits == 0 && tokens > 64 && rot >= 16 && rot % 16 == 0 && dim % 8 == 0 &&
+  if (dtype == kBFloat16 && partial_splits == 0 && tokens > 16 && rot >= 16 && rot % 16 == 0 && dim % 8 == 0 &&
       q_stride % 8 == 0 &&
       ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pool) |
         reinterpret_cast<uintptr_t>(v_pool) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0) {

@@ -10,6 +10,8 @@ multiple of 16 tokens), else to the mma.sync prefill kernel.
 
 from __future__ import annotations
 
+import os
+
 from ctypes import c_float, c_int, c_void_p
 from typing import Any
 
@@ -20,6 +22,14 @@ from .build import load_library
 BM = 128           # query rows of a prefill tile (must match the kernel)
 SM_COUNT = 148
 MIN_KEYS_PER_SPLIT = 128
+# several clusters per request only while each CTA keeps this many keys: handing the shares over
+# through global memory costs about as much as streaming a thousand keys
+MIN_KEYS_PER_CHUNKED_CTA = int(os.environ.get("CIE_DECODE_CHUNK_KEYS", "1024"))
+# CTAs of clusters that can be counted on to run at one time, one CTA an SM: a cluster stays inside
+# one of the 8 GPCs (18 or so SMs each).  Measured: 128 CTAs in 16 clusters of 8 sometimes ran in
+# two rounds, 144 always did
+CLUSTERED_CTAS = 112
+MAX_CHUNKS = 16                  # must match DECODE_MAX_CHUNKS of the kernel
 
 
 def supports(head_dim: int) -> bool:
@@ -58,9 +68,15 @@ class TensorAttention:
         )
         self._decode = lib.function(
             "cie_attention_decode",
-            [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, f, i, i, v, v],
+            [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, i, i, v, v, f, i, i, v, v],
         )
         import os
+
+        # where clusters of one request leave their shares (at most one CTA an SM takes part), and
+        # the tickets that tell the last one; the kernel leaves the tickets at zero
+        torch = ops.torch
+        self._chunk_shares = torch.zeros(SM_COUNT * 16 * (head_dim + 2), dtype=torch.float32, device=ops.device)
+        self._chunk_tickets = torch.zeros(SM_COUNT, dtype=torch.int32, device=ops.device)
 
         self.use_tma = 0 if os.environ.get("CIE_DECODE_TMA", "1") == "0" else 1
         # prompt portions on tcgen05 where the kernel exists: head size 64 or 128, no window,
@@ -90,6 +106,18 @@ class TensorAttention:
             splits = 4   # big clusters cost more than they bring once half the SMs have work
         return splits
 
+    @staticmethod
+    def chunks_for(requests: int, kv_heads: int, group: int, max_keys: int, splits: int) -> int:
+        """Clusters per request: long contexts at small batches leave most SMs without work
+        even with clusters of 8, so the keys are cut once more, as long as every SM gets at
+        most one CTA and every CTA keeps MIN_KEYS_PER_CHUNKED_CTA keys."""
+        ctas = requests * kv_heads * -(-group // 16) * splits
+        if ctas * 4 > CLUSTERED_CTAS:
+            return 1   # half the SMs have work already: measured, a second cluster brings nothing
+        by_sms = CLUSTERED_CTAS // ctas
+        by_keys = max_keys // (splits * MIN_KEYS_PER_CHUNKED_CTA)
+        return max(1, min(by_sms, by_keys, MAX_CHUNKS))
+
     def run(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
             scale: float, window: int, plan: dict[str, Any] | None = None) -> bool:
         ops = self.ops
@@ -104,11 +132,13 @@ class TensorAttention:
             if window > 0:
                 max_keys = min(max_keys, window)
             splits = self.splits_for(requests, kv_heads, group, max_keys)
+            chunks = self.chunks_for(requests, kv_heads, group, max_keys, splits)
             ops.launches += 1
             self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                          kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
                          ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, kv.page_size,
-                         splits, scale, window, self.use_tma, ops.error_word.data_ptr(), ops.stream)
+                         splits, chunks, MIN_KEYS_PER_CHUNKED_CTA, self._chunk_shares.data_ptr(), self._chunk_tickets.data_ptr(),
+                         scale, window, self.use_tma, ops.error_word.data_ptr(), ops.stream)
             return True
         if plan is None:
             tiles = plan_tiles(ctx.host.query_lens, group)

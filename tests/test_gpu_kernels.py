@@ -371,6 +371,31 @@ def test_tensor_attention_far_key(ops):
     tensor_case(ops, 128, [2047], [1], 16, 2, 128, 16, seed=8, plant=(0, 2040, 4.0))
 
 
+def test_tensor_attention_decode_of_a_long_context_in_several_clusters(ops, monkeypatch):
+    """Few requests with thousands of keys: the keys of a request go to several clusters, whose
+    shares the CTA that delivers last merges.  A planted key near the start, in the middle and at
+    the end of the context; a short request beside a long one (it uses one cluster of those
+    launched for it); a cluster count that is no power of two; the cp.async variant; and the same
+    object again and again (the tickets must be back at zero after every launch)."""
+    from cloud_inference_from_scratch_b200.native import tensor_attention
+    from cloud_inference_from_scratch_b200.native.tensor_attention import TensorAttention
+
+    # the threshold as it ships: 20,000 keys of one request make two clusters
+    assert TensorAttention.chunks_for(1, 2, 8, 20016, TensorAttention.splits_for(1, 2, 8, 20016)) == 2
+    assert TensorAttention.chunks_for(8, 2, 8, 32768, TensorAttention.splits_for(8, 2, 8, 32768)) == 1
+    tensor_case(ops, 128, [20000], [1], 16, 2, 128, 16, seed=10, plant=(0, 11000, 4.0))
+    # a lower one, so that shorter contexts reach every case
+    monkeypatch.setattr(tensor_attention, "MIN_KEYS_PER_CHUNKED_CTA", 256)
+    assert TensorAttention.chunks_for(1, 2, 8, 9008, TensorAttention.splits_for(1, 2, 8, 9008)) == 4
+    tensor_case(ops, 128, [9000], [1], 16, 2, 128, 16, seed=11)
+    tensor_case(ops, 128, [9000], [1], 16, 2, 128, 16, seed=12, plant=(0, 5, 4.0))
+    tensor_case(ops, 128, [8999], [1], 16, 2, 128, 16, seed=13, plant=(0, 8990, 4.0))
+    tensor_case(ops, 64, [6000, 37], [1, 1], 4, 1, 64, 16, seed=14, plant=(0, 3000, 4.0))
+    tensor_case(ops, 32, [7000], [1], 4, 2, 32, 8, seed=15, plant=(0, 6100, 4.0))
+    tensor_case(ops, 128, [20000], [1], 28, 4, 128, 32, seed=16)
+    tensor_case(ops, 128, [700, 9000], [1, 1], 16, 2, 128, 16, seed=17, plant=(1, 4500, 4.0))
+
+
 def test_tensor_attention_long_prompt_whole(ops):
     tensor_case(ops, 128, [0], [1500], 16, 2, 128, 16, seed=9)
     tensor_case(ops, 64, [300, 0], [700, 64], 14, 2, 64, 16, seed=10)
