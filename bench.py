@@ -263,7 +263,7 @@ def run_own(args: argparse.Namespace) -> int:
     achieved = step_bytes / (main["ms_per_step"] / 1e3) / 1e9
     flops = prefill_flops(used, PROMPT_TOKENS, 1)
     line = {
-        "metric": "decode tok/s (Qwen2.5-3B shape, batch 8, context 2048+)",
+        "metric": f"decode tok/s (Qwen2.5-3B shape, batch {args.batch}, context {PROMPT_TOKENS}+)",
         "value": round(main["tokens_per_s"], 1),
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -312,6 +312,7 @@ def run_reference(args: argparse.Namespace) -> int:
 
 
 def main() -> int:
+    global PROMPT_TOKENS, CONTEXT
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=128)
@@ -319,6 +320,9 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the model has (named in config; for quick runs)")
+    parser.add_argument("--prompt-tokens", type=int, default=PROMPT_TOKENS,
+                        help="prompt length of every request and of the timed prefill (the record's "
+                             "default is 2048; longer ones are for profiles of long contexts, own arm only)")
     parser.add_argument("--impl", default="own", choices=("own", "reference"))
     parser.add_argument("--only", default="all", choices=("all", "decode", "prefill"),
                         help="measure only the decode step at --batch, or only the prefill "
@@ -329,6 +333,14 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.prompt_tokens != PROMPT_TOKENS:
+        limit = QWEN25_3B["max_position_embeddings"]
+        room = args.warmup + args.steps + 2
+        if args.impl != "own" or args.prompt_tokens < 16 or args.prompt_tokens + room > limit:
+            print(f"bench.py: --prompt-tokens takes 16 .. {limit - room} with these steps, own arm only")
+            return 2
+        PROMPT_TOKENS = args.prompt_tokens
+        CONTEXT = min(limit, PROMPT_TOKENS + max(2048, room))
     if args.impl == "reference":
         return run_reference(args)
     return run_own(args)
