@@ -892,6 +892,36 @@ static int launch_decode(const CUtensorMap& k_map, const CUtensorMap& v_map, con
   return 0;
 }
 
+// How many clusters of `splits` CTAs of the decode kernel the device runs at one time (a cluster
+// stays inside one GPC and a CTA takes most of an SM's shared memory); -1 if the query fails.
+template <bool kTma>
+static int decode_clusters_at_once(int splits) {
+  constexpr size_t smem = decode_smem<kTma>();
+  if (cudaFuncSetAttribute(decode_kernel<kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(splits, 1, 1);
+  config.blockDim = dim3(DECODE_WARPS * 32);
+  config.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = splits;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, decode_kernel<kTma>, &config) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return clusters;
+}
+
+extern "C" int cie_attention_decode_clusters(int splits, int use_tma) {
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -1;
+  return use_tma && D % 64 == 0 ? decode_clusters_at_once<true>(splits) : decode_clusters_at_once<false>(splits);
+}
+
 extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int out_stride,
                                     const void* k_pool, const void* v_pool, const int* table,
                                     int table_width, int num_pages, const int* context_lens,

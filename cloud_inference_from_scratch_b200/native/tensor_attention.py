@@ -25,9 +25,9 @@ MIN_KEYS_PER_SPLIT = 128
 # several clusters per request only while each CTA keeps this many keys: handing the shares over
 # through global memory costs about as much as streaming a thousand keys
 MIN_KEYS_PER_CHUNKED_CTA = int(os.environ.get("CIE_DECODE_CHUNK_KEYS", "1024"))
-# CTAs of clusters that can be counted on to run at one time, one CTA an SM: a cluster stays inside
-# one of the 8 GPCs (18 or so SMs each).  Measured: 128 CTAs in 16 clusters of 8 sometimes ran in
-# two rounds, 144 always did
+# CTAs of clusters that can be counted on to run at one time when the device cannot be asked: a
+# cluster stays inside one of the 8 GPCs, and with one CTA an SM the device reports room for 15
+# clusters of 8 (a 16th waits for a second round, which costs more than the cut brings)
 CLUSTERED_CTAS = 112
 MAX_CHUNKS = 16                  # must match DECODE_MAX_CHUNKS of the kernel
 
@@ -70,8 +70,10 @@ class TensorAttention:
             "cie_attention_decode",
             [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, i, i, v, v, f, i, i, v, v],
         )
-        import os
-
+        self._decode_clusters = lib.handle.cie_attention_decode_clusters
+        self._decode_clusters.argtypes = [i, i]
+        self._decode_clusters.restype = c_int
+        self._cluster_room: dict[int, int] = {}
         # where clusters of one request leave their shares (at most one CTA an SM takes part), and
         # the tickets that tell the last one; the kernel leaves the tickets at zero
         torch = ops.torch
@@ -93,6 +95,16 @@ class TensorAttention:
                 [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, v, v],
             )
 
+    def cluster_room(self, splits: int) -> int:
+        """CTAs in clusters of ``splits`` that run at one time, one cluster held back for whatever
+        still runs beside them (asked of the device once per cluster size)."""
+        room = self._cluster_room.get(splits)
+        if room is None:
+            clusters = int(self._decode_clusters(splits, self.use_tma))
+            room = CLUSTERED_CTAS if clusters < 2 else min(SM_COUNT, (clusters - 1) * splits)
+            self._cluster_room[splits] = room
+        return room
+
     @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int) -> int:
         """CTAs (of one cluster) that share a request's keys: enough to put work on every SM,
@@ -107,14 +119,15 @@ class TensorAttention:
         return splits
 
     @staticmethod
-    def chunks_for(requests: int, kv_heads: int, group: int, max_keys: int, splits: int) -> int:
+    def chunks_for(requests: int, kv_heads: int, group: int, max_keys: int, splits: int,
+                   room: int = CLUSTERED_CTAS) -> int:
         """Clusters per request: long contexts at small batches leave most SMs without work
         even with clusters of 8, so the keys are cut once more, as long as every SM gets at
-        most one CTA and every CTA keeps MIN_KEYS_PER_CHUNKED_CTA keys."""
+        most one CTA (``room`` CTAs run at one time) and every CTA keeps MIN_KEYS_PER_CHUNKED_CTA keys."""
         ctas = requests * kv_heads * -(-group // 16) * splits
-        if ctas * 4 > CLUSTERED_CTAS:
+        if ctas * 4 > room:
             return 1   # half the SMs have work already: measured, a second cluster brings nothing
-        by_sms = CLUSTERED_CTAS // ctas
+        by_sms = room // ctas
         by_keys = max_keys // (splits * MIN_KEYS_PER_CHUNKED_CTA)
         return max(1, min(by_sms, by_keys, MAX_CHUNKS))
 
@@ -132,7 +145,7 @@ class TensorAttention:
             if window > 0:
                 max_keys = min(max_keys, window)
             splits = self.splits_for(requests, kv_heads, group, max_keys)
-            chunks = self.chunks_for(requests, kv_heads, group, max_keys, splits)
+            chunks = self.chunks_for(requests, kv_heads, group, max_keys, splits, self.cluster_room(splits))
             ops.launches += 1
             self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                          kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,

@@ -380,6 +380,10 @@ def test_tensor_attention_decode_of_a_long_context_in_several_clusters(ops, monk
     from cloud_inference_from_scratch_b200.native import tensor_attention
     from cloud_inference_from_scratch_b200.native.tensor_attention import TensorAttention
 
+    # the device says how many clusters run at one time; the plan keeps one of them back
+    ops[torch.bfloat16].require_attention(128)
+    room = ops[torch.bfloat16]._tensor_attention[128].cluster_room(8)
+    assert room % 8 == 0 and 64 <= room <= 148, room
     # the threshold as it ships: 20,000 keys of one request make two clusters
     assert TensorAttention.chunks_for(1, 2, 8, 20016, TensorAttention.splits_for(1, 2, 8, 20016)) == 2
     assert TensorAttention.chunks_for(8, 2, 8, 32768, TensorAttention.splits_for(8, 2, 8, 32768)) == 1
