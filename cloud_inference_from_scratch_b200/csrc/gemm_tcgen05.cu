@@ -2,7 +2,7 @@
 // TMA (cp.async.bulk.tensor, 128-byte swizzle) into a multi-stage shared-memory ring, one elected
 // thread issues tcgen05.mma with the float32 accumulator in tensor memory, tcgen05.commit hands
 // stages back to the TMA thread through mbarriers, and the four warps read the accumulator with
-// tcgen05.ld for the epilogue.  No cluster multicast is used.
+// tcgen05.ld for the epilogue.  Every CTA copies its own tiles; nothing is shared across a cluster.
 //
 // Both matrices are K-major ([rows, K], K contiguous), so either can be the 128-row operand:
 //  * many tokens (prefill): tokens are the 128-row operand, weight rows the N operand (BN = 128);
