@@ -398,6 +398,9 @@ def test_tensor_attention_decode_of_a_long_context_in_several_clusters(ops, monk
     tensor_case(ops, 32, [7000], [1], 4, 2, 32, 8, seed=15, plant=(0, 6100, 4.0))
     tensor_case(ops, 128, [20000], [1], 28, 4, 128, 32, seed=16)
     tensor_case(ops, 128, [700, 9000], [1, 1], 16, 2, 128, 16, seed=17, plant=(1, 4500, 4.0))
+    # a window: the clusters share the last 5,000 keys only, and a key before them must not count
+    tensor_case(ops, 32, [7000], [1], 4, 2, 32, 8, window=5000, seed=18, plant=(0, 2500, 4.0))
+    tensor_case(ops, 32, [7000], [1], 4, 2, 32, 8, window=5000, seed=19, plant=(0, 1500, 4.0))
 
 
 def test_tensor_attention_long_prompt_whole(ops):
