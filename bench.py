@@ -300,8 +300,17 @@ def run_own(args: argparse.Namespace) -> int:
                    for suffix, key, digits in (("", "tokens_per_s", 1), ("_ms", "ms_per_step", 4))},
         "clocks": main["clocks"],
     }
-    print(json.dumps(line))
+    print(json.dumps(without_nan(line)))
     return 0
+
+
+def without_nan(value):
+    """A part that was not measured (--only) is null in the record, not NaN."""
+    if isinstance(value, dict):
+        return {key: without_nan(item) for key, item in value.items()}
+    if isinstance(value, float) and value != value:
+        return None
+    return value
 
 
 def run_reference(args: argparse.Namespace) -> int:
