@@ -10,8 +10,12 @@ ids.  ``--url`` and ``--api-key`` are accepted and ignored so that existing invo
 
     cie generate "5,17,3" --model DIR --max-output-tokens 8
     cie generate "5 17 3" --model DIR --temperature 0.8 --seed 7 --no-stream
+    cie generate "5 17 3" --random-config config.json --weights-seed 3   (random weights, no folder)
     cie models --model DIR        cie health        cie metrics --model DIR
+    cie info [--model DIR]        (device, kernels, architectures, engine defaults in one report)
     cie random-model DIR --config config.json --seed 3     (writes config.json + model.safetensors)
+    cie replay --model DIR --dtype float32 --out OUT --max-tokens 256 [--trace FILE]   (trace replay)
+    cie bench [options of bench.py]                                    (the benchmark of the repository)
 """
 
 from __future__ import annotations
@@ -40,6 +44,9 @@ def parser() -> argparse.ArgumentParser:
     def engine_options(sub: argparse.ArgumentParser) -> None:
         sub.add_argument("--model", default=os.environ.get("ENGINE_MODEL"),
                          help="model folder (config.json + *.safetensors)")
+        sub.add_argument("--random-config", default=None,
+                         help="instead of --model: a config.json (path or JSON text) to draw random weights for")
+        sub.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
         sub.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
         sub.add_argument("--block-size", type=int, default=16)
         sub.add_argument("--kv-cache-blocks", type=int, default=None)
@@ -64,6 +71,11 @@ def parser() -> argparse.ArgumentParser:
     generate.add_argument("--eos-token-id", type=int, default=None)
     metrics = commands.add_parser("metrics", help="print engine metrics as JSON")
     engine_options(metrics)
+    info = commands.add_parser("info", help="device, kernels, architectures and engine defaults")
+    info.add_argument("--model", default=os.environ.get("ENGINE_MODEL"))
+    # their own options follow the command word and are handed on as they are
+    commands.add_parser("replay", help="trace replay (the options of bin/trace_run)", add_help=False)
+    commands.add_parser("bench", help="run the repository's bench.py", add_help=False)
     random_model = commands.add_parser("random-model", help="write a model folder with random weights")
     random_model.add_argument("folder")
     random_model.add_argument("--config", required=True, help="config.json to build from")
@@ -74,8 +86,15 @@ def parser() -> argparse.ArgumentParser:
 def _engine(args: argparse.Namespace, prompt_len: int = 1, max_output: int = 1) -> Any:
     from .. import InferenceEngine, build_config
 
-    if not args.model:
-        parser().error("--model or ENGINE_MODEL is required")
+    random_config = None
+    if args.random_config:
+        text = args.random_config
+        if not text.lstrip().startswith("{"):
+            with open(text, encoding="utf-8") as handle:
+                text = handle.read()
+        random_config = json.loads(text)
+    elif not args.model:
+        parser().error("--model, ENGINE_MODEL or --random-config is required")
     max_len = args.max_model_len or max(64, prompt_len + max_output)
     config = build_config(
         "ragged", dtype=args.dtype, block_size=args.block_size, kv_cache_blocks=args.kv_cache_blocks,
@@ -84,36 +103,72 @@ def _engine(args: argparse.Namespace, prompt_len: int = 1, max_output: int = 1) 
         max_model_len=max_len, max_output_tokens=max(256, max_output),
         cuda_graph_decode=not args.no_cuda_graph_decode,
     )
+    if random_config is not None:
+        return InferenceEngine(config, None, random_config=random_config, seed=args.weights_seed)
     return InferenceEngine(config, args.model)
 
 
+def _health() -> tuple[dict[str, Any], dict[str, Any]]:
+    import torch
+
+    live = {"status": "ok"}
+    ready: dict[str, Any] = {"cuda": torch.cuda.is_available()}
+    if ready["cuda"]:
+        from ..native.ops import Ops
+
+        ready["device"] = torch.cuda.get_device_name(0)
+        ready["capability"] = list(torch.cuda.get_device_capability(0))
+        Ops("cuda:0", torch.bfloat16)
+        ready["kernels"] = "built"
+    ready["status"] = "ready" if ready["cuda"] else "no CUDA device"
+    return live, ready
+
+
+def _models(model: str | None) -> dict[str, Any]:
+    from ..config.registry import registered_architectures, resolve_model
+
+    listing: dict[str, Any] = {"architectures": list(registered_architectures())}
+    if model:
+        arch, config, _ = resolve_model(model)
+        listing["model"] = {"folder": str(model), "architecture": arch.name, "config": config.to_dict()}
+    return listing
+
+
 def main(argv: list[str] | None = None) -> int:
-    args = parser().parse_args(argv)
+    args, rest = parser().parse_known_args(argv)
+    if rest and args.command not in ("replay", "bench"):
+        parser().error("unrecognized arguments: " + " ".join(rest))
+    args.rest = rest
     try:
         if args.command == "health":
-            import torch
-
-            live = {"status": "ok"}
-            ready: dict[str, Any] = {"cuda": torch.cuda.is_available()}
-            if ready["cuda"]:
-                from ..native.ops import Ops
-
-                ready["device"] = torch.cuda.get_device_name(0)
-                ready["capability"] = list(torch.cuda.get_device_capability(0))
-                Ops("cuda:0", torch.bfloat16)
-                ready["kernels"] = "built"
-            ready["status"] = "ready" if ready["cuda"] else "no CUDA device"
+            live, ready = _health()
             print(json.dumps({"liveness": live, "readiness": ready}, indent=2))
             return 0 if ready["cuda"] else 1
         if args.command == "models":
-            from ..config.registry import registered_architectures, resolve_model
+            print(json.dumps(_models(args.model), indent=2))
+            return 0
+        if args.command == "info":
+            from dataclasses import asdict
 
-            listing: dict[str, Any] = {"architectures": list(registered_architectures())}
-            if args.model:
-                arch, config, _ = resolve_model(args.model)
-                listing["model"] = {"folder": str(args.model), "architecture": arch.name,
-                                    "config": config.to_dict()}
-            print(json.dumps(listing, indent=2))
+            from .. import __version__, build_config
+
+            live, ready = _health()
+            print(json.dumps({"version": __version__, "liveness": live, "readiness": ready,
+                              **_models(args.model), "engine_defaults": asdict(build_config("ragged"))}, indent=2))
+            return 0
+        if args.command == "replay":
+            from .replay import main as replay_main
+
+            return replay_main(args.rest)
+        if args.command == "bench":
+            import runpy
+            from pathlib import Path
+
+            script = Path(__file__).resolve().parents[2] / "bench.py"
+            if not script.is_file():
+                raise RuntimeError(f"bench.py is not beside the package ({script})")
+            sys.argv = [str(script), *args.rest]
+            runpy.run_path(str(script), run_name="__main__")
             return 0
         if args.command == "random-model":
             from ..weights.random_init import write_random_model

@@ -54,6 +54,7 @@ def build_core(
     random_config: dict[str, Any] | None = None,
     seed: int = 0,
     random_device: str = "cpu",
+    random_scales: dict[str, float] | None = None,
 ) -> EngineCore:
     """``model_dir`` is a folder with config.json and *.safetensors; or give ``random_config``
     (a config.json dictionary) and ``seed`` to draw the weights without writing a folder."""
@@ -69,12 +70,13 @@ def build_core(
         source: Any = SafetensorsSource(model_dir)
         check_tensors(source, table, spec.optional_tensors)
     else:
-        source = RandomSource(table, seed, device=random_device)
+        source = RandomSource(table, seed, device=random_device, scales=random_scales)
     if max_model_len > spec.max_positions:
         raise ValueError(
             f"max_model_len {max_model_len} exceeds the model's position range {spec.max_positions}"
         )
-    runtime = Runtime(device=device, dtype=dtype, max_tokens=max_tokens_per_step, gemm=gemm)
+    runtime = Runtime(device=device, dtype=dtype, max_tokens=max_tokens_per_step, gemm=gemm,
+                      max_requests=max_requests)
     model.bind(device_tensors(source, table, runtime.device, runtime.dtype), runtime)
 
     needs = model.cache_needs()

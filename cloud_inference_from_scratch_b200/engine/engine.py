@@ -102,6 +102,7 @@ class InferenceEngine:
         preemption_priority: Callable[[PreemptionCandidate], tuple] = largest_sequence_preemption,
         random_config: dict[str, Any] | None = None,
         seed: int = 0,
+        random_scales: dict[str, float] | None = None,
     ) -> None:
         self.config = config or build_config("ragged")
         self.model_dir = Path(model_dir) if model_dir is not None else None
@@ -109,6 +110,7 @@ class InferenceEngine:
         self._runner_factory = runner_factory
         self._random_config = random_config
         self._seed = seed
+        self._random_scales = random_scales
         self.scheduling_priority = scheduling_priority
         self.preemption_priority = preemption_priority
         self.metrics = Metrics()
@@ -143,6 +145,7 @@ class InferenceEngine:
                 random_config=self._random_config,
                 seed=self._seed,
                 random_device="cuda" if self._random_config is not None else "cpu",
+                random_scales=self._random_scales,
             )
             self.runner = EngineRunner(self.core, config)
         self.scheduler = Scheduler(

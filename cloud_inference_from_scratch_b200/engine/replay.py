@@ -1,8 +1,9 @@
 """Trace replay: feeds given token ids through a model step by step and writes logits.
 
-    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--trace FILE]
 
-Steps come on standard input, one JSON object a line:
+(also ``cie replay`` with the same options).  Steps come on standard input (or from ``--trace``),
+one JSON object a line:
 
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
 
@@ -38,6 +39,7 @@ def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (sizes the cache pool)")
+    parser.add_argument("--trace", default=None, help="file with the steps (default: standard input)")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE)
     parser.add_argument("--device", default="cuda:0")
     return parser.parse_args(argv)
@@ -65,8 +67,9 @@ def main(argv: list[str] | None = None) -> int:
     )
     step_fn = core.step
     live: set[str] = set()
+    steps = open(args.trace, encoding="utf-8") if args.trace else sys.stdin
     while True:
-        line = sys.stdin.readline()
+        line = steps.readline()
         if not line:
             break
         line = line.strip()

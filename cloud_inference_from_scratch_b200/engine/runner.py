@@ -38,18 +38,20 @@ class _DecodeGraph:
         self.event = torch.cuda.Event()
         self.feed_index = torch.zeros(bucket, dtype=torch.int64, device=result_dev.device)
         self.feed_real = -1
+        self.logits: Any = None                 # the float32 logits buffer the captured step writes
 
 
 class _InFlight:
     """A decode step that has been launched and whose tokens have not been read yet."""
 
     def __init__(self, graph: _DecodeGraph, request_ids: list[str], spans: dict, real: int,
-                 committed: bool) -> None:
+                 committed: bool, logits: Any = None) -> None:
         self.graph = graph
         self.request_ids = request_ids
         self.spans = spans
         self.real = real
         self.committed = committed
+        self.logits = logits     # a copy of the step's logits rows, only while logits are traced
 
 
 class EngineRunner:
@@ -76,6 +78,13 @@ class EngineRunner:
         self.pipeline_decode = True
         self.steps_launched_ahead = 0
         self.steps_ahead_adopted = 0
+        self.steps_ahead_dropped = 0
+        # For tests and self-checks: with ``trace_logits`` on, every step leaves (request ids,
+        # position of each sampled row's token, a device copy of the float32 logits rows) in
+        # ``logit_trace``.  A decode step's rows are copied on the stream right behind the step,
+        # before the step launched ahead of the host can overwrite the shared logits buffer.
+        self.trace_logits = False
+        self.logit_trace: list[tuple[list[str], list[int], Any]] = []
         self.forward_invocations = 0
         self.max_forward_request_count = 0
         self.cuda_graph_captures = 0
@@ -95,29 +104,34 @@ class EngineRunner:
         return self.core.cache.allocated_tokens(request.request_id)
 
     def execute_batch(self, plan: Any) -> dict[str, int]:
-        items = plan.items
+        requests, starts, lengths, samples = plan.requests, plan.starts, plan.lengths, plan.samples
         entries = [
-            StepEntry(item.request.request_id, item.token_ids,
-                      want=(len(item.token_ids) - 1,) if item.sample else (), start_pos=item.start_pos)
-            for item in items
+            StepEntry(request.request_id, request.tokens[start:start + length],
+                      want=(length - 1,) if sample else (), start_pos=start)
+            for request, start, length, sample in zip(requests, starts, lengths, samples)
         ]
-        sampled = [item for item in items if item.sample]
+        sampled = [request for request, sample in zip(requests, samples) if sample]
         self.forward_invocations += 1
-        self.max_forward_request_count = max(self.max_forward_request_count, len(items))
+        self.max_forward_request_count = max(self.max_forward_request_count, len(requests))
         self.forward_plans.append(
-            tuple((i.request.request_id, i.start_pos, i.query_length, i.sample) for i in items)
+            tuple(zip((r.request_id for r in requests), starts, lengths, samples))
         )
         if len(self.forward_plans) > 256:
             del self.forward_plans[:128]
-        decode_only = all(item.query_length == 1 and item.sample for item in items)
+        decode_only = plan.decode_only
         phase = "decode" if decode_only else "mixed"
-        with nvtx_range(f"ragged.forward.{phase}.requests_{len(items)}.tokens_{plan.token_count}"):
-            if decode_only and self.use_graphs and len(items) <= self.max_rows:
-                tokens = self._pipelined_decode(items, entries)
+        with nvtx_range(f"ragged.forward.{phase}.requests_{len(requests)}.tokens_{plan.token_count}"):
+            if decode_only and self.use_graphs and len(requests) <= self.max_rows:
+                tokens = self._pipelined_decode(requests, starts, entries)
             else:
-                self._ahead = None   # a step launched ahead is dropped: it committed nothing
+                self._drop_ahead()   # a step launched ahead committed nothing
                 tokens = self._eager(entries, sampled)
-        return {item.request.request_id: int(tokens[i]) for i, item in enumerate(sampled)}
+        return {request.request_id: int(tokens[i]) for i, request in enumerate(sampled)}
+
+    def _drop_ahead(self) -> None:
+        if self._ahead is not None:
+            self.steps_ahead_dropped += 1
+            self._ahead = None
 
     # ------------------------------------------------------------------ sampling parameters
     @staticmethod
@@ -127,8 +141,7 @@ class EngineRunner:
         so that a padded row samples what the row it repeats samples."""
         temperature = np.zeros(rows, dtype=np.float32)
         keys = np.zeros(rows, dtype=np.int64)
-        for index, item in enumerate(sampled):
-            request = item.request
+        for index, request in enumerate(sampled):
             temperature[index] = request.config.temperature
             if request.config.temperature > 0:
                 keys[index] = as_signed(
@@ -171,6 +184,9 @@ class EngineRunner:
         step.tokens_run += host.num_tokens
         if rows:
             self._launch_sampling(logits, ctx, self.result_dev, rows)
+            if self.trace_logits:
+                ids = [request.request_id for request in sampled]
+                self.logit_trace.append((ids, [spans[rid][1] - 1 for rid in ids], logits[:rows].clone()))
         return self._read_back(self.result_dev, rows)
 
     # ------------------------------------------------------------------ graphed decode
@@ -240,6 +256,7 @@ class EngineRunner:
                 self._launch_sampling(logits, ctx, result_dev, bucket)
             self.launches_per_graph[bucket] = self.ops.launches - launches_before
             cached = _DecodeGraph(bucket, meta, graph, result_dev, ctx, torch)
+            cached.logits = logits
             self._graphs[(bucket, self._parity)] = cached
             self.cuda_graph_captures += 1
         else:
@@ -255,7 +272,9 @@ class EngineRunner:
         self.cuda_graph_replays += 1
         step.steps_run += 1
         step.tokens_run += real
-        return _InFlight(cached, [entry.request_id for entry in entries], spans, real, committed=False)
+        kept = cached.logits[:real].clone() if self.trace_logits else None
+        return _InFlight(cached, [entry.request_id for entry in entries], spans, real, committed=False,
+                         logits=kept)
 
     def _commit(self, flight: _InFlight) -> None:
         if not flight.committed:
@@ -263,49 +282,50 @@ class EngineRunner:
                 self.core.cache.commit_lengths({rid: end for rid, (_, end) in flight.spans.items()})
             flight.committed = True
 
-    def _launch_ahead(self, items: Any, current: _InFlight) -> _InFlight | None:
+    def _launch_ahead(self, requests: list[Any], ends: list[int], current: _InFlight) -> _InFlight | None:
         """Launches the decode step that will most likely be asked for next: the same requests,
-        one position further, their token ids taken on the device from what ``current`` samples.
-        It commits nothing; if the next plan turns out different it is simply dropped (what it
-        wrote lies beyond every committed length and is written again before it is read)."""
+        one position further (``ends``), their token ids taken on the device from what ``current``
+        samples.  It commits nothing; if the next plan turns out different it is simply dropped
+        (what it wrote lies beyond every committed length and is written again before it is read)."""
         if not self.pipeline_decode or (current.graph.bucket, self._parity ^ 1) not in self._graphs:
             return None
-        for item in items:
-            request = item.request
+        for request, end in zip(requests, ends):
             if request.generated_count + 1 >= request.config.max_output_tokens:
                 return None    # this request ends with the token being sampled now
-            if item.end_pos + 1 > self.config.max_model_len:
+            if end + 1 > self.config.max_model_len:
                 return None
-        entries = [StepEntry(item.request.request_id, (0,), want=(0,), start_pos=item.end_pos) for item in items]
+        entries = [StepEntry(request.request_id, (0,), want=(0,), start_pos=end)
+                   for request, end in zip(requests, ends)]
         try:
-            flight = self._launch_decode(entries, list(items), ahead=1, feed=current.graph)
+            flight = self._launch_decode(entries, requests, ahead=1, feed=current.graph)
         except Exception as exc:  # noqa: BLE001 - no pages (or anything else): run the step when asked
             if not bool(getattr(exc, "is_capacity_error", False)):
                 raise
-            self._parity ^= 1
-            return None
+            return None    # pages ran out while preparing: nothing was launched, nothing flipped
         self.steps_launched_ahead += 1
         return flight
 
-    def _pipelined_decode(self, items: Any, entries: list[StepEntry]) -> np.ndarray:
+    def _pipelined_decode(self, requests: list[Any], starts: list[int], entries: list[StepEntry]) -> np.ndarray:
         ahead, self._ahead = self._ahead, None
         current = None
         if ahead is not None:
-            same = ahead.request_ids == [item.request.request_id for item in items] and all(
-                ahead.spans[item.request.request_id][0] == item.start_pos for item in items
+            same = ahead.request_ids == [request.request_id for request in requests] and all(
+                ahead.spans[request.request_id][0] == start for request, start in zip(requests, starts)
             )
             if same:
                 current = ahead
                 self.steps_ahead_adopted += 1
+            else:
+                self.steps_ahead_dropped += 1
         if current is None:
-            current = self._launch_decode(entries, list(items), ahead=0, feed=None)
+            current = self._launch_decode(entries, requests, ahead=0, feed=None)
         self._commit(current)
         graph = current.graph
         with nvtx_range("ragged.sample.readback"):
             graph.result_host.copy_(graph.result_dev, non_blocking=True)
             graph.event.record()
         # while the device works on the current step, the next one is prepared and queued
-        self._ahead = self._launch_ahead(items, current)
+        self._ahead = self._launch_ahead(requests, [start + 1 for start in starts], current)
         graph.event.synchronize()
         self.d2h_bytes = 4 * (1 + graph.bucket)
         values = graph.result_host.numpy()
@@ -313,4 +333,6 @@ class EngineRunner:
             self._ahead = None
             self.ops.error_word = graph.result_dev[0:1]
             self.ops.check_errors()
+        if current.logits is not None:
+            self.logit_trace.append(([request.request_id for request in requests], list(starts), current.logits))
         return values[1:1 + current.real].copy()

@@ -173,6 +173,7 @@ class DecoderModel:
         if ctx.num_logit_rows == 0:
             return None
         x = self.final_norm.forward(residual, pending, ctx, rows=ctx.logit_rows)
-        logits = rt.workspace.get("logits", ctx.num_logit_rows, spec.vocab_size, torch.float32)
+        logits = rt.workspace.get("logits", ctx.num_logit_rows, spec.vocab_size, torch.float32,
+                                  per_request=True)
         rt.ops.linear(x, self.head, None, logits)
         return logits

@@ -232,8 +232,12 @@ class Ops:
             self.error_word.zero_()
             faults = [name for bit, name in ((1, "a token had no valid cache page"),
                                               (2, "a token id was outside the vocabulary"),
-                                              (4, "a request index was outside the batch"))
+                                              (4, "a request index was outside the batch"),
+                                              (8, "a bounded wait for a tensor copy or a tensor-core "
+                                                  "product ran out"))
                       if word & bit]
+            if word & ~15:
+                faults.append(f"unknown bits {word & ~15:#x}")
             raise KernelError("device error word set: " + "; ".join(faults))
 
     # ------------------------------------------------------------------ kernels

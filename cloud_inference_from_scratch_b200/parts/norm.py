@@ -30,7 +30,7 @@ class RMSNorm(Norm):
         rt = self.runtime
         count = residual.shape[0] if rows is None else rows.shape[0]
         out = rt.workspace.get("norm.out" if rows is None else "norm.rows", count,
-                               self.hidden_size, rt.dtype)
+                               self.hidden_size, rt.dtype, per_request=rows is not None)
         rt.ops.add_rmsnorm(residual, update, self.weight, self.eps, out, rows)
         return out
 

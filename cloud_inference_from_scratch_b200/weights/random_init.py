@@ -21,6 +21,7 @@ def write_random_model(
     std: float = 0.02,
     store_dtype: str = "bfloat16",
     vector_dtype: str | None = None,
+    scales: dict[str, float] | None = None,
 ) -> Path:
     """``config`` is a config.json dictionary of a registered architecture."""
     import safetensors.torch
@@ -31,7 +32,8 @@ def write_random_model(
     model_dir.mkdir(parents=True, exist_ok=True)
     _, typed, spec = resolve_config(config)
     table = DecoderModel(spec).tensor_table()
-    source = RandomSource(table, seed, std=std, store_dtype=store_dtype, vector_dtype=vector_dtype)
+    source = RandomSource(table, seed, std=std, store_dtype=store_dtype, vector_dtype=vector_dtype,
+                          scales=scales)
     tensors = {name: source.get(name).contiguous() for name in source.names()}
     stored = typed.to_dict() if hasattr(typed, "to_dict") else dict(config)
     stored["torch_dtype"] = store_dtype

@@ -72,17 +72,22 @@ def _tensor_seed(seed: int, name: str) -> int:
 class RandomSource:
     """Seeded random tensors for a name table: weights and biases N(0, std), norm gains
     1 + N(0, std); drawn in float32 and rounded to ``store_dtype`` (bfloat16 by default, so a
-    32-bit run and a bfloat16 run of the same folder start from identical values)."""
+    32-bit run and a bfloat16 run of the same folder start from identical values).
+
+    ``scales`` maps a piece of a tensor name to a factor: every tensor whose name contains the
+    piece is multiplied by it before rounding (``{".q_proj.": 1.9, ".k_proj.": 1.9}`` spreads
+    attention scores, which N(0, 0.02) weights leave close to uniform)."""
 
     def __init__(self, table: dict[str, TensorSpec], seed: int, std: float = 0.02,
                  store_dtype: str = "bfloat16", vector_dtype: str | None = None,
-                 device: str = "cpu") -> None:
+                 device: str = "cpu", scales: dict[str, float] | None = None) -> None:
         self.table = dict(table)
         self.seed = int(seed)
         self.std = float(std)
         self.store_dtype = store_dtype
         self.vector_dtype = vector_dtype or store_dtype
         self.device = device
+        self.scales = dict(scales or {})
 
     def names(self) -> list[str]:
         return sorted(self.table)
@@ -105,5 +110,8 @@ class RandomSource:
                 values += 1.0
             elif spec.init != "normal":
                 raise ValueError(f"tensor {name}: unknown init {spec.init!r}")
+        for piece, factor in self.scales.items():
+            if piece in name:
+                values *= factor
         dtype = self.vector_dtype if spec.role == "vector" else self.store_dtype
         return values.to(getattr(torch, dtype))

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_model
-from helpers import random_tokens
+from helpers import check_trace_rows, random_tokens, record, tolerance
 from tiny_configs import PAGE_SIZE, TINY
 
 pytestmark = pytest.mark.gpu
@@ -46,25 +46,67 @@ def test_greedy_generation_matches_the_plain_model(tiny_models, name, lengths, s
         assert [r.token_ids for r in results] == [plain_model.greedy_generate(config, weights, p, steps) for p in prompts]
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_temperature_draws_do_not_depend_on_the_batch_or_the_cut(tiny_models, dtype):
-    from cloud_inference_from_scratch_b200 import generate
+def _temperature_run(folder, prompts, dtype, temperature, seed, **overrides):
+    """Generation at a temperature with the logits of every sampled row kept; returns the results and,
+    per request, (stream number, prompt + generated tokens, prompt length, {position: logits row})."""
+    from cloud_inference_from_scratch_b200 import GenerationConfig, InferenceEngine, build_config
 
+    settings = dict(dtype=dtype, block_size=8, kv_cache_blocks=64, max_model_len=128)
+    settings.update(overrides)
+    with InferenceEngine(build_config("ragged", **settings), folder) as engine:
+        engine.runner.trace_logits = True
+        handles = [engine.submit(p, GenerationConfig(max_output_tokens=6, temperature=temperature, seed=seed))
+                   for p in prompts]
+        results = [h.wait() for h in handles]
+        rows = {h.request_id: {} for h in handles}
+        for ids, positions, logits in engine.runner.logit_trace:
+            kept = logits.float().cpu().numpy()
+            for row, (rid, position) in enumerate(zip(ids, positions)):
+                rows[rid][position] = kept[row]
+        detail = [(h.request.sequence_number, list(p) + list(r.token_ids), len(p), rows[h.request_id])
+                  for h, p, r in zip(handles, prompts, results)]
+    return results, detail
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_draws_do_not_depend_on_the_batch_or_the_cut(sharp_models, dtype):
+    """Every drawn token is the inverse CDF of softmax(row / T) at the uniform number of its key
+    (seed, stream number, output index), whatever the batch and the cut; the rows themselves match
+    the plain model.  In 32-bit the tokens of all cuttings are equal as well."""
+    import numpy as np
+
+    from cloud_inference_from_scratch_b200.sampling import draw_key, uniform_from_key
+
+    folder = sharp_models.get("B", dtype)
+    config, weights = plain_model.read_model_folder(folder)
     prompts = prompts_for("B", (9, 23, 40))
-    common = dict(max_output_tokens=6, temperature=0.8, seed=5, dtype=dtype, block_size=8, kv_cache_blocks=64)
-    alone = generate(tiny_models["B"], prompts[:1], **common)
-    together = generate(tiny_models["B"], prompts, **common)
-    chopped = generate(tiny_models["B"], prompts, prefill_chunk_size=3, max_batched_tokens=7, **common)
-    greedy = generate(tiny_models["B"], prompts, **dict(common, temperature=0.0))
+    temperature, seed = 0.8, 5
+    runs = {
+        "alone": _temperature_run(folder, prompts[:1], dtype, temperature, seed),
+        "together": _temperature_run(folder, prompts, dtype, temperature, seed),
+        "chopped": _temperature_run(folder, prompts, dtype, temperature, seed, prefill_chunk_size=3, max_batched_tokens=7),
+    }
+    for kind, (results, detail) in runs.items():
+        for stream, tokens, prompt_len, rows in detail:
+            reference = plain_model.forward(config, weights, tokens).numpy()
+            assert sorted(rows) == list(range(prompt_len - 1, len(tokens) - 1)), kind
+            for position, row in rows.items():
+                error = float(np.abs(row - reference[position]).max() / reference.std())
+                assert record("B runner", dtype, error) <= tolerance(dtype, "B runner"), (kind, position, error)
+                scaled = row.astype(np.float64) / temperature
+                cdf = np.cumsum(np.exp(scaled - scaled.max()))
+                cdf /= cdf[-1]
+                u = uniform_from_key(draw_key(seed, stream, position - (prompt_len - 1)))
+                drawn = tokens[position + 1]
+                below = cdf[drawn - 1] if drawn else 0.0
+                assert below - 1e-5 <= u <= cdf[drawn] + 1e-5, (kind, position, drawn, u, below, cdf[drawn])
     if dtype == "float32":
-        assert alone[0].token_ids == together[0].token_ids == chopped[0].token_ids
-        assert [r.token_ids for r in together] == [r.token_ids for r in chopped]
-    else:
-        same = sum(a == b for a, b in zip(together[0].token_ids, chopped[0].token_ids))
-        assert same >= 4   # bfloat16 products round differently per batch shape; a draw near an edge may move
-    assert [r.token_ids for r in together] != [r.token_ids for r in greedy]
-    other_seed = generate(tiny_models["B"], prompts, **dict(common, seed=6))
-    assert [r.token_ids for r in other_seed] != [r.token_ids for r in together]
+        assert runs["alone"][0][0].token_ids == runs["together"][0][0].token_ids == runs["chopped"][0][0].token_ids
+        assert [r.token_ids for r in runs["together"][0]] == [r.token_ids for r in runs["chopped"][0]]
+    greedy, _ = _temperature_run(folder, prompts, dtype, 0.0, seed)
+    assert [r.token_ids for r in runs["together"][0]] != [r.token_ids for r in greedy]
+    other_seed, _ = _temperature_run(folder, prompts, dtype, temperature, 6)
+    assert [r.token_ids for r in other_seed] != [r.token_ids for r in runs["together"][0]]
 
 
 def test_eos_stops_generation(tiny_models):
@@ -80,31 +122,36 @@ def test_eos_stops_generation(tiny_models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_pages_running_out_preempts_and_recomputes_without_token_drift(tiny_models, dtype):
+def test_pages_running_out_preempts_and_recomputes_without_token_drift(sharp_models, tiny_models, dtype):
     from cloud_inference_from_scratch_b200 import GenerationConfig, InferenceEngine, build_config
 
+    folder = sharp_models.get("A", dtype)
     prompts = prompts_for("A", (56, 56, 30))
     prompts[1] = list(prompts[0])            # identical prompts must give identical outputs
     def run(blocks):
         config = build_config("ragged", dtype=dtype, block_size=4, kv_cache_blocks=blocks, max_model_len=128,
                               max_batched_tokens=32, prefill_chunk_size=16, max_active_sequences=4)
-        with InferenceEngine(config, tiny_models["A"]) as engine:
+        with InferenceEngine(config, folder) as engine:
+            engine.runner.trace_logits = True
             handles = [engine.submit(p, GenerationConfig(max_output_tokens=12)) for p in prompts]
             results = [h.wait() for h in handles]
             snapshot = engine.snapshot_metrics()
             engine.core.cache.assert_invariants()
             assert engine.core.cache.free_pages() == engine.core.cache.total_pages()
+            trace = [(ids, positions, logits.float().cpu().numpy()) for ids, positions, logits in engine.runner.logit_trace]
+            requests = {h.request_id: (list(p) + list(r.token_ids), len(p), r.finish_reason)
+                        for h, p, r in zip(handles, prompts, results)}
+        # every row a token was sampled from, before and after the recomputation, against the plain model
+        check_trace_rows(folder, requests, trace, dtype, "A runner")
         return results, snapshot
     roomy, _ = run(64)
     tight, snapshot = run(30)                # 120 tokens of cache for 142 + 36 tokens of demand
     assert snapshot["requests"]["preempted_total"] > 0 and snapshot["requests"]["recomputed_total"] > 0
     assert sum(r.preemptions for r in tight) == snapshot["requests"]["preempted_total"]
+    assert all(len(r.token_ids) == 12 for r in tight)
     if dtype == "float32":
         assert [r.token_ids for r in tight] == [r.token_ids for r in roomy]
         assert tight[0].token_ids == tight[1].token_ids
-    else:
-        for a, b in zip(tight, roomy):
-            assert len(a.token_ids) == len(b.token_ids) == 12
     # one request that can never fit is rejected, not looped on
     config = build_config("ragged", dtype=dtype, block_size=4, kv_cache_blocks=8, max_model_len=128)
     with InferenceEngine(config, tiny_models["A"]) as engine:
@@ -154,3 +201,32 @@ def test_cie_command_line(tiny_models):
     assert health.returncode == 0 and json.loads(health.stdout)["readiness"]["kernels"] == "built"
     models = subprocess.run([sys.executable, str(ROOT / "bin" / "cie"), "models"], capture_output=True, text=True, env=env, timeout=600)
     assert json.loads(models.stdout)["model"]["architecture"] == "Qwen2ForCausalLM"
+
+
+def test_cie_random_config_info_and_replay(tiny_models, tmp_path):
+    """The added sub-commands on the device: generation from an inline random configuration, the
+    one-page report, and trace replay through ``cie replay``."""
+    import numpy as np
+
+    cie = [sys.executable, str(ROOT / "bin" / "cie")]
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(TINY["A"]))
+    common = ["--max-output-tokens", "5", "--dtype", "float32", "--block-size", "4", "--kv-cache-blocks", "32", "--no-stream"]
+    first = subprocess.run([*cie, "generate", "5,17,3", "--random-config", str(config), "--weights-seed", "3", *common],
+                           capture_output=True, text=True, timeout=600)
+    again = subprocess.run([*cie, "generate", "5,17,3", "--random-config", json.dumps(TINY["A"]), "--weights-seed", "3", *common],
+                           capture_output=True, text=True, timeout=600)
+    assert first.returncode == 0, first.stderr[-2000:]
+    assert len(first.stdout.split()) == 5 and first.stdout == again.stdout
+    info = subprocess.run([*cie, "info", "--model", str(tiny_models["A"])], capture_output=True, text=True, timeout=600)
+    report = json.loads(info.stdout)
+    assert report["readiness"]["kernels"] == "built" and report["model"]["architecture"] == "Qwen2ForCausalLM"
+    trace = tmp_path / "trace.jsonl"
+    trace.write_text(json.dumps({"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3, 9], "want": [3]}], "end": ["a"]}) + "\n")
+    done = subprocess.run([*cie, "replay", "--model", str(tiny_models["A"]), "--dtype", "float32", "--out", str(tmp_path / "out"),
+                           "--max-tokens", "64", "--trace", str(trace)], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0 and done.stdout.strip() == "done 0", done.stderr[-2000:]
+    cfg, weights = plain_model.read_model_folder(tiny_models["A"])
+    want = plain_model.forward(cfg, weights, [5, 17, 3, 9])[-1].numpy()
+    got = np.fromfile(tmp_path / "out" / "0.f32", dtype="<f4")
+    assert np.abs(got - want).max() <= 1e-5

@@ -12,11 +12,10 @@ import pytest
 import torch
 
 import plain_model
-from helpers import BF16_TOL, FP32_TOL, random_tokens, relative_error, replay, sharpen, trace_mixed, trace_portions, trace_whole
+from helpers import random_tokens, record, relative_error, replay, sharpen, tolerance, trace_mixed, trace_portions, trace_whole
 from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu
-TOL = {"float32": FP32_TOL, "bfloat16": BF16_TOL}
 
 
 def runtime(dtype):
@@ -31,8 +30,8 @@ def rand(*shape, scale=1.0, seed=0):
 
 
 def close(got, want, dtype):
-    error = relative_error(got.float().cpu().numpy(), want.float().cpu().numpy())
-    assert error <= TOL[dtype] * (4 if dtype == "bfloat16" else 1), error
+    error = record("a part alone", dtype, relative_error(got.float().cpu().numpy(), want.float().cpu().numpy()))
+    assert error <= tolerance(dtype, "a part alone"), error
 
 
 # ------------------------------------------------------------------ parts alone
@@ -262,7 +261,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
         for rid, tokens in requests.items():
             ref = toy_plain_forward(folder, tokens).numpy()
             mine = np.stack([got[rid][p] for p in range(len(tokens))])
-            assert relative_error(mine, ref) <= TOL[dtype], (rid, relative_error(mine, ref))
+            assert record("toy models", dtype, relative_error(mine, ref)) <= tolerance(dtype, "toy models"), (rid, relative_error(mine, ref))
     # through the public entry point; CUDA graphs must stay off because of the per-request state
     prompts = [requests["t1"], requests["t3"]]
     results = generate(folder, prompts, max_output_tokens=5, dtype=dtype, block_size=8, kv_cache_blocks=40,
@@ -319,7 +318,7 @@ def test_layer_run_twice_and_cache_read_by_a_later_run(dtype, tmp_path):
         for rid, tokens in requests.items():
             ref = plain_model.forward(cfg, weights, tokens, schedule=schedule).numpy()
             mine = np.stack([got[rid][p] for p in range(len(tokens))])
-            assert relative_error(mine, ref) <= TOL[dtype], (rid, relative_error(mine, ref))
+            assert record("toy models", dtype, relative_error(mine, ref)) <= tolerance(dtype, "toy models"), (rid, relative_error(mine, ref))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -356,7 +355,7 @@ def test_windowed_and_full_attention_in_one_model(dtype, name, tmp_path):
     for rid, tokens in requests.items():
         ref = plain_model.forward(cfg, weights, tokens, window=[11, 0]).numpy()
         mine = np.stack([got[rid][p] for p in range(len(tokens))])
-        assert relative_error(mine, ref) <= TOL[dtype], (rid, relative_error(mine, ref))
+        assert record("toy models", dtype, relative_error(mine, ref)) <= tolerance(dtype, "toy models"), (rid, relative_error(mine, ref))
     assert core.cache.groups[window_group].allocator.allocations_total > per_group[window_group]
     assert core.cache.free_pages(0) == core.cache.total_pages(0)
     assert core.cache.free_pages(1) == core.cache.total_pages(1)
@@ -506,5 +505,5 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
             ref, choice = toy_routed_plain_forward(folder, tokens)
             used.update(choice.tolist())
             mine = np.stack([got[rid][p] for p in range(len(tokens))])
-            assert relative_error(mine, ref.numpy()) <= TOL["float32"], (rid, relative_error(mine, ref.numpy()))
+            assert record("toy routed", "float32", relative_error(mine, ref.numpy())) <= tolerance("float32", "toy routed"), (rid, relative_error(mine, ref.numpy()))
     assert used == {0, 1}      # both experts took tokens

@@ -13,41 +13,15 @@ import pytest
 
 import plain_model
 from helpers import (
-    BF16_TOL, FP32_TOL, check_against_plain, peak_tokens, random_tokens, replay, sharpen,
+    FP32_TOL, check_against_plain, peak_tokens, random_tokens, replay, requests_in, sharpen,
     trace_mixed, trace_portions, trace_tail, trace_whole,
 )
 from tiny_configs import PAGE_SIZE, TINY
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
-TOL = {"float32": FP32_TOL, "bfloat16": BF16_TOL}
 LENGTHS = {"A": (5, 11, 17, 70, 129, 48), "B": (1, 9, 23, 40, 97, 64), "C": (33, 16, 2, 81, 50),
            "D": (19, 65, 128, 37, 3)}
-
-
-# Sharpened weights give attention scores a standard deviation of ``score_std`` instead of
-# nearly zero.  The 32-bit runs use 3.0, where a wrong key or page changes logits by far more
-# than the 2e-5 gate.  Keys, values and activations of the bfloat16 path carry a relative
-# rounding error of 2^-9, and a score's absolute error grows with its size; those runs use 1.5
-# so that honest bfloat16 rounding stays inside the 2e-2 gate while attention is still far
-# from uniform.
-SHARPNESS = {"float32": dict(score_std=3.0), "bfloat16": dict(score_std=1.5)}
-
-
-class _Sharp:
-    def __init__(self, tiny_models, root):
-        self.tiny_models, self.root, self.made = tiny_models, root, {}
-
-    def get(self, name, dtype):
-        if (name, dtype) not in self.made:
-            self.made[name, dtype] = sharpen(self.tiny_models[name], self.root / dtype / name,
-                                             **SHARPNESS[dtype])
-        return self.made[name, dtype]
-
-
-@pytest.fixture(scope="module")
-def sharp_models(tiny_models, tmp_path_factory):
-    return _Sharp(tiny_models, tmp_path_factory.mktemp("sharp"))
 
 
 def make_requests(name):
@@ -67,12 +41,15 @@ def make_core(folder, name, dtype, tokens):
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_four_cuttings_match_the_plain_model(sharp_models, name, dtype):
     requests = make_requests(name)
+    interrupted = max(requests, key=lambda rid: len(requests[rid]))
     traces = {
         "whole": trace_whole(requests),
         "tail32": trace_tail(requests, 32),
         "portions": trace_portions(requests),
-        "mixed": trace_mixed(requests, seed=7),
+        # one request is ended half-way (pages given back) and fed again from its first token
+        "mixed": trace_mixed(requests, seed=7, interrupt=interrupted),
     }
+    assert interrupted + "@again" in requests_in(traces["mixed"])
     results = {}
     for kind, steps in traces.items():
         # a pool just large enough for the trace, so that freed pages are taken again
@@ -80,22 +57,24 @@ def test_four_cuttings_match_the_plain_model(sharp_models, name, dtype):
         total_pages = core.cache.total_pages()
         got = replay(core, steps)
         results[kind] = got
-        check_against_plain(sharp_models.get(name, dtype), requests, got, TOL[dtype])
+        check_against_plain(sharp_models.get(name, dtype), requests_in(steps), got, dtype, name)
         assert core.cache.free_pages() == total_pages, f"{kind}: pages were not all given back"
         assert core.cache.groups[0].allocator.allocations_total > total_pages, f"{kind}: no page reused"
     if dtype == "float32":
-        # the 32-bit kernels sum in an order that does not depend on the cut: bit-equal logits
+        # the 32-bit kernels sum in an order that does not depend on the cut: bit-equal logits,
+        # also for the request that was released and computed again
         for kind in ("tail32", "portions", "mixed"):
-            for rid, rows in results["whole"].items():
+            for rid, rows in results[kind].items():
                 for position, row in rows.items():
-                    assert np.array_equal(row, results[kind][rid][position]), (kind, rid, position)
+                    assert np.array_equal(row, results["whole"][rid.split("@")[0]][position]), (kind, rid, position)
+        assert len(results["mixed"][interrupted + "@again"]) == len(requests[interrupted])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_unsharpened_weights_too(tiny_models, dtype):
     requests = make_requests("B")
     core = make_core(tiny_models["B"], "B", dtype, 512)
-    check_against_plain(tiny_models["B"], requests, replay(core, trace_mixed(requests, seed=3)), TOL[dtype])
+    check_against_plain(tiny_models["B"], requests, replay(core, trace_mixed(requests, seed=3)), dtype, "B unsharpened")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -104,7 +83,7 @@ def test_long_decoding_one_token_at_a_time(sharp_models, dtype):
     requests = {"long": tokens}
     core = make_core(sharp_models.get("A", dtype), "A", dtype, 320)
     got = replay(core, trace_tail(requests, tail=296))
-    check_against_plain(sharp_models.get("A", dtype), requests, got, TOL[dtype])
+    check_against_plain(sharp_models.get("A", dtype), requests, got, dtype, "A long")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -114,10 +93,9 @@ def test_first_tokens_of_a_sequence(sharp_models, name, dtype):
     requests = {"one": random_tokens(vocab, 1, 1), "two": random_tokens(vocab, 2, 2),
                 "three": random_tokens(vocab, 3, 3)}
     core = make_core(sharp_models.get(name, dtype), name, dtype, 256)
-    check_against_plain(sharp_models.get(name, dtype), requests, replay(core, trace_whole(requests)), TOL[dtype])
+    check_against_plain(sharp_models.get(name, dtype), requests, replay(core, trace_whole(requests)), dtype, name)
     single = trace_tail({"s": random_tokens(vocab, 6, 4)}, tail=5)   # every token on its own
-    check_against_plain(sharp_models.get(name, dtype), {"s": random_tokens(vocab, 6, 4)}, replay(core, single),
-                        TOL[dtype])
+    check_against_plain(sharp_models.get(name, dtype), {"s": random_tokens(vocab, 6, 4)}, replay(core, single), dtype, name)
 
 
 def test_a_far_key_among_hundreds_is_found(tiny_models, tmp_path):
@@ -133,7 +111,7 @@ def test_a_far_key_among_hundreds_is_found(tiny_models, tmp_path):
     assert (plain_model.forward(config, weights, altered)[-1] - ref[-1]).abs().max() > 100 * FP32_TOL
     core = make_core(folder, "B", "float32", 448)
     got = replay(core, trace_portions({"far": tokens}, sizes=(100, 2, 57, 8)))
-    check_against_plain(folder, {"far": tokens}, got, FP32_TOL)
+    check_against_plain(folder, {"far": tokens}, got, "float32", "B far key")
 
 
 def test_page_running_out_is_a_host_error_that_changes_nothing(tiny_models):
@@ -183,7 +161,7 @@ def test_trace_run_program(sharp_models, tmp_path, dtype):
                 got.setdefault(entry["id"], {})[position[entry["id"]] + place] = logits[row]
                 row += 1
             position[entry["id"]] += len(entry["tokens"])
-    check_against_plain(sharp_models.get("B", dtype), requests, got, TOL[dtype])
+    check_against_plain(sharp_models.get("B", dtype), requests, got, dtype, "B")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
