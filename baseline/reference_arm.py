@@ -133,7 +133,7 @@ async def _prefill_rate(engine: Any, prompt_tokens: int, vocab: int) -> dict:
     return {"ms": best * 1e3, "tokens_per_s": prompt_tokens / best}
 
 
-def run(args: Any, model_config: dict, prompt_tokens: int, context: int) -> dict:
+def run(args: Any, model_config: dict, prompt_tokens: int, context: int, config_record: dict | None = None) -> dict:
     if not (REF / "cloud_engine").is_dir():
         return {"impl": "reference",
                 "unavailable": "baseline/_ref/cloud_engine is not installed on this machine (see baseline/reference_arm.py)"}
@@ -205,9 +205,12 @@ def run(args: Any, model_config: dict, prompt_tokens: int, context: int) -> dict
         "vs_baseline": round(main["tokens_per_s"] / 178.986, 2),
         "dtype": "fp16",
         "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
-        "config": {"model": "Qwen2.5-3B shape", "layers": config_json["num_hidden_layers"], "layers_of_model": 36,
-                   "global_batch": args.batch, "seq_len": context, "prompt_tokens": prompt_tokens, "page_size": 16,
-                   "parallelism": "single GPU", "timing": "wall clock over streamed tokens, device synchronised"},
+        # the same keys and values as the own arm's line (same model shape, batch, prompt and context)
+        "config": dict(config_record) if config_record else {
+            "model": "Qwen2.5-3B shape", "layers": config_json["num_hidden_layers"], "layers_of_model": 36,
+            "global_batch": args.batch, "seq_len": context, "prompt_tokens": prompt_tokens, "page_size": 16,
+            "parallelism": "single GPU"},
+        "timing": "wall clock over streamed tokens, device synchronised; prompt portions of 256 tokens (its stock setting)",
         "e2e": {"value": round(main["tokens_per_s"], 1), "unit": "tokens/s"},
         "prefill": {"value": round(prefill["tokens_per_s"], 1), "tokens": prompt_tokens, "ms": round(prefill["ms"], 3)}
         if prefill else None,

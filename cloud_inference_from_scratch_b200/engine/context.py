@@ -55,6 +55,7 @@ class StepContext:
     host: Any                 # HostBatch (numpy) the device views were copied from
     bindings: list[LayerBinding] = field(default_factory=list)
     all_decode: bool = False  # every request brings exactly one token
+    num_single: int = 0       # the first this many requests bring one token each (token row == request index)
     extras: dict[Any, dict[str, Any]] = field(default_factory=dict)
     # The float32 residual stream [T, H] when every norm of the model accepts an ``Accumulated``
     # update, else None.  A mixer or feed-forward may hand it to ``ops.linear(..., residual=...)``

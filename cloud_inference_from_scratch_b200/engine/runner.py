@@ -212,6 +212,7 @@ class EngineRunner:
         host.request_of_token = np.arange(bucket, dtype=np.int32)
         host.query_start = np.arange(bucket + 1, dtype=np.int32)
         host.logit_rows = np.arange(bucket, dtype=np.int32)
+        host.num_single = bucket
         host.tables = [grow(table) for table in host.tables]
 
     def _launch_decode(self, entries: list[StepEntry], sampled: list[Any], ahead: int,

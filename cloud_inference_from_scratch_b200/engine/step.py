@@ -52,6 +52,9 @@ class HostBatch:
     logit_rows: np.ndarray
     tables: list[np.ndarray]
     extras: dict[Any, dict[str, np.ndarray]] = field(default_factory=dict)
+    # requests that bring exactly one token come first in a step; this many lead the batch (their
+    # token row equals their request index, which is what the decode kernels count on)
+    num_single: int = 0
 
     @property
     def num_tokens(self) -> int:
@@ -188,6 +191,10 @@ class StepFunction:
     # ------------------------------------------------------------------ packing
     def build_host_batch(self, entries: Sequence[StepEntry], table_width: int | None = None
                          ) -> tuple[HostBatch, list[tuple[Hashable, int]], dict[Hashable, tuple[int, int]]]:
+        """Checks the entries and lays the step out.  Inside the step, requests that bring a single
+        token are placed before the others (each class in the order given), so that the kernels for
+        single queries can take the leading rows of a mixed step; the wanted rows keep the order of
+        the entries and of ``want``."""
         cache = self.cache
         seen: set[Hashable] = set()
         starts: list[int] = []
@@ -209,17 +216,23 @@ class StepFunction:
                 raise ValueError(f"request {entry.request_id!r} brings no tokens")
             starts.append(start)
             lens.append(len(entry.token_ids))
-        query_lens = np.asarray(lens, dtype=np.int32)
-        context_lens = np.asarray(starts, dtype=np.int32)
-        query_start = np.zeros(len(entries) + 1, dtype=np.int32)
+        count = len(entries)
+        singles = [i for i in range(count) if lens[i] == 1]
+        order = singles + [i for i in range(count) if lens[i] != 1] if 0 < len(singles) < count else list(range(count))
+        place_of = [0] * count
+        for placed, index in enumerate(order):
+            place_of[index] = placed
+        query_lens = np.asarray([lens[i] for i in order], dtype=np.int32)
+        context_lens = np.asarray([starts[i] for i in order], dtype=np.int32)
+        query_start = np.zeros(count + 1, dtype=np.int32)
         np.cumsum(query_lens, out=query_start[1:])
         total = int(query_start[-1])
         token_ids = np.fromiter(
-            (t for entry in entries for t in entry.token_ids), dtype=np.int64, count=total
+            (t for i in order for t in entries[i].token_ids), dtype=np.int64, count=total
         )
         if total and (token_ids.min() < 0 or token_ids.max() >= self.vocab_size):
             raise ValueError(f"token id outside the vocabulary of {self.vocab_size}")
-        request_of_token = np.repeat(np.arange(len(entries), dtype=np.int32), query_lens)
+        request_of_token = np.repeat(np.arange(count, dtype=np.int32), query_lens)
         positions = (
             np.arange(total, dtype=np.int32)
             - np.repeat(query_start[:-1] - context_lens, query_lens)
@@ -227,6 +240,7 @@ class StepFunction:
         rows: list[tuple[Hashable, int]] = []
         logit_rows: list[int] = []
         for index, entry in enumerate(entries):
+            first = int(query_start[place_of[index]])
             for place in entry.want:
                 if not 0 <= place < lens[index]:
                     raise ValueError(
@@ -234,11 +248,11 @@ class StepFunction:
                         f"{lens[index]} tokens"
                     )
                 rows.append((entry.request_id, int(place)))
-                logit_rows.append(int(query_start[index]) + int(place))
+                logit_rows.append(first + int(place))
         spans = {
             entry.request_id: (starts[i], starts[i] + lens[i]) for i, entry in enumerate(entries)
         }
-        slots = np.asarray([cache.slot(entry.request_id) for entry in entries], dtype=np.int32)
+        slots = np.asarray([cache.slot(entries[i].request_id) for i in order], dtype=np.int32)
         host = HostBatch(
             token_ids=token_ids.astype(np.int32),
             positions=positions,
@@ -249,6 +263,7 @@ class StepFunction:
             slots=slots,
             logit_rows=np.asarray(logit_rows, dtype=np.int32),
             tables=[],
+            num_single=len(singles),
         )
         host._table_width = table_width  # type: ignore[attr-defined]
         return host, rows, spans
@@ -293,7 +308,8 @@ class StepFunction:
             block_tables=list(views[8:8 + len(host.tables)]),
             host=host,
             bindings=self.pools.bindings,
-            all_decode=bool((host.query_lens == 1).all()),
+            all_decode=host.num_single == host.num_requests,
+            num_single=host.num_single,
             extras=extras,
         )
 

@@ -219,11 +219,11 @@ class Ops:
 
     def plan_attention(self, host: Any, group: int) -> dict[str, Any]:
         """Integer work lists the attention kernels want in a step's metadata (may be empty)."""
-        if self.code != BF16 or bool((host.query_lens == 1).all()):
+        if self.code != BF16 or host.num_single == host.num_requests:
             return {}
         from . import tensor_attention
 
-        return tensor_attention.plan_tiles(host.query_lens, group)
+        return tensor_attention.plan_tiles(host.query_lens, group, skip=host.num_single)
 
     def check_errors(self) -> None:
         """Reads the device error word (synchronises) and raises if a kernel flagged a fault."""

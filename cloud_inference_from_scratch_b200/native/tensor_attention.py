@@ -2,10 +2,11 @@
 csrc/attention_prefill_tc.cu), one build per head size.
 
 ``plan`` turns a step's request lengths into the tile list of the prefill kernels (on the host,
-with numpy; it rides in the step's single metadata copy).  ``run`` picks the kernel: a step in
-which every request brings exactly one token goes to the split-key decode kernel; any other
-step to the tcgen05 prefill kernel where it exists (head size 64 or 128, no window, pages of a
-multiple of 16 tokens), else to the mma.sync prefill kernel.
+with numpy; it rides in the step's single metadata copy).  ``run`` picks the kernels: requests
+that bring exactly one token (they lead the batch) go to the split-key decode kernel; the
+others to the tcgen05 prefill kernel where it exists (head size 64 or 128, no window, pages of a
+multiple of 16 tokens), else to the mma.sync prefill kernel.  A mixed step therefore launches
+two attention kernels, each on its own rows.
 """
 
 from __future__ import annotations
@@ -40,10 +41,12 @@ def heads_per_tile(group: int) -> int:
     return min(group, BM)
 
 
-def plan_tiles(query_lens: np.ndarray, group: int) -> dict[str, np.ndarray]:
-    """Tile list of the prefill kernel: (request, first token of the tile), longest work first."""
+def plan_tiles(query_lens: np.ndarray, group: int, skip: int = 0) -> dict[str, np.ndarray]:
+    """Tile list of the prefill kernel: (request, first token of the tile), longest work first.
+    The first ``skip`` requests get no tile (single tokens that the decode kernel takes)."""
     tokens_per_tile = BM // heads_per_tile(group)
     counts = -(-query_lens.astype(np.int64) // tokens_per_tile)
+    counts[:skip] = 0
     total = int(counts.sum())
     request = np.repeat(np.arange(len(query_lens), dtype=np.int32), counts)
     first = np.cumsum(counts) - counts
@@ -139,8 +142,9 @@ class TensorAttention:
             return False
         table = ctx.block_tables[kv.group]
         group = q_heads // kv_heads
-        if ctx.all_decode:
-            requests = ctx.num_requests
+        singles = ctx.num_single
+        if singles:
+            requests = singles
             max_keys = table.shape[1] * kv.page_size
             if window > 0:
                 max_keys = min(max_keys, window)
@@ -152,9 +156,10 @@ class TensorAttention:
                          ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, kv.page_size,
                          splits, chunks, MIN_KEYS_PER_CHUNKED_CTA, self._chunk_shares.data_ptr(), self._chunk_tickets.data_ptr(),
                          scale, window, self.use_tma, ops.error_word.data_ptr(), ops.stream)
-            return True
+            if singles == ctx.num_requests:
+                return True
         if plan is None:
-            tiles = plan_tiles(ctx.host.query_lens, group)
+            tiles = plan_tiles(ctx.host.query_lens, group, skip=singles)
             plan = {name: torch.from_numpy(array).to(ops.device) for name, array in tiles.items()}
         num_tiles = plan["tile_request"].shape[0]
         ops.launches += 1

@@ -222,6 +222,7 @@ def attention_case(ops, dtype, contexts, query_lens, q_heads, kv_heads, dim, pag
                            query_start=np.concatenate([[0], np.cumsum(query_lens)]).astype(np.int32))
     ctx = SimpleNamespace(positions=positions, request_of_token=request_of, block_tables=[table],
                           host=host, all_decode=all(n == 1 for n in query_lens), extras={},
+                          num_single=len(query_lens) if all(n == 1 for n in query_lens) else 0,
                           num_tokens=tokens, num_requests=len(query_lens),
                           context_lens=torch.tensor(contexts, dtype=torch.int32).cuda(),
                           query_lens=torch.tensor(query_lens, dtype=torch.int32).cuda(),
