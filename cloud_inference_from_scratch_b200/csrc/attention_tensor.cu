@@ -811,6 +811,371 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
   if (tid == 0) a.counters[unit] = 0;   // ready for the next launch
 }
 
+// ------------------------------------------------------------------------------------ decode, split over CTAs
+// The decode kernel for pools that TMA can read (pages of a power of two >= 16 tokens, head size a
+// multiple of 64).  A request's keys are cut into `splits` ranges, one CTA each, with no cluster:
+// a CTA is 4 warps and a ring of SPLIT_STAGES stages of 64 keys (K and V of a stage arrive by
+// one mbarrier; 16 KB of keys and 16 KB of values at head size 128), so two or three CTAs fit an
+// SM and every SM has work at small batches.  Warp w multiplies the w-th 16 keys of a stage.  A
+// CTA leaves its share (unnormalised output, maximum, sum of 16 head rows) in global memory and
+// draws a ticket; whoever draws the last ticket of a (request, kv head, 16 heads) unit adds the
+// shares up and writes the output.  Nobody waits for anybody.
+//
+// Before `griddepcontrol.wait` a CTA already asks for the stages that do not hold the newest key:
+// block tables and context lengths come with the step's metadata and older keys and values are
+// not touched by the kernel before this one (it writes the newest token only).
+constexpr int SPLIT_WARPS = 4;
+constexpr int SPLIT_TILE = SPLIT_WARPS * DN;          // keys per stage
+constexpr int SPLIT_MAX_STAGES = 8;                   // one lane of the first warp per 16-key block in flight
+constexpr int SPLIT_MAX = 64;                         // most CTAs that share a request's keys
+constexpr int SPLIT_BLOCK = DN * D;                   // elements of one 16-key block of K (or V)
+constexpr int SPLIT_STAGE = 2 * SPLIT_TILE * D;       // elements of a stage: 4 K blocks, then 4 V blocks
+constexpr int SPLIT_SHARE_ROW = D + 4;                // floats of a share's row: D outputs, maximum, sum, padding
+constexpr int SPLIT_SHARE = 16 * SPLIT_SHARE_ROW;     // floats of a CTA's share
+constexpr int SPLIT_PAGE_SLOTS = 512;                 // the first block-table entries of a request, kept in shared memory
+constexpr size_t SPLIT_STAGE_BYTES = (size_t)SPLIT_STAGE * sizeof(bf16);
+constexpr size_t SPLIT_MERGE_BYTES = (size_t)SPLIT_WARPS * 16 * D * sizeof(float);
+constexpr int SPLIT_MIN_STAGES = (int)((SPLIT_MERGE_BYTES + SPLIT_STAGE_BYTES - 1) / SPLIT_STAGE_BYTES);   // the merge buffers reuse the ring
+static_assert(SPLIT_MAX_STAGES * SPLIT_WARPS <= 32, "one lane of the first warp per 16-key block in flight");
+constexpr size_t split_smem(int stages) { return 1024 + DECODE_Q_BYTES + (size_t)stages * SPLIT_STAGE_BYTES; }
+
+struct SplitArgs {
+  const bf16* q;            // row b of q_stride elements: the request's single query token
+  int q_stride;
+  bf16* out;
+  int out_stride;
+  Pools pools;
+  const int* context_lens;  // keys before the query token; it attends to context + 1 keys
+  int group;
+  int head_chunks;          // ceil(group / 16)
+  int page_shift;           // log2(page_size)
+  int splits;               // CTAs launched per unit (1 .. SPLIT_MAX)
+  int min_keys;             // a request uses only as many of them as leave every CTA this many keys
+  int stages;               // stages of the ring (SPLIT_MIN_STAGES .. SPLIT_MAX_STAGES)
+  float* shares;            // [unit][split][16][D + 4]
+  int* tickets;             // [unit]; zero between launches
+  float scale_log2;
+  int window;
+  int* err;
+};
+
+// The CTA that drew a unit's last ticket adds up the unit's shares: every thread takes four columns
+// of one head row, asks for the maxima, sums and outputs of eight shares at one time and merges
+// them with a running maximum (in the order of the shares, so the result does not depend on who
+// came last).
+__device__ __noinline__ void merge_shares(const float* unit_shares, int count, bf16* out_rows, int rows, int tid) {
+  for (int idx = tid; idx < rows * (D / 4); idx += SPLIT_WARPS * 32) {
+    const int r = idx / (D / 4), c4 = idx % (D / 4);
+    const float* row = unit_shares + r * SPLIT_SHARE_ROW;
+    float m_run = -INFINITY, sum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c0 = 0; c0 < count; c0 += 8) {
+      float ms[8], ls[8];
+      float4 part[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool live = c0 + j < count;
+        const float* share = row + (size_t)(live ? c0 + j : c0) * SPLIT_SHARE;
+        ms[j] = live ? __ldcg(share + D) : -INFINITY;
+        ls[j] = live ? __ldcg(share + D + 1) : 0.f;
+        part[j] = __ldcg(reinterpret_cast<const float4*>(share + c4 * 4));
+      }
+      float m_new = m_run;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m_new = fmaxf(m_new, ms[j]);
+      const float keep = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+      sum *= keep; acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float f = (ms[j] == -INFINITY) ? 0.f : exp2f(ms[j] - m_new);
+        sum += ls[j] * f;
+        acc.x += part[j].x * f; acc.y += part[j].y * f; acc.z += part[j].z * f; acc.w += part[j].w * f;
+      }
+      m_run = m_new;
+    }
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    uint2 packed;
+    packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+    packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out_rows + (size_t)r * D + c4 * 4) = packed;
+  }
+}
+
+#ifdef SPLIT_TRACE
+// Debug builds only (-DSPLIT_TRACE): every CTA leaves the global timer at eight points of its life.
+__device__ long long* g_split_trace = nullptr;
+__device__ __forceinline__ void split_mark(int point) {
+  if (threadIdx.x == 0 && g_split_trace) {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    g_split_trace[cta * 8 + point] = t;
+  }
+}
+#define SPLIT_MARK(point) split_mark(point)
+#else
+#define SPLIT_MARK(point)
+#endif
+
+__global__ void __launch_bounds__(SPLIT_WARPS * 32)
+decode_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    const SplitArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_unaligned[];
+  unsigned char* smem_raw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                          // [16][ROW]
+  bf16* ring = reinterpret_cast<bf16*>(smem_raw + DECODE_Q_BYTES);        // a.stages stages
+  float* merge_s = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES);   // reused after the loop: [warp][16][D]
+  __shared__ __align__(8) uint64_t full[SPLIT_MAX_STAGES];
+  __shared__ int pages_s[SPLIT_PAGE_SLOTS];
+  __shared__ float warp_max_s[SPLIT_WARPS][16], warp_sum_s[SPLIT_WARPS][16];
+  __shared__ int last_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  SPLIT_MARK(0);
+  // the split is the slowest index of the grid: the CTAs a short request does not use come last
+  const int split = blockIdx.z;
+  const int kvh = blockIdx.x / a.head_chunks, h0 = (blockIdx.x % a.head_chunks) * 16;
+  const int request = blockIdx.y;
+  const int stages = a.stages;
+  const int* table_row = a.pools.table + (size_t)request * a.pools.table_width;
+  // the request's block-table row goes to shared memory once, asked for together with its length,
+  // so that no copy has to wait for a table entry from global memory first
+  const int cached = min(a.pools.table_width, SPLIT_PAGE_SLOTS);
+  for (int i = tid; i < cached; i += SPLIT_WARPS * 32) pages_s[i] = table_row[i];
+  const int length = a.context_lens[request] + 1;
+  const int first = (a.window > 0 && length > a.window) ? length - a.window : 0;
+  const int first_block = first / DN;                      // 16-key blocks are the unit of a copy
+  const int blocks = (length + DN - 1) / DN - first_block;
+  // how many of the launched CTAs this request uses: the launch is sized for the longest context
+  // the tables can hold, the request may be far shorter; the others leave at once
+  const int used = max(1, min(a.splits, (length - first) / a.min_keys));
+  if (split >= used) return;
+  const int per_split = (blocks + used - 1) / used;        // in blocks
+  const int begin = (first_block + split * per_split) * DN;
+  const int end = min(length, begin + per_split * DN);
+  const int tiles = begin < end ? (end - begin + SPLIT_TILE - 1) / SPLIT_TILE : 0;
+
+  if (tid < stages) mbar_init(&full[tid], 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  __syncthreads();
+
+  // The first warp feeds the ring: tiles [tile0, tile0 + count) go to stages slot0, slot0 + 1, ...;
+  // lane 4 t + b copies the b-th 16 keys (and values) of the t-th of them.
+  auto issue = [&](int tile0, int count, int slot0) {
+    const int t = lane >> 2, b = lane & 3;
+    const int tile = tile0 + t;
+    const int k0 = begin + tile * SPLIT_TILE;
+    const bool active = t < count && tile < tiles;
+    const int in_tile = active ? min(SPLIT_WARPS, (end - k0 + DN - 1) / DN) : 0;   // 16-key blocks of the tile
+    int slot = slot0 + t;
+    if (slot >= stages) slot -= stages;
+    uint64_t* bar = &full[slot];
+    if (active && b == 0) mbar_expect_tx(bar, (uint32_t)(in_tile * 2 * SPLIT_BLOCK * sizeof(bf16)));
+    __syncwarp();
+    if (b < in_tile) {
+      const int key = k0 + b * DN;
+      const int index = key >> a.page_shift, within = key & (a.pools.page_size - 1);
+      int page;
+      if (index < cached) page = pages_s[index];
+      else page = index < a.pools.table_width ? table_row[index] : -1;
+      if (page < 0 || page >= a.pools.num_pages) {
+        atomicOr(a.err, kErrBadPage);
+        page = 0;   // the copies must still happen, or the barrier would never complete
+      }
+      const int row0 = (page * a.pools.kv_heads + kvh) * a.pools.page_size + within;
+      bf16* k_dst = ring + slot * SPLIT_STAGE + b * SPLIT_BLOCK;
+      bf16* v_dst = k_dst + SPLIT_WARPS * SPLIT_BLOCK;
+      if constexpr (kBlockCopies) {
+        if constexpr (D == 128) {
+          bw::tma_load_4d(k_dst, &k_map, bar, 0, 0, 0, row0 / 8);
+          bw::tma_load_4d(v_dst, &v_map, bar, 0, 0, 0, row0 / 8);
+        } else {
+          bw::tma_load_3d(k_dst, &k_map, bar, 0, 0, row0 / 8);
+          bw::tma_load_3d(v_dst, &v_map, bar, 0, 0, row0 / 8);
+        }
+      } else {
+#pragma unroll
+        for (int sub = 0; sub < D / 64; ++sub) {
+          tma_load_2d(k_dst + sub * 1024, &k_map, bar, sub * 64, row0);
+          tma_load_2d(v_dst + sub * 1024, &v_map, bar, sub * 64, row0);
+        }
+      }
+    }
+  };
+  // stages that can be asked for before the kernels before this one have finished: those that do
+  // not hold the newest key (position length - 1)
+  int early = 0;
+  while (early < stages && early < tiles && begin + (early + 1) * SPLIT_TILE <= length - 1) ++early;
+  SPLIT_MARK(1);
+  if (warp == 0 && early) issue(0, early, 0);
+  pdl_wait();
+  pdl_trigger();
+  SPLIT_MARK(2);
+  for (int idx = tid; idx < 16 * CHUNKS; idx += SPLIT_WARPS * 32) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = h0 + r < a.group;
+    const bf16* src = ok ? a.q + (size_t)request * a.q_stride + (size_t)(kvh * a.group + h0 + r) * D + c * 8 : a.q;
+    cp_async16(q_s + r * ROW + c * 8, src, ok);
+  }
+  cp_async_commit();
+  if (warp == 0 && early < stages && early < tiles) issue(early, stages - early, early);
+  cp_async_wait<0>();
+  __syncthreads();
+  uint32_t q_frag[KSTEPS][4];
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk)
+    ldsm_x4(q_frag[kk], q_s + (lane & 15) * ROW + kk * 16 + (lane >> 4) * 8);
+
+  float o[NTILES_D][4];
+#pragma unroll
+  for (int i = 0; i < NTILES_D; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int t4 = lane & 3;
+
+  // A copy that did not arrive in time has set the error bit.  Before the CTA gives up the shared
+  // memory that copies still in flight target, every one of them gets one more bounded wait: the
+  // tiles from `it` on that were asked for, each on its stage and parity.
+  auto drain = [&](int it, int stage, uint32_t phases) {
+    for (int j = 0; j < stages && it + j < tiles; ++j) {
+      int slot = stage + j;
+      if (slot >= stages) slot -= stages;
+      mbar_wait(&full[slot], (phases >> slot) & 1u, a.err);
+    }
+  };
+  int stage = 0, failed_at = -1, failed_stage = 0;
+  uint32_t phases = 0;   // bit s: the parity to wait for on stage s
+  for (int it = 0; it < tiles; ++it) {
+    const uint32_t parity = (phases >> stage) & 1u;
+    const bool landed = mbar_wait(&full[stage], parity, a.err);
+    if (it == 0) SPLIT_MARK(3);
+    const int k0 = begin + it * SPLIT_TILE + warp * DN;      // this warp's 16 keys of the stage
+    if (landed && k0 < end) {
+      const bf16* k_tile = ring + stage * SPLIT_STAGE + warp * SPLIT_BLOCK;
+      const bf16* v_tile = k_tile + SPLIT_WARPS * SPLIT_BLOCK;
+      float s[DN / 8][4];
+      scores<DN / 16, true>(q_frag, k_tile, s, lane);
+      if (k0 >= first && k0 + DN <= end) {
+#pragma unroll
+        for (int i = 0; i < DN / 8; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[i][e] *= a.scale_log2;
+      } else {
+#pragma unroll
+        for (int i = 0; i < DN / 8; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = k0 + i * 8 + 2 * t4 + (e & 1);
+            s[i][e] = (key >= first && key < end) ? s[i][e] * a.scale_log2 : -INFINITY;
+          }
+      }
+      if (a.group - h0 <= 8) softmax_update<DN / 8, 1>(s, m, l, o);
+      else softmax_update<DN / 8, 2>(s, m, l, o);
+      accumulate<DN / 16, true>(s, v_tile, o, lane);
+    }
+    if (it + stages < tiles) {
+      // everybody is done with the stage (and agrees on whether its copies arrived) before it is refilled
+      if (!__syncthreads_and(landed)) {
+        if (tid == 0) drain(it, stage, phases);
+        return;
+      }
+      if (warp == 0) issue(it + stages, 1, stage);
+    } else if (!landed) {
+      // nothing is refilled any more, so no barrier lies ahead in the loop: leave it, and find out
+      // together below
+      failed_at = it;
+      failed_stage = stage;
+      break;
+    }
+    phases ^= 1u << stage;
+    if (++stage == stages) stage = 0;
+  }
+  SPLIT_MARK(4);
+
+  // ---- merge the warps.  Each warp puts its row maxima and sums down; then everybody knows the
+  // CTA's maxima, scales its own outputs to them in registers and puts them down too ([warp][16][D],
+  // the ring is free by then); the sums over the warps are formed while the share is written.
+  const int g = lane >> 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const float total = quad_sum(l[h]);
+    if (t4 == 0) {
+      warp_max_s[warp][g + h * 8] = m[h];
+      warp_sum_s[warp][g + h * 8] = total;
+    }
+  }
+  // (this barrier lies behind every warp's last use of the ring, which the merge buffers reuse)
+  if (!__syncthreads_and(failed_at < 0)) {
+    if (tid == 0 && failed_at >= 0) drain(failed_at, failed_stage, phases);
+    return;
+  }
+  float scale_mine[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + h * 8;
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < SPLIT_WARPS; ++w) m_all = fmaxf(m_all, warp_max_s[w][r]);
+    scale_mine[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_all);
+  }
+  float* my_merge = merge_s + warp * 16 * D;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + h * 8;
+#pragma unroll
+    for (int i = 0; i < NTILES_D; ++i)
+      *reinterpret_cast<float2*>(my_merge + r * D + i * 8 + 2 * t4) =
+          make_float2(o[i][2 * h] * scale_mine[h], o[i][2 * h + 1] * scale_mine[h]);
+  }
+  __syncthreads();
+  const int unit = request * gridDim.x + blockIdx.x;
+  float* unit_shares = a.shares + (size_t)unit * a.splits * SPLIT_SHARE;
+  float* share = unit_shares + (size_t)split * SPLIT_SHARE;
+  const int live_rows = min(16, a.group - h0);
+  bf16* out_rows = a.out + (size_t)request * a.out_stride + (size_t)(kvh * a.group + h0) * D;
+  for (int idx = tid; idx < live_rows * (D / 4); idx += SPLIT_WARPS * 32) {
+    const int r = idx / (D / 4), c4 = idx % (D / 4);
+    float4 acc = *reinterpret_cast<const float4*>(merge_s + r * D + c4 * 4);
+#pragma unroll
+    for (int w = 1; w < SPLIT_WARPS; ++w) {
+      const float4 part = *reinterpret_cast<const float4*>(merge_s + (w * 16 + r) * D + c4 * 4);
+      acc.x += part.x; acc.y += part.y; acc.z += part.z; acc.w += part.w;
+    }
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < SPLIT_WARPS; ++w) m_all = fmaxf(m_all, warp_max_s[w][r]);
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < SPLIT_WARPS; ++w) {
+      const float mw = warp_max_s[w][r];
+      sum += warp_sum_s[w][r] * ((mw == -INFINITY) ? 0.f : exp2f(mw - m_all));
+    }
+    if (used == 1) {   // the request is this CTA's alone: no share, the output itself
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+      uint2 packed;
+      packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+      packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(out_rows + (size_t)r * D + c4 * 4) = packed;
+    } else {
+      __stcg(reinterpret_cast<float4*>(share + r * SPLIT_SHARE_ROW + c4 * 4), acc);
+      if (c4 == 0) {
+        __stcg(share + r * SPLIT_SHARE_ROW + D, m_all);
+        __stcg(share + r * SPLIT_SHARE_ROW + D + 1, sum);
+      }
+    }
+  }
+  if (used == 1) return;
+  SPLIT_MARK(5);
+  __threadfence();   // this thread's part of the share is visible before the ticket is drawn
+  __syncthreads();
+  if (tid == 0) last_s = atomicAdd(&a.tickets[unit], 1) == used - 1;
+  __syncthreads();
+  SPLIT_MARK(6);
+  if (!last_s) return;
+  __threadfence();
+  merge_shares(unit_shares, used, out_rows, live_rows, tid);
+  if (tid == 0) a.tickets[unit] = 0;   // ready for the next launch
+  SPLIT_MARK(7);
+}
+
 // ------------------------------------------------------------------------------------ tensor maps
 }  // namespace cie
 
@@ -955,4 +1320,85 @@ extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int 
     return launch_decode<true>(k_map, v_map, a, requests, (cudaStream_t)stream);
   }
   return launch_decode<false>(k_map, v_map, a, requests, (cudaStream_t)stream);
+}
+
+// How many CTAs of the split decode kernel with a ring of `stages` stages fit one SM (its shared
+// memory decides); 0 if the head size is not its kind or the ring is out of range, -1 on failure.
+extern "C" int cie_attention_decode_split_ctas_per_sm(int stages) {
+  if (D % 64 || stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES) return 0;
+  const size_t smem = split_smem(stages);
+  if (cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)split_smem(SPLIT_MAX_STAGES)) != cudaSuccess) {
+    cudaGetLastError();
+    if (cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+  }
+  int ctas = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, decode_split_kernel, SPLIT_WARPS * 32, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return ctas;
+}
+
+extern "C" int cie_attention_decode_split_max() { return SPLIT_MAX; }
+extern "C" int cie_attention_decode_split_tile() { return SPLIT_TILE; }
+
+#ifdef SPLIT_TRACE
+extern "C" int cie_attention_decode_split_trace(void* buffer) {
+  return cudaMemcpyToSymbol(g_split_trace, &buffer, sizeof(buffer)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
+// The split decode kernel.  splits: CTAs launched per (request, kv head, 16 heads) unit, 1 ..
+// cie_attention_decode_split_max(); a request uses as many of them as leave each `min_keys` keys.
+// shares: float32 [requests * kv_heads * ceil(group / 16)][splits][16][head size + 4]; tickets: one
+// int per unit, zero before the first launch (the kernel leaves them zero).  Needs pages of a power
+// of two >= 16 tokens, a head size that is a multiple of 64 and 16-byte-aligned pools (the caller
+// checks and takes the other decode kernel where that does not hold).
+extern "C" int cie_attention_decode_split(const void* q, int q_stride, void* out, int out_stride,
+                                          const void* k_pool, const void* v_pool, const int* table,
+                                          int table_width, int num_pages, const int* context_lens,
+                                          int requests, int q_heads, int kv_heads, int page_size,
+                                          int splits, int min_keys, int stages, float* shares, int* tickets,
+                                          float scale, int window, int* err, void* stream) {
+  if (requests <= 0) return 0;
+  if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_decode_split: %d query heads over %d kv heads", q_heads, kv_heads);
+  if (splits < 1 || splits > SPLIT_MAX) CIE_FAIL("attention_decode_split: 1 to %d CTAs per request, got %d", SPLIT_MAX, splits);
+  if (q_stride % 8) CIE_FAIL("attention_decode_split: row stride must keep 16-byte alignment");
+  if (min_keys < 1) CIE_FAIL("attention_decode_split: min_keys must be positive");
+  if (stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES)
+    CIE_FAIL("attention_decode_split: %d to %d stages, got %d", SPLIT_MIN_STAGES, SPLIT_MAX_STAGES, stages);
+  if (splits > 1 && (!shares || !tickets)) CIE_FAIL("attention_decode_split: several CTAs per request need scratch memory");
+  int page_shift = -1;
+  for (int shift = 0; shift < 31; ++shift)
+    if ((1 << shift) == page_size) page_shift = shift;
+  if (D % 64 || page_shift < 4 ||
+      ((reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) != 0)
+    CIE_FAIL("attention_decode_split: needs head size %% 64 == 0 (got %d), pages of a power of two >= 16 "
+             "(got %d) and 16-byte-aligned pools", D, page_size);
+  SplitArgs a;
+  a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
+  a.pools = Pools{(const bf16*)k_pool, (const bf16*)v_pool, table, table_width, num_pages, kv_heads, page_size};
+  a.context_lens = context_lens; a.group = q_heads / kv_heads; a.head_chunks = (a.group + 15) / 16;
+  a.page_shift = page_shift; a.splits = splits; a.min_keys = min_keys; a.stages = stages; a.shares = shares; a.tickets = tickets;
+  a.scale_log2 = scale * kLog2e; a.window = window; a.err = err;
+  CUtensorMap k_map = {}, v_map = {};
+  const long long rows = (long long)num_pages * kv_heads * page_size;
+  const bool mapped = kBlockCopies
+      ? bw::tensor_map_bf16_row_blocks(k_pool, rows, D, 16, &k_map) && bw::tensor_map_bf16_row_blocks(v_pool, rows, D, 16, &v_map)
+      : bw::tensor_map_bf16(k_pool, rows, D, 16, &k_map) && bw::tensor_map_bf16(v_pool, rows, D, 16, &v_map);
+  if (!mapped) CIE_FAIL("attention_decode_split: cuTensorMapEncodeTiled failed");
+  const size_t smem = split_smem(stages);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t status = cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (status != cudaSuccess) CIE_FAIL("attention_decode_split: shared memory %zu: %s", smem, cudaGetErrorString(status));
+    configured = smem;
+  }
+  if (requests > 65535) CIE_FAIL("attention_decode_split: at most 65535 requests a launch, got %d", requests);
+  dim3 grid(kv_heads * a.head_chunks, requests, splits);
+  CIE_LAUNCH("attention_decode_split", decode_split_kernel, grid, dim3(SPLIT_WARPS * 32), smem, (cudaStream_t)stream, k_map, v_map, a);
+  return 0;
 }

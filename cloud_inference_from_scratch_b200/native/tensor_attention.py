@@ -21,8 +21,13 @@ import numpy as np
 from .build import load_library
 
 BM = 128           # query rows of a prefill tile (must match the kernel)
-SM_COUNT = 148
+SM_COUNT = 148     # only where the device cannot be asked (the planners take the device's own count)
 MIN_KEYS_PER_SPLIT = 128
+# the split decode kernel: a CTA keeps at least this many keys (four stages of 64), so that its
+# set-up and the hand-over of its share stay small beside the keys it streams
+MIN_KEYS_PER_SPLIT_CTA = int(os.environ.get("CIE_DECODE_SPLIT_KEYS", "256"))
+# "CTAs per unit,stages" to launch the split decode kernel with whatever the sizes (for measurements)
+FORCE_SPLIT_PLAN = tuple(int(n) for n in os.environ["CIE_DECODE_SPLIT_PLAN"].split(",")) if os.environ.get("CIE_DECODE_SPLIT_PLAN") else None
 # several clusters per request only while each CTA keeps this many keys: handing the shares over
 # through global memory costs about as much as streaming a thousand keys
 MIN_KEYS_PER_CHUNKED_CTA = int(os.environ.get("CIE_DECODE_CHUNK_KEYS", "1024"))
@@ -77,11 +82,35 @@ class TensorAttention:
         self._decode_clusters.argtypes = [i, i]
         self._decode_clusters.restype = c_int
         self._cluster_room: dict[int, int] = {}
+        # the split decode kernel (no clusters; shares merged by whoever draws the last ticket): for
+        # pools TMA can read.  Its scratch is sized once for the most CTAs a launch with more than
+        # one CTA per unit can have: four per SM.
         # where clusters of one request leave their shares (at most one CTA an SM takes part), and
         # the tickets that tell the last one; the kernel leaves the tickets at zero
         torch = ops.torch
         self._chunk_shares = torch.zeros(SM_COUNT * 16 * (head_dim + 2), dtype=torch.float32, device=ops.device)
         self._chunk_tickets = torch.zeros(SM_COUNT, dtype=torch.int32, device=ops.device)
+        self._decode_split = None
+        self.sm_count = ops.torch.cuda.get_device_properties(ops.device).multi_processor_count
+        if head_dim % 64 == 0 and os.environ.get("CIE_DECODE_SPLIT", "1") != "0":
+            self._decode_split = lib.function(
+                "cie_attention_decode_split",
+                [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, i, i, v, v, f, i, v, v],
+            )
+            self.split_max = int(lib.handle.cie_attention_decode_split_max())
+            self.split_tile = int(lib.handle.cie_attention_decode_split_tile())
+            per_sm = lib.handle.cie_attention_decode_split_ctas_per_sm
+            per_sm.argtypes = [i]
+            per_sm.restype = c_int
+            # ring depths the kernel can be launched with, and how many CTAs an SM then holds
+            self.split_rings = {stages: int(per_sm(stages)) for stages in range(1, 9)}
+            self.split_rings = {stages: ctas for stages, ctas in self.split_rings.items() if ctas >= 1}
+            if not self.split_rings:
+                raise RuntimeError(f"the split decode kernel does not fit this device at head size {head_dim}")
+            self.split_cta_limit = 4 * self.sm_count
+            self._split_shares = ops.torch.zeros(self.split_cta_limit * 16 * (head_dim + 4), dtype=ops.torch.float32,
+                                                 device=ops.device)
+            self._split_tickets = ops.torch.zeros(self.split_cta_limit, dtype=ops.torch.int32, device=ops.device)
 
         self.use_tma = 0 if os.environ.get("CIE_DECODE_TMA", "1") == "0" else 1
         # prompt portions on tcgen05 where the kernel exists: head size 64 or 128, no window,
@@ -109,6 +138,35 @@ class TensorAttention:
         return room
 
     @staticmethod
+    def split_plan(units: int, max_keys: int, sm_count: int, rings: dict[int, int], limit: int, most: int,
+                   tile: int = 64, min_keys: int = MIN_KEYS_PER_SPLIT_CTA) -> tuple[int, int]:
+        """(CTAs per unit, stages of the ring) for the split decode kernel.  ``units``: (request, kv
+        head, 16 heads) triples; ``rings``: ring depth -> CTAs an SM holds with it.
+
+        Few units (half the SMs or fewer): one CTA an SM with the deepest ring, so that a CTA can ask
+        for its whole range of keys at once, even before the kernel before it has finished.  More
+        units: two CTAs an SM with the deepest ring that allows it (a CTA is four warps, and four
+        warps alone do not keep an SM's tensor pipe and copy engine busy), every CTA of the launch
+        resident at one time.  Every CTA keeps at least ``min_keys`` keys of the longest context the
+        tables hold; a launch stays within ``limit`` CTAs (the scratch is sized for that) and a unit
+        within ``most``.  Measured on a B200 at head size 128: 8 requests of 2,048 keys 9.8 us with
+        (9, 6) against 10.4 with (8, 3); 64 requests 26.8 us with (2, 3) against 37 with (1, 6)."""
+        depths = sorted(rings, reverse=True)
+        paired = [depth for depth in depths if rings[depth] >= 2]
+        if units * 2 <= sm_count or not paired:
+            stages, slots = depths[0], sm_count
+        else:
+            stages, slots = paired[0], 2 * sm_count
+        by_keys = max(1, max_keys // min_keys)
+        splits = max(1, min(by_keys, slots // max(1, units), most))
+        while splits > 1 and units * splits > limit:
+            splits -= 1
+        # no deeper than the longest range a CTA can get
+        wanted = max(min(depths), min(stages, -(-(-(-max_keys // splits)) // tile)))
+        stages = min(depth for depth in depths if depth >= wanted)
+        return splits, stages
+
+    @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int) -> int:
         """CTAs (of one cluster) that share a request's keys: enough to put work on every SM,
         at least MIN_KEYS_PER_SPLIT keys each, a power of two up to 8."""
@@ -134,6 +192,39 @@ class TensorAttention:
         by_keys = max_keys // (splits * MIN_KEYS_PER_CHUNKED_CTA)
         return max(1, min(by_sms, by_keys, MAX_CHUNKS))
 
+    def _run_decode(self, qkv: Any, out: Any, ctx: Any, kv: Any, table: Any, requests: int, q_heads: int,
+                    kv_heads: int, scale: float, window: int) -> None:
+        """One query token for each of the first ``requests`` requests of the step (their token row
+        is their request index)."""
+        ops = self.ops
+        group = q_heads // kv_heads
+        max_keys = table.shape[1] * kv.page_size
+        if window > 0:
+            max_keys = min(max_keys, window)
+        page = kv.page_size
+        ops.launches += 1
+        if (self._decode_split is not None and page >= 16 and page & (page - 1) == 0
+                and (kv.k.data_ptr() | kv.v.data_ptr()) % 16 == 0):
+            units = requests * kv_heads * -(-group // 16)
+            ctas, stages = self.split_plan(units, max_keys, self.sm_count, self.split_rings, self.split_cta_limit,
+                                           self.split_max, self.split_tile, MIN_KEYS_PER_SPLIT_CTA)
+            if FORCE_SPLIT_PLAN:
+                ctas, stages = FORCE_SPLIT_PLAN
+            self._decode_split(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
+                               kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
+                               ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, page, ctas,
+                               MIN_KEYS_PER_SPLIT_CTA, stages, self._split_shares.data_ptr(),
+                               self._split_tickets.data_ptr(), scale, window, ops.error_word.data_ptr(),
+                               ops.stream)
+            return
+        splits = self.splits_for(requests, kv_heads, group, max_keys)
+        chunks = self.chunks_for(requests, kv_heads, group, max_keys, splits, self.cluster_room(splits))
+        self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
+                     kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
+                     ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, kv.page_size,
+                     splits, chunks, MIN_KEYS_PER_CHUNKED_CTA, self._chunk_shares.data_ptr(), self._chunk_tickets.data_ptr(),
+                     scale, window, self.use_tma, ops.error_word.data_ptr(), ops.stream)
+
     def run(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
             scale: float, window: int, plan: dict[str, Any] | None = None) -> bool:
         ops = self.ops
@@ -144,18 +235,7 @@ class TensorAttention:
         group = q_heads // kv_heads
         singles = ctx.num_single
         if singles:
-            requests = singles
-            max_keys = table.shape[1] * kv.page_size
-            if window > 0:
-                max_keys = min(max_keys, window)
-            splits = self.splits_for(requests, kv_heads, group, max_keys)
-            chunks = self.chunks_for(requests, kv_heads, group, max_keys, splits, self.cluster_room(splits))
-            ops.launches += 1
-            self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
-                         kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
-                         ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, kv.page_size,
-                         splits, chunks, MIN_KEYS_PER_CHUNKED_CTA, self._chunk_shares.data_ptr(), self._chunk_tickets.data_ptr(),
-                         scale, window, self.use_tma, ops.error_word.data_ptr(), ops.stream)
+            self._run_decode(qkv, out, ctx, kv, table, singles, q_heads, kv_heads, scale, window)
             if singles == ctx.num_requests:
                 return True
         if plan is None:

@@ -222,7 +222,7 @@ def attention_case(ops, dtype, contexts, query_lens, q_heads, kv_heads, dim, pag
                            query_start=np.concatenate([[0], np.cumsum(query_lens)]).astype(np.int32))
     ctx = SimpleNamespace(positions=positions, request_of_token=request_of, block_tables=[table],
                           host=host, all_decode=all(n == 1 for n in query_lens), extras={},
-                          num_single=len(query_lens) if all(n == 1 for n in query_lens) else 0,
+                          num_single=next((i for i, n in enumerate(query_lens) if n != 1), len(query_lens)),
                           num_tokens=tokens, num_requests=len(query_lens),
                           context_lens=torch.tensor(contexts, dtype=torch.int32).cuda(),
                           query_lens=torch.tensor(query_lens, dtype=torch.int32).cuda(),
@@ -402,6 +402,32 @@ def test_tensor_attention_decode_of_a_long_context_in_several_clusters(ops, monk
     # a window: the clusters share the last 5,000 keys only, and a key before them must not count
     tensor_case(ops, 32, [7000], [1], 4, 2, 32, 8, window=5000, seed=18, plant=(0, 2500, 4.0))
     tensor_case(ops, 32, [7000], [1], 4, 2, 32, 8, window=5000, seed=19, plant=(0, 1500, 4.0))
+
+
+def test_split_decode_kernel(ops):
+    """The decode kernel that cuts a request's keys over CTAs without a cluster (head sizes that are
+    multiples of 64, pages of a power of two >= 16): 64 requests of very different lengths in one
+    launch; a window whose first key lies inside a page; more than 16 heads on a kv head; head size
+    192; planted keys in the first, a middle and the last CTA's range; and the same object again and
+    again (the tickets must be back at zero after every launch)."""
+    item = ops[torch.bfloat16]
+    item.require_attention(128)
+    assert item._tensor_attention[128]._decode_split is not None
+    contexts = [(i * 379) % 4001 for i in range(64)]
+    contexts[5], contexts[17], contexts[40] = 0, 15, 16
+    tensor_case(ops, 128, contexts, [1] * 64, 16, 2, 128, 16, seed=20, plant=(63, contexts[63] // 2, 4.0))
+    tensor_case(ops, 128, contexts[:33], [1] * 33, 16, 2, 128, 16, seed=21)
+    tensor_case(ops, 128, [2047] * 8, [1] * 8, 16, 2, 128, 16, seed=22, plant=(3, 1, 4.0))
+    tensor_case(ops, 128, [2047] * 8, [1] * 8, 16, 2, 128, 16, seed=23, plant=(7, 2046, 4.0))
+    tensor_case(ops, 128, [30000], [1], 16, 2, 128, 16, seed=24, plant=(0, 17000, 4.0))
+    tensor_case(ops, 64, [7000, 100, 16, 40], [1, 1, 1, 1], 4, 1, 64, 16, window=5000, seed=25, plant=(0, 2100, 4.0))
+    tensor_case(ops, 64, [7000, 100, 16, 40], [1, 1, 1, 1], 4, 1, 64, 16, window=5000, seed=26, plant=(0, 1900, 4.0))
+    tensor_case(ops, 64, [700, 100, 16, 40], [1, 1, 1, 1], 4, 1, 64, 32, window=33, seed=27)
+    tensor_case(ops, 64, [900, 3], [1, 1], 20, 1, 64, 16, seed=28, plant=(0, 450, 4.0))
+    tensor_case(ops, 192, [1000, 77], [1, 1], 3, 1, 192, 32, seed=29, plant=(0, 999, 4.0))
+    tensor_case(ops, 256, [5000], [1], 2, 1, 256, 16, seed=30, plant=(0, 2500, 4.0))
+    # a mixed step: single tokens lead, a prompt portion follows (two launches)
+    tensor_case(ops, 128, [1500, 16, 700, 40], [1, 1, 1, 300], 16, 2, 128, 16, seed=31, plant=(0, 750, 4.0))
 
 
 def test_tensor_attention_long_prompt_whole(ops):
