@@ -251,10 +251,13 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
 #pragma unroll
   for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
+  bool alive = true;
   for (int it = 0; it < steps; ++it) {
     cp_async_wait<STAGES - 2>();
     if constexpr (TMA) {
-      if (!bw::mbar_wait(&full[it % STAGES], (it / STAGES) & 1, a.err ? a.err : &timeout_sink)) break;
+      // A wait that ran out has set the error bit.  The thread waits for nothing more but goes on
+      // through the loop with the others (every barrier is still met; the result is void anyway).
+      if (alive) alive = bw::mbar_wait(&full[it % STAGES], (it / STAGES) & 1, a.err ? a.err : &timeout_sink);
     }
     __syncthreads();
     if (it + STAGES - 1 < steps) load_stage(it + STAGES - 1);
@@ -287,6 +290,13 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
     }
   }
   cp_async_wait<0>();
+  if constexpr (TMA) {
+    // after a time-out copies may still be in flight: each stage gets one more bounded wait before
+    // the shared memory they target is reused below or given up
+    if (!alive && tid == 0)
+      for (int late = max(0, steps - STAGES); late < steps; ++late)
+        bw::mbar_wait(&full[late % STAGES], (late / STAGES) & 1, a.err ? a.err : &timeout_sink);
+  }
   __syncthreads();
 
   // ---- epilogue through shared memory: out_s[token][weight row]

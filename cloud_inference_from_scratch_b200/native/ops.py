@@ -96,8 +96,11 @@ class GateUpWeight:
         self.weight, self.inter, self.block = weight, inter, block
 
 
-SM_COUNT = 148
-STREAM_MAX_ROWS = 16   # more rows than this go to the tile kernels (tcgen05 or the library)
+# More rows than this go to the tile kernels (tcgen05 or the library).  The streaming kernel
+# multiplies with mma.sync, 8 tokens an instruction: built for 32 and 64 rows it was bound by that
+# tensor path (the gate/up product of 64 tokens took 30 us against the library's 17) and its
+# epilogues, which finish a token row per warp, by the number of rows.
+STREAM_MAX_ROWS = 16
 # Up to this many rows a projection adds itself into the residual stream, or rotates and stores
 # q/k/v (cluster epilogues of the streaming kernel): every row count that kernel takes.
 FUSED_RESIDUAL_MAX_ROWS = STREAM_MAX_ROWS
@@ -146,6 +149,7 @@ class Ops:
             raise KernelError(f"unknown gemm mode {self.gemm_mode!r}")
         self.error_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
         v, i, f = c_void_p, c_int, c_float
         ew = _Lib(load_library("elementwise.cu"))
@@ -266,14 +270,16 @@ class Ops:
 
     def stream_plan(self, m: int, n: int, k: int, allow_partials: bool) -> tuple[int, int] | None:
         """(weight rows per CTA, splits along K) for the streaming kernel, or None if the shape
-        is not its kind (more than 64 rows, or K not a multiple of 8)."""
+        is not its kind (more than 16 rows, or K not a multiple of 8)."""
         if self._gemm_stream is None or m > STREAM_MAX_ROWS or k % 8 or k < 8:
             return None
         block_rows = 32
         tiles = -(-n // block_rows)
         splits = 1
         if allow_partials:
-            splits = max(1, min(-(-4 * SM_COUNT // tiles), k // 256, 8))
+            # K is cut until the CTAs fill the slots the device has for them: an SM holds five CTAs
+            # of the kernel, one is left free for the kernel that follows
+            splits = max(1, min(-(-4 * self.sm_count // tiles), k // 256, 8))
         return block_rows, splits
 
     def scratch(self, tag: str, elements: int, reserve: int = 0) -> Any:
@@ -459,7 +465,7 @@ class Ops:
         projection; kept as a yardstick for the hand-written tensor-core kernel."""
         torch = self.torch
         if out.dtype == torch.float32:
-            out.copy_(torch.mm(x, weight.t(), out_dtype=torch.float32))
+            torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)   # float32 straight into the caller's buffer
         else:
             torch.mm(x, weight.t(), out=out)
         if bias is not None:
@@ -539,7 +545,7 @@ class Ops:
         # K slices per block of weight rows (the size of a cluster): about two and a half CTAs an SM
         # was measured best for this small product (its successor, attention, cannot start beside it)
         splits = 8
-        while splits > 1 and (2 * tiles * splits > 5 * SM_COUNT or k_tiles // splits < 2):
+        while splits > 1 and (2 * tiles * splits > 5 * self.sm_count or k_tiles // splits < 2):
             splits //= 2
         row_sq, row_tiles, eps = None, 0, 0.0
         if isinstance(x, NormedInput):
