@@ -58,6 +58,50 @@ def pages_from_bytes(groups: list[GroupSpec], page_size: int, budget: int) -> in
     return int(count)
 
 
+def plan_page_counts(groups: list[GroupSpec], page_size: int, max_requests: int, step_tokens: int = 0,
+                     num_pages: int | None = None, kv_cache_bytes: int | None = None) -> list[int]:
+    """Pages of every group's pool.  A group that keeps all keys gets ``num_pages`` (or what the
+    byte budget allows).  A group that keeps a window of them can never use more than
+    ``max_requests`` times the pages of (window + the tokens one request may bring in one step) plus
+    one, because pages behind the window go back when a step is committed; it gets no more than
+    that, and under a byte budget what it does not need goes to the other groups.  ``step_tokens``
+    0 means the bound is not known: every group is sized alike."""
+    if not groups:
+        return [1]
+    caps: list[int | None] = []
+    for group in groups:
+        if group.window > 0 and step_tokens > 0:
+            caps.append(max_requests * (-(-(group.window + step_tokens) // page_size) + 1))
+        else:
+            caps.append(None)
+
+    def counts(pages: int) -> list[int]:
+        return [pages if cap is None else min(pages, cap) for cap in caps]
+
+    if num_pages is not None:
+        return counts(int(num_pages))
+    if kv_cache_bytes is None:
+        raise ValueError("give num_pages or kv_cache_bytes")
+
+    def cost(pages: int) -> int:
+        return sum(group.bytes_per_token * page_size * n for group, n in zip(groups, counts(pages)))
+
+    if cost(1) > kv_cache_bytes:
+        raise ValueError("kv_cache_bytes too small for even one page")
+    low, high = 1, 2
+    while cost(high) <= kv_cache_bytes and cost(high) > cost(high // 2):
+        low, high = high, high * 2
+    if cost(high) <= kv_cache_bytes:      # every group is at its bound: more pages cost nothing more
+        return counts(high)
+    while high - low > 1:
+        middle = (low + high) // 2
+        if cost(middle) <= kv_cache_bytes:
+            low = middle
+        else:
+            high = middle
+    return counts(low)
+
+
 class CachePools:
     def __init__(self, needs: list[Any], groups: list[GroupSpec], place: dict[int, tuple[int, int]],
                  pages_per_group: list[int], page_size: int, max_slots: int, dtype: Any,

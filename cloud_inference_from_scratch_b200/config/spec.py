@@ -2,8 +2,9 @@
 
 An architecture module turns its typed configuration into a ``ModelSpec``.  Nothing
 below ``ModelSpec`` knows which architecture it came from: a layer is a block kind
-plus a norm, a mixer and a feed-forward, each a ``PartSpec`` (a registered kind and
-its constants).  The run order is a list of ``ScheduleEntry``: it may name a layer
+plus a named map of parts (norms, mixers, feed-forwards), each a ``PartSpec`` (the
+family it belongs to, a registered kind and its constants); which names a block
+expects is the block's own business.  The run order is a list of ``ScheduleEntry``: it may name a layer
 more than once (the weights are shared, each run has a cache of its own unless it
 says otherwise) and an entry may read the cache that an earlier entry wrote instead
 of writing one.
@@ -22,26 +23,60 @@ from typing import Any
 @dataclass(frozen=True)
 class PartSpec:
     """One part: the kind it is registered under, the constants it is built with, and the
-    tensor-name prefix (relative to its layer's prefix) under which its weights are stored."""
+    tensor-name prefix (relative to its layer's prefix) under which its weights are stored.
+    ``family`` is the registry it is looked up in ("norm", "mixer", "feed_forward", "position",
+    "block"); empty means "what the slot's name says" (see ``LayerSpec``)."""
 
     kind: str
     params: dict[str, Any] = field(default_factory=dict)
     prefix: str = ""
+    family: str = ""
 
 
-@dataclass(frozen=True)
+def _family_of(slot: str, spec: PartSpec) -> str:
+    if spec.family:
+        return spec.family
+    if slot.endswith("norm"):
+        return "norm"
+    if slot in ("mixer", "feed_forward"):
+        return slot
+    raise ValueError(f"slot {slot!r} does not say which family its part belongs to; give PartSpec.family")
+
+
+@dataclass(frozen=True, init=False, eq=True)
 class LayerSpec:
-    """One decoder layer: how its parts are arranged (``block``) and what they are.
+    """One decoder layer: how its parts are arranged (``block``) and what they are (``parts``, by
+    slot name).  ``prefix`` is the tensor-name prefix of the layer in the weight files.
 
-    ``prefix`` is the tensor-name prefix of the layer in the weight files.
-    """
+    The pre-norm residual block expects the slots ``mixer``, ``feed_forward``, ``mixer_norm`` and
+    ``feed_forward_norm``, which may also be given as keyword arguments (and read as attributes);
+    another block kind names the slots it wants: a post-norm, a second feed-forward, no
+    feed-forward at all.  ``dataclasses.replace(layer, mixer=...)`` swaps one part."""
 
     prefix: str
     block: PartSpec
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: dict[str, PartSpec]
+
+    def __init__(self, prefix: str, block: PartSpec, parts: dict[str, PartSpec] | None = None,
+                 **named: PartSpec) -> None:
+        merged = dict(parts or {})
+        merged.update(named)
+        for slot, spec in merged.items():
+            if not isinstance(spec, PartSpec):
+                raise TypeError(f"layer {prefix!r}: slot {slot!r} is not a PartSpec")
+        object.__setattr__(self, "prefix", prefix)
+        object.__setattr__(self, "block", block)
+        object.__setattr__(self, "parts", {
+            slot: spec if spec.family else PartSpec(spec.kind, spec.params, spec.prefix, _family_of(slot, spec))
+            for slot, spec in merged.items()
+        })
+
+    def __getattr__(self, name: str) -> PartSpec:
+        # mixer, feed_forward, mixer_norm, feed_forward_norm (or any other slot) by name
+        parts = self.__dict__.get("parts")
+        if parts is not None and name in parts:
+            return parts[name]
+        raise AttributeError(f"layer {self.__dict__.get('prefix')!r} has no part {name!r}")
 
 
 @dataclass(frozen=True)
@@ -73,10 +108,15 @@ class ModelSpec:
     eos_token_id: int | None = None
     # tensors that may be present in the files and are ignored (e.g. a tied head stored twice)
     optional_tensors: tuple[str, ...] = ()
+    embedding_scale: float = 1.0      # the gathered embedding rows are multiplied by this
+    logit_scale: float = 1.0          # logits = softcap * tanh(head(x) * scale / softcap), or head(x) * scale
+    logit_softcap: float = 0.0        # 0: no soft cap
 
     def validate(self) -> None:
         if not self.layers:
             raise ValueError("a model needs at least one layer")
+        if self.logit_softcap < 0:
+            raise ValueError("logit_softcap must be >= 0")
         for index, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule entry {index} names layer {entry.layer}, which does not exist")

@@ -15,7 +15,7 @@ namespace cie {
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ residual, int hidden, int vocab, int* err) {
+                                 float* __restrict__ residual, int hidden, int vocab, float scale, int* err) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
@@ -26,7 +26,18 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
   }
   const T* row = table + (size_t)id * hidden;
   float* out = residual + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_float(row[i]) * scale;
+}
+
+// ---------------------------------------------------------------- logits: scale and soft cap
+// logits[i] = cap * tanh(logits[i] * scale / cap), or logits[i] * scale when cap == 0; float32, in place.
+__global__ void shape_logits_kernel(float* __restrict__ logits, long long count, float scale, float cap) {
+  pdl_wait();
+  pdl_trigger();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const float v = logits[i] * scale;
+    logits[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
@@ -487,12 +498,21 @@ static int threads_for(int n) {
 }
 
 extern "C" int cie_embedding(const int* ids, const void* table, float* residual, int tokens,
-                             int hidden, int vocab, int dtype, int* err, void* stream) {
+                             int hidden, int vocab, float scale, int dtype, int* err, void* stream) {
   if (tokens <= 0) return 0;
   DISPATCH_DTYPE(dtype, "embedding", {
     CIE_LAUNCH("embedding", embedding_kernel<T>, dim3(tokens), dim3(threads_for(hidden / 4)), 0,
-               (cudaStream_t)stream, ids, (const T*)table, residual, hidden, vocab, err);
+               (cudaStream_t)stream, ids, (const T*)table, residual, hidden, vocab, scale, err);
   })
+  return 0;
+}
+
+extern "C" int cie_shape_logits(float* logits, long long count, float scale, float cap, void* stream) {
+  if (count <= 0) return 0;
+  if (cap < 0.f) CIE_FAIL("shape_logits: the soft cap must be >= 0, got %f", cap);
+  const long long blocks = (count + 1023) / 1024;
+  CIE_LAUNCH("shape_logits", shape_logits_kernel, dim3((unsigned)(blocks > 4096 ? 4096 : blocks)), dim3(256), 0,
+             (cudaStream_t)stream, logits, count, scale, cap);
   return 0;
 }
 

@@ -78,6 +78,7 @@ struct StreamArgs {
   int m, n, k;
   int k_per_split;     // multiple of BK
   int mode;
+  int early_trigger;   // mode 4: let the next kernel start before this one has waited for its predecessor
   int* err;            // error word for a wait that ran out (TMA variant), may be null
   // row scale: with row_sq the result rows are multiplied by rstd[m] = rsqrt(sum over tiles of
   // row_sq[m][tile] / K + eps) before bias, partial-sum output or activation (x then holds
@@ -227,13 +228,14 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s)
     if (s < steps) load_w(s);
-  // A product with the residual epilogue lets the next kernel start already now, beside the kernel
-  // before this one: what follows is the next product, and before its own wait a kernel of this
-  // engine touches only what no kernel of the same step writes (weight tiles; key/value tiles of
-  // earlier steps).
-  if (a.mode == kOutResidual) pdl_trigger();
+  // A product with the residual epilogue may let the next kernel start already now, beside the
+  // kernel before this one, if its caller says so (early_trigger): the caller knows that what
+  // follows touches, before its own wait, only what no kernel of the same step writes (weight
+  // tiles; key/value tiles of earlier steps), which is the rule for every kernel of this engine.
+  const bool early = a.mode == kOutResidual && a.early_trigger;
+  if (early) pdl_trigger();
   pdl_wait();
-  if (a.mode != kOutResidual) pdl_trigger();
+  if (!early) pdl_trigger();
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < steps) load_x(s);
@@ -530,12 +532,14 @@ using namespace cie;
 //          3 SiLU(gate)*up with gate/up rows interleaved in blocks of block_rows/2 (one split),
 //          4 residual[M, N] += product (+ bias), sq[M, ceil(N / 32)] = sums of squares of the new
 //          rows per block of 32 columns and, with next_gain, scaled[M, N] = bfloat16(new row *
-//          next_gain); splits must be 1, 2, 4 or 8 (the size of a cluster), block_rows 32.
+//          next_gain); splits must be 1, 2, 4 or 8 (the size of a cluster), block_rows 32;
+//          early_trigger != 0 lets the kernel after this one start before this one has waited for
+//          the kernel before it (see the kernel).
 // block_rows: weight rows per CTA; 32 is the one size built.
 extern "C" int cie_gemm_stream_ex(const void* x, const float* row_sq, int row_tiles, float eps, const void* w,
                                   const float* bias, void* out, float* residual, float* sq, void* scaled,
                                   const float* next_gain, int m, int n, int k, int splits, int mode,
-                                  int block_rows, int* err, void* stream) {
+                                  int block_rows, int early_trigger, int* err, void* stream) {
   if (m <= 0 || n <= 0) return 0;
   if (!x || !w) CIE_FAIL("gemm_stream: null operand");
   if (m > 16) CIE_FAIL("gemm_stream: takes at most 16 rows, got %d", m);
@@ -556,6 +560,7 @@ extern "C" int cie_gemm_stream_ex(const void* x, const float* row_sq, int row_ti
   a.m = m; a.n = n; a.k = k; a.mode = mode; a.err = err;
   a.row_sq = row_sq; a.row_tiles = row_tiles; a.eps = eps;
   a.residual = residual; a.sq = sq; a.scaled = (bf16*)scaled; a.next_gain = next_gain;
+  a.early_trigger = early_trigger;
   return dispatch(a, splits, block_rows, (cudaStream_t)stream);
 }
 
@@ -597,7 +602,7 @@ extern "C" int cie_gemm_stream(const void* x, const void* w, const float* bias, 
                                int n, int k, int splits, int mode, int block_rows, int* err, void* stream) {
   if (mode == kOutResidual) CIE_FAIL("gemm_stream: the residual epilogue is reached through cie_gemm_stream_ex");
   return cie_gemm_stream_ex(x, nullptr, 0, 0.f, w, bias, out, nullptr, nullptr, nullptr, nullptr, m, n, k, splits,
-                            mode, block_rows, err, stream);
+                            mode, block_rows, 0, err, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -49,6 +49,9 @@ class StepContext:
     context_lens: Any         # [B] tokens already in the cache before this step
     query_lens: Any           # [B]
     slots: Any                # [B] per-request state slot
+    request_active: Any       # [B] 1; 0 for a row that only pads a captured batch (it repeats a real
+                              #     row: what it writes to pages is the same again, but per-request
+                              #     state must not be advanced for it)
     logit_rows: Any           # [R] flat token rows whose logits are wanted
     block_tables: list[Any]   # per cache group: [B, W_g], -1 where no page
     # host side ----------------------------------------------------------------------------

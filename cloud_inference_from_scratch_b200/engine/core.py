@@ -15,7 +15,7 @@ from pathlib import Path
 from typing import Any
 
 from ..cache.manager import CacheManager
-from ..cache.pools import CachePools, pages_from_bytes, plan_groups
+from ..cache.pools import CachePools, plan_groups, plan_page_counts
 from ..config.registry import resolve_config, resolve_model
 from ..models.decoder import DecoderModel
 from ..weights.loader import check_tensors, device_tensors
@@ -82,11 +82,11 @@ def build_core(
     needs = model.cache_needs()
     element_size = 4 if dtype in ("float32", "fp32") else 2
     groups, place = plan_groups(needs, element_size)
-    if num_pages is None:
-        if kv_cache_bytes is None:
-            raise ValueError("give num_pages or kv_cache_bytes")
-        num_pages = pages_from_bytes(groups, page_size, kv_cache_bytes) if groups else 1
-    pages_per_group = [num_pages] * max(1, len(groups))
+    if num_pages is None and kv_cache_bytes is None:
+        raise ValueError("give num_pages or kv_cache_bytes")
+    # every group's pool by what its layers can use: a windowed group needs far fewer pages
+    pages_per_group = plan_page_counts(groups, page_size, max_requests, max_tokens_per_step,
+                                       num_pages=num_pages, kv_cache_bytes=kv_cache_bytes)
     cache = CacheManager(groups, page_size, pages_per_group, max_requests, max_model_len)
     pools = CachePools(needs, groups, place, pages_per_group, page_size, max_requests,
                        runtime.dtype, runtime.device)

@@ -7,8 +7,9 @@ token id}``.  Counterpart of ``RaggedRunner`` (src/cloud_engine/engine.py:193-48
 A plan made only of single decoded tokens is replayed from a CUDA graph captured per
 power-of-two batch size (engine.py:320-408): the step's metadata goes into the graph's fixed
 buffers with one copy, rows beyond the real batch repeat the last real row (they rewrite the
-same cache slot with the same values and their tokens are dropped).  Graphs are not used when
-a mixer keeps per-request state, because a repeated row would advance that state twice.
+same cache slot with the same values and their tokens are dropped; ``request_active`` is 0 for
+them).  Graphs are not used when a mixer keeps per-request state and has not declared that it
+honours that flag (``state_in_graphs``), because a repeated row would advance the state twice.
 Sampling parameters (temperature and draw key per row) ride in the same metadata copy; only
 the sampled token ids and the device error word come back to the host.
 """
@@ -67,15 +68,25 @@ class EngineRunner:
         self.result_dev = torch.zeros(1 + self.max_rows, dtype=torch.int32, device=core.runtime.device)
         self.result_host = torch.zeros(1 + self.max_rows, dtype=torch.int32, pin_memory=True)
         self.ops.error_word = self.result_dev[0:1]
-        has_state = any(need.state is not None for need in core.model.cache_needs())
-        self.use_graphs = bool(config.cuda_graph_decode) and not has_state
+        # Steps are captured in CUDA graphs (and decode batches padded by repeating their last row)
+        # unless a part keeps per-request state and has not declared ``state_in_graphs``: that its
+        # forward runs on the device alone and leaves the state of rows with request_active == 0 alone.
+        keepers = [layer.cache_part for layer in core.model.layers
+                   if layer.cache_part is not None and getattr(layer.cache_part, "state_spec", lambda: None)() is not None]
+        self.use_graphs = bool(config.cuda_graph_decode) and all(
+            getattr(part, "state_in_graphs", False) for part in keepers)
+        self.stateful = bool(keepers)
         if self.use_graphs:
             core.step.enable_graphs(config.max_model_len)
         self.table_width = -(-config.max_model_len // core.page_size)
         self._graphs: dict[tuple[int, int], _DecodeGraph] = {}
         self._parity = 0
         self._ahead: _InFlight | None = None   # the next decode step, launched before it was asked for
-        self.pipeline_decode = True
+        # The next decode step is launched before the host knows whether it will be asked for; if it
+        # is not, it is dropped.  What a dropped step wrote to pages lies beyond every committed
+        # length and is written again, but per-request state would have been advanced for good: no
+        # steps ahead when a part keeps state.
+        self.pipeline_decode = not self.stateful
         self.steps_launched_ahead = 0
         self.steps_ahead_adopted = 0
         self.steps_ahead_dropped = 0
@@ -209,6 +220,7 @@ class EngineRunner:
         host.context_lens = grow(host.context_lens)
         host.query_lens = grow(host.query_lens)
         host.slots = grow(host.slots)
+        host.request_active = np.concatenate([host.request_active, np.zeros(extra, dtype=np.int32)])
         host.request_of_token = np.arange(bucket, dtype=np.int32)
         host.query_start = np.arange(bucket + 1, dtype=np.int32)
         host.logit_rows = np.arange(bucket, dtype=np.int32)
@@ -238,6 +250,11 @@ class EngineRunner:
                 raise RuntimeError("a decode graph is captured by a step that has its token ids")
             meta = MetadataBuffer(self.core.runtime.device, words=1 << 12)
             result_dev = torch.zeros(1 + bucket, dtype=torch.int32, device=self.core.runtime.device)
+            # the launches run once before they are captured and replayed: with per-request state
+            # that first run sees every row as inactive, so that the state moves once, not twice
+            active = host.request_active
+            if self.stateful:
+                host.request_active = np.zeros_like(active)
             ctx = step.upload(host, meta)
             self.ops.error_word = result_dev[0:1]
             # once eagerly (allocates workspace, loads kernels), then capture the same launches
@@ -248,6 +265,9 @@ class EngineRunner:
                 self._launch_sampling(logits, ctx, result_dev, bucket)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
+            if self.stateful:
+                host.request_active = active
+                ctx = step.upload(host, meta)      # the same addresses, the real flags
             graph = torch.cuda.CUDAGraph()
             self.core.runtime.workspace.frozen = True
             self.ops.freeze_scratch()

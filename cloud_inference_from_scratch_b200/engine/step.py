@@ -49,6 +49,7 @@ class HostBatch:
     context_lens: np.ndarray
     query_lens: np.ndarray
     slots: np.ndarray
+    request_active: np.ndarray   # 1 per request; 0 for a row that only pads a captured batch
     logit_rows: np.ndarray
     tables: list[np.ndarray]
     extras: dict[Any, dict[str, np.ndarray]] = field(default_factory=dict)
@@ -169,9 +170,10 @@ class StepFunction:
         ``plan_key`` and ``plan(host, cache)`` is asked once per distinct key."""
         planners: dict[Any, Any] = {}
         for layer in self.model.layers:
-            key = getattr(layer.mixer, "plan_key", None)
-            if key is not None and key not in planners:
-                planners[key] = layer.mixer
+            for part in layer.parts.values():
+                key = getattr(part, "plan_key", None)
+                if key is not None and key not in planners:
+                    planners[key] = part
         return planners
 
     def enable_graphs(self, max_model_len: int) -> None:
@@ -261,6 +263,7 @@ class StepFunction:
             context_lens=context_lens,
             query_lens=query_lens,
             slots=slots,
+            request_active=np.ones(count, dtype=np.int32),
             logit_rows=np.asarray(logit_rows, dtype=np.int32),
             tables=[],
             num_single=len(singles),
@@ -285,13 +288,13 @@ class StepFunction:
                        for name, array in arrays.items()]
         arrays = [
             host.token_ids, host.positions, host.request_of_token, host.query_start,
-            host.context_lens, host.query_lens, host.slots, host.logit_rows, *host.tables,
-            *[array for _, _, array in extra_items],
+            host.context_lens, host.query_lens, host.slots, host.request_active, host.logit_rows,
+            *host.tables, *[array for _, _, array in extra_items],
         ]
         views = meta.upload(arrays)
         self.h2d_bytes = sum(_align(a.size) for a in arrays) * 4
         extras: dict[Any, dict[str, Any]] = {}
-        for (key, name, _), view in zip(extra_items, views[8 + len(host.tables):], strict=True):
+        for (key, name, _), view in zip(extra_items, views[9 + len(host.tables):], strict=True):
             extras.setdefault(key, {})[name] = view
         return StepContext(
             num_tokens=host.num_tokens,
@@ -304,8 +307,9 @@ class StepFunction:
             context_lens=views[4],
             query_lens=views[5],
             slots=views[6],
-            logit_rows=views[7],
-            block_tables=list(views[8:8 + len(host.tables)]),
+            request_active=views[7],
+            logit_rows=views[8],
+            block_tables=list(views[9:9 + len(host.tables)]),
             host=host,
             bindings=self.pools.bindings,
             all_decode=host.num_single == host.num_requests,

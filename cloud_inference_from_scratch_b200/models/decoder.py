@@ -1,4 +1,5 @@
-"""A decoder put together from a ``ModelSpec``: embedding, scheduled layers, final norm, head.
+"""A decoder put together from a ``ModelSpec``: embedding (times a constant), scheduled layers,
+final norm, head, logits (times a constant, softly capped).
 
 This is the only model class of the framework; an architecture contributes a
 description, not a class.  The forward pass is the reference's
@@ -14,13 +15,11 @@ from dataclasses import dataclass
 from typing import Any
 
 from ..config.spec import ModelSpec
-from ..native.ops import ResidualSink
 from ..parts.base import (
     Block,
     CacheSpec,
-    FeedForward,
-    Mixer,
     Norm,
+    Part,
     StateSpec,
     TensorSpec,
     build_part,
@@ -30,19 +29,29 @@ from ..parts.base import (
 
 @dataclass
 class LayerParts:
+    """The built parts of one layer by slot name, their arrangement, and the tensor-name prefix of
+    each part in the weight files."""
+
     prefix: str
-    mixer: Mixer
-    feed_forward: FeedForward
-    mixer_norm: Norm
-    feed_forward_norm: Norm
+    parts: dict[str, Part]
+    families: dict[str, str]
     block: Block
     prefixes: dict[str, str]
 
     def named_parts(self):
-        yield self.prefixes["mixer"], self.mixer
-        yield self.prefixes["feed_forward"], self.feed_forward
-        yield self.prefixes["mixer_norm"], self.mixer_norm
-        yield self.prefixes["feed_forward_norm"], self.feed_forward_norm
+        for slot, part in self.parts.items():
+            yield self.prefixes[slot], part
+
+    @property
+    def cache_part(self) -> Part | None:
+        """The part whose cache the layer's binding belongs to (at most one part of a layer keeps one)."""
+        return self.parts.get(self.block.cache_slot)
+
+    def __getattr__(self, name: str) -> Part:      # layer.mixer, layer.feed_forward, ...
+        try:
+            return self.__dict__["parts"][name]
+        except KeyError:
+            raise AttributeError(name) from None
 
 
 @dataclass(frozen=True)
@@ -62,33 +71,27 @@ class DecoderModel:
         self.spec = spec
         self.layers: list[LayerParts] = []
         for layer in spec.layers:
-            mixer = build_part("mixer", layer.mixer)
-            feed_forward = build_part("feed_forward", layer.feed_forward)
-            mixer_norm = build_part("norm", layer.mixer_norm)
-            feed_forward_norm = build_part("norm", layer.feed_forward_norm)
-            block = part_class("block", layer.block.kind)(
-                mixer, feed_forward, mixer_norm, feed_forward_norm, **layer.block.params
-            )
+            parts = {slot: build_part(part.family, part) for slot, part in layer.parts.items()}
+            block = part_class("block", layer.block.kind)(parts, **layer.block.params)
+            keepers = [slot for slot, part in parts.items()
+                       if getattr(part, "cache_spec", None) and (part.cache_spec() or part.state_spec())]
+            if any(slot != block.cache_slot for slot in keepers):
+                raise ValueError(
+                    f"layer {layer.prefix!r}: the parts {keepers} keep a cache, but the block binds only "
+                    f"{block.cache_slot!r} to one"
+                )
             self.layers.append(
                 LayerParts(
-                    prefix=layer.prefix,
-                    mixer=mixer,
-                    feed_forward=feed_forward,
-                    mixer_norm=mixer_norm,
-                    feed_forward_norm=feed_forward_norm,
-                    block=block,
-                    prefixes={
-                        "mixer": layer.prefix + layer.mixer.prefix,
-                        "feed_forward": layer.prefix + layer.feed_forward.prefix,
-                        "mixer_norm": layer.prefix + layer.mixer_norm.prefix,
-                        "feed_forward_norm": layer.prefix + layer.feed_forward_norm.prefix,
-                    },
+                    prefix=layer.prefix, parts=parts, block=block,
+                    families={slot: part.family for slot, part in layer.parts.items()},
+                    prefixes={slot: layer.prefix + part.prefix for slot, part in layer.parts.items()},
                 )
             )
         self.final_norm: Norm = build_part("norm", spec.final_norm)
         # a projection may add itself into the residual stream only if whoever normalises next
         # understands that the sum is already there
-        norms = [self.final_norm] + [n for layer in self.layers for n in (layer.mixer_norm, layer.feed_forward_norm)]
+        norms = [self.final_norm] + [part for layer in self.layers for slot, part in layer.parts.items()
+                                     if layer.families[slot] == "norm"]
         self.norms_accept_accumulated = all(getattr(norm, "accepts_accumulated", False) for norm in norms)
         self.embedding: Any = None
         self.head: Any = None
@@ -114,9 +117,11 @@ class DecoderModel:
     def cache_needs(self) -> list[CacheNeed]:
         needs: list[CacheNeed] = []
         for index, entry in enumerate(self.spec.schedule):
-            mixer = self.layers[entry.layer].mixer
+            keeper = self.layers[entry.layer].cache_part
             owner = index if entry.reads_cache_of is None else entry.reads_cache_of
-            needs.append(CacheNeed(index, owner, mixer.cache_spec(), mixer.state_spec()))
+            pages = keeper.cache_spec() if keeper is not None and hasattr(keeper, "cache_spec") else None
+            state = keeper.state_spec() if keeper is not None and hasattr(keeper, "state_spec") else None
+            needs.append(CacheNeed(index, owner, pages, state))
         for need in needs:
             if need.owner != need.entry:
                 owner = needs[need.owner]
@@ -154,19 +159,17 @@ class DecoderModel:
         rt = self.runtime
         spec = self.spec
         residual = rt.workspace.get("residual", ctx.num_tokens, spec.hidden_size, torch.float32)
-        rt.ops.embedding(ctx.token_ids, self.embedding, residual)
-        sink = ResidualSink(residual) if self.norms_accept_accumulated else None
+        rt.ops.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale)
+        sink = rt.ops.residual_sink(residual) if self.norms_accept_accumulated else None
         ctx.residual_sink = sink
         pending = None
         for index, entry in enumerate(spec.schedule):
             if sink is not None:
-                # who normalises after this layer: the next layer's first norm, if its mixer can
-                # finish a pre-scaled norm; the final norm takes the plain kernel
+                # what the block after this layer wants to know of its first norm (the final norm
+                # takes plain rows)
                 sink.following_gain = None
                 if index + 1 < len(spec.schedule):
-                    following = self.layers[spec.schedule[index + 1].layer].block
-                    if getattr(following.mixer, "takes_normed_input", False) and hasattr(following.mixer_norm, "forward_lazy"):
-                        sink.following_gain = getattr(following.mixer_norm, "lazy_gain", None)
+                    sink.following_gain = self.layers[spec.schedule[index + 1].layer].block.entry_gain()
             pending = self.layers[entry.layer].block.forward(
                 residual, pending, ctx, ctx.bindings[index]
             )
@@ -176,4 +179,5 @@ class DecoderModel:
         logits = rt.workspace.get("logits", ctx.num_logit_rows, spec.vocab_size, torch.float32,
                                   per_request=True)
         rt.ops.linear(x, self.head, None, logits)
+        rt.ops.shape_logits(logits, spec.logit_scale, spec.logit_softcap)
         return logits

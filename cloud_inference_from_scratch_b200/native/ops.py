@@ -15,6 +15,7 @@ import os
 from ctypes import c_float, c_int, c_void_p
 from typing import Any
 
+from ..lazy import Accumulated, GateUpWeight, NormedInput, Partials, ResidualSink  # noqa: F401  (re-exported)
 from .build import load_library
 
 F32, BF16 = 0, 1
@@ -26,74 +27,6 @@ class KernelError(RuntimeError):
 
 def _ptr(tensor: Any) -> int | None:
     return None if tensor is None else tensor.data_ptr()
-
-
-class Partials:
-    """A projection whose last additions are left to the kernel that consumes it.
-
-    ``splits`` > 0: ``data`` holds float32 partial sums [splits, rows, width] of a matrix product
-    that was cut along K.  ``splits`` == 0: ``data`` is the product itself [rows, width] in the
-    compute dtype.  In both cases ``bias`` (or None) is still to be added.  The consumers
-    (residual-add + RMSNorm, rotary + cache write) add everything up in float32, parts in
-    ascending split order."""
-
-    def __init__(self, data: Any, splits: int, rows: int, width: int, bias: Any) -> None:
-        self.data, self.splits, self.rows, self.width, self.bias = data, splits, rows, width, bias
-
-    @property
-    def shape(self) -> tuple[int, int]:
-        return (self.rows, self.width)
-
-
-class ResidualSink:
-    """The float32 residual stream [T, H] as a target: a projection handed this (``Ops.linear(...,
-    residual=sink)``) may add its result into ``tensor`` itself.  ``gain`` is the gain vector of the
-    norm that will read the stream next, when that norm can take its input pre-scaled (else None);
-    whoever arranges the layers sets it before each projection."""
-
-    def __init__(self, tensor: Any) -> None:
-        self.tensor = tensor
-        self.gain: Any = None
-        self.following_gain: Any = None   # for the last projection of the current layer
-
-
-class Accumulated:
-    """A projection that its own kernel has already added into the float32 residual stream.
-
-    ``sq`` holds, for every token row, the sums of squares of the new residual row per block of 32
-    columns ([rows, tiles] float32): a norm that follows needs no pass over the row to know its
-    mean square.  ``scaled`` (or None) is bfloat16(new row * ``gain``) for the norm whose gain
-    vector ``gain`` is.  A consumer that only wants the sum treats this as "nothing left to add"."""
-
-    def __init__(self, residual: Any, sq: Any, tiles: int, scaled: Any = None, gain: Any = None) -> None:
-        self.residual, self.sq, self.tiles, self.scaled, self.gain = residual, sq, tiles, scaled, gain
-
-    @property
-    def shape(self) -> tuple[int, ...]:
-        return tuple(self.residual.shape)
-
-
-class NormedInput:
-    """RMSNorm of the residual rows, not yet divided by the root mean square: ``accumulated.scaled``
-    holds bfloat16(row * gain) and the matrix product that takes this (``Ops.linear``,
-    ``Ops.gate_up``) multiplies its result rows by rstd, which it forms from ``accumulated.sq``.
-    ``materialize()`` runs the ordinary norm kernel and returns a plain tensor for anyone else."""
-
-    def __init__(self, accumulated: Accumulated, eps: float, materialize: Any) -> None:
-        self.accumulated, self.eps, self.materialize = accumulated, eps, materialize
-
-    @property
-    def shape(self) -> tuple[int, ...]:
-        return tuple(self.accumulated.scaled.shape)
-
-
-class GateUpWeight:
-    """Stacked gate and up matrices [2I, H].  ``block`` == I: all gate rows, then all up rows.
-    ``block`` < I: rows interleaved in blocks (``block`` gate rows, the matching ``block`` up
-    rows, ...), which lets one CTA of the streaming kernel finish SiLU(gate) * up by itself."""
-
-    def __init__(self, weight: Any, inter: int, block: int) -> None:
-        self.weight, self.inter, self.block = weight, inter, block
 
 
 # More rows than this go to the tile kernels (tcgen05 or the library).  The streaming kernel
@@ -153,8 +86,9 @@ class Ops:
 
         v, i, f = c_void_p, c_int, c_float
         ew = _Lib(load_library("elementwise.cu"))
-        self._embedding = ew.function("cie_embedding", [v, v, v, i, i, i, i, v, v])
+        self._embedding = ew.function("cie_embedding", [v, v, v, i, i, i, f, i, v, v])
         ll = ctypes.c_longlong
+        self._shape_logits = ew.function("cie_shape_logits", [v, ll, f, f, v])
         self._add_rmsnorm = ew.function("cie_add_rmsnorm", [v, v, i, ll, v, v, v, v, i, i, f, i, v])
         self._rope_kv_write = ew.function(
             "cie_rope_kv_write",
@@ -187,7 +121,7 @@ class Ops:
             st = _Lib(load_library("gemm_stream.cu"))
             self._gemm_stream = st.function("cie_gemm_stream", [v, v, v, v, i, i, i, i, i, i, v, v])
             self._gemm_stream_ex = st.function(
-                "cie_gemm_stream_ex", [v, v, i, f, v, v, v, v, v, v, v, i, i, i, i, i, i, v, v])
+                "cie_gemm_stream_ex", [v, v, i, f, v, v, v, v, v, v, v, i, i, i, i, i, i, i, v, v])
             self._gemm_stream_rope = st.function(
                 "cie_gemm_stream_rope",
                 [v, v, i, f, v, v, v, i, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, i, v, v])
@@ -245,11 +179,23 @@ class Ops:
             raise KernelError("device error word set: " + "; ".join(faults))
 
     # ------------------------------------------------------------------ kernels
-    def embedding(self, token_ids: Any, table: Any, residual: Any) -> None:
+    def embedding(self, token_ids: Any, table: Any, residual: Any, scale: float = 1.0) -> None:
+        """residual[t] = table[token_ids[t]] * scale, float32."""
         tokens, hidden = residual.shape
         self.launches += 1
         self._embedding(_ptr(token_ids), _ptr(table), _ptr(residual), tokens, hidden,
-                        table.shape[0], self._code_of(table), _ptr(self.error_word), self.stream)
+                        table.shape[0], float(scale), self._code_of(table), _ptr(self.error_word), self.stream)
+
+    def shape_logits(self, logits: Any, scale: float = 1.0, softcap: float = 0.0) -> None:
+        """logits = softcap * tanh(logits * scale / softcap) (or logits * scale), float32, in place."""
+        if scale == 1.0 and softcap == 0.0:
+            return
+        self.launches += 1
+        self._shape_logits(_ptr(logits), logits.numel(), float(scale), float(softcap), self.stream)
+
+    def residual_sink(self, residual: Any) -> "ResidualSink":
+        """The float32 stream as a target that projections may add themselves into."""
+        return ResidualSink(residual)
 
     def add_rmsnorm(self, residual: Any, update: Any, gain: Any, eps: float, out: Any,
                     rows: Any = None) -> None:
@@ -305,7 +251,7 @@ class Ops:
 
     def _stream(self, x: Any, weight: Any, bias: Any, out: Any, m: int, n: int, k: int, splits: int,
                 mode: int, residual: Any = None, sq: Any = None, scaled: Any = None,
-                next_gain: Any = None) -> None:
+                next_gain: Any = None, early_trigger: bool = False) -> None:
         """One launch of the streaming kernel; ``x`` is a tensor or a ``NormedInput``."""
         self.launches += 1
         row_sq, tiles, eps = None, 0, 0.0
@@ -313,7 +259,7 @@ class Ops:
             row_sq, tiles, eps, x = x.accumulated.sq, x.accumulated.tiles, x.eps, x.accumulated.scaled
         self._gemm_stream_ex(_ptr(x), _ptr(row_sq), tiles, eps, _ptr(weight), _ptr(bias), _ptr(out),
                              _ptr(residual), _ptr(sq), _ptr(scaled), _ptr(next_gain), m, n, k, splits,
-                             mode, 32, _ptr(self.error_word), self.stream)
+                             mode, 32, 1 if early_trigger else 0, _ptr(self.error_word), self.stream)
 
     def linear(self, x: Any, weight: Any, bias: Any, out: Any, allow_partials: bool = False,
                tag: str = "", defer_bias: bool = False, residual: Any = None) -> Any:
@@ -352,7 +298,7 @@ class Ops:
                                           reserve=STREAM_MAX_ROWS * n // 2)
                     scaled = scaled.view(self.torch.bfloat16)[: m * n].view(m, n)
                 self._stream(x, weight, bias, None, m, n, k, cluster, 4, residual=residual.tensor, sq=sq,
-                             scaled=scaled, next_gain=gain)
+                             scaled=scaled, next_gain=gain, early_trigger=residual.early_trigger)
                 return Accumulated(residual.tensor, sq, tiles, scaled, gain)
             if splits > 1:
                 scratch = self.scratch("partials." + (tag or "linear"), splits * m * n,

@@ -41,8 +41,9 @@ class Attention(Mixer):
         self.head_dim = int(head_dim)
         self.qkv_bias = bool(qkv_bias)
         self.window = int(window)
-        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.position = build_part("position", position) if position is not None else None
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.scale *= float(getattr(self.position, "attention_factor", 1.0))
         self.q_width = self.num_heads * self.head_dim
         self.kv_width = self.num_kv_heads * self.head_dim
         self.qkv_width = self.q_width + 2 * self.kv_width
@@ -83,8 +84,18 @@ class Attention(Mixer):
         self.paired = bool(self.position is not None and getattr(ops, "can_pair_rotary", None)
                            and ops.can_pair_rotary(self.head_dim, rotary))
 
+        # an encoding may want the elements of every q and k head stored in another order (its
+        # pairs side by side for the kernels); scores do not change when q and k move together
+        order = getattr(self.position, "row_order", lambda: None)()
+
+        def reorder(rows, heads):
+            index = (torch.arange(heads).view(-1, 1) * self.head_dim + torch.tensor(order).view(1, -1)).reshape(-1)
+            return rows.index_select(0, index.to(rows.device)).contiguous()
+
         def stacked(suffix):
             q, k, v = (tensors[f"{name}_proj.{suffix}"] for name in "qkv")
+            if order is not None:
+                q, k = reorder(q, self.num_heads), reorder(k, self.num_kv_heads)
             if self.paired:
                 q = ops.pair_rotary_rows(q, self.num_heads, self.head_dim, rotary)
                 k = ops.pair_rotary_rows(k, self.num_kv_heads, self.head_dim, rotary)

@@ -100,6 +100,12 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # A mixer with per-request state sets this to True to say: my forward runs on the device alone
+    # (it reads this step's numbers from the device views of ``ctx``, never from ``ctx.host``) and
+    # leaves the state of requests with ``ctx.request_active == 0`` as it is.  Steps with such a
+    # mixer may then run from captured CUDA graphs, padded decode batches included.
+    state_in_graphs = False
+
     def cache_spec(self) -> CacheSpec | None:
         return None
 
@@ -119,14 +125,23 @@ class FeedForward(Part):
 
 
 class Block:
-    """Arrangement of the parts of one layer around the residual stream."""
+    """Arrangement of the parts of one layer around the residual stream.
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm, **params: Any) -> None:
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    A block is built from the layer's parts by slot name (``parts["mixer"]``, ...; every part is
+    also an attribute of that name) and its own constants.  ``slots`` names what it needs; the
+    model checks a layer's description against it.  ``cache_slot`` names the part whose cache
+    (pages and/or per-request state) the layer's binding belongs to."""
+
+    slots: tuple[str, ...] = ()
+    cache_slot: str = "mixer"
+
+    def __init__(self, parts: "dict[str, Part]", **params: Any) -> None:
+        missing = [name for name in self.slots if name not in parts]
+        if missing:
+            raise ValueError(f"{type(self).__name__} needs the parts {list(self.slots)}; missing {missing}")
+        self.parts = dict(parts)
+        for name, part in parts.items():
+            setattr(self, name, part)
 
     def forward(
         self,
@@ -138,6 +153,12 @@ class Block:
         """Runs the layer.  ``pending`` is an update not yet added to ``residual``; the
         returned tensor is this layer's last update, again pending."""
         raise NotImplementedError
+
+    def entry_gain(self) -> Any:
+        """What the layer BEFORE this one may know about this block's first norm: the gain vector
+        its last projection may multiply the new residual rows with, if this block's first
+        consumer finishes that norm itself; None (the default) if the block wants plain rows."""
+        return None
 
 
 _KINDS = ("norm", "position", "mixer", "feed_forward", "block")

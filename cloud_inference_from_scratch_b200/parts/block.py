@@ -27,8 +27,18 @@ def _lazy_gain(norm, consumer):
 
 
 class PreNormResidual(Block):
+    slots = ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+
+    def entry_gain(self):
+        return _lazy_gain(self.mixer_norm, self.mixer)
+
     def forward(self, residual, pending, ctx, binding):
         sink = getattr(ctx, "residual_sink", None)
+        if sink is not None:
+            # after a projection of this block comes a product of this engine (the feed-forward's, or
+            # the next layer's first) or a norm kernel: before their dependency wait they ask for
+            # weights only, so the projection may let them start early
+            sink.early_trigger = True
         x = _normalise(self.mixer_norm, self.mixer, residual, pending, ctx)
         if sink is not None:   # the mixer's sum is read next by this layer's second norm
             sink.gain = _lazy_gain(self.feed_forward_norm, self.feed_forward)

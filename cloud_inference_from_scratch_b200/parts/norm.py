@@ -8,7 +8,7 @@ the same kernel, and the result is rounded once to the compute dtype.
 
 from __future__ import annotations
 
-from ..native.ops import Accumulated, NormedInput
+from ..lazy import Accumulated, NormedInput
 from .base import Norm, TensorSpec, register_part
 
 

@@ -21,14 +21,14 @@ GATES = {
     "float32": {
         "A": 1.6e-5, "A long": 2e-5, "A runner": 1e-5, "B": 6e-5, "B unsharpened": 8e-6, "B far key": 2.6e-4,
         "B runner": 3e-5, "C": 1e-5, "D": 6e-5, "D runner": 5e-5, "a part alone": 5e-6, "toy models": 5e-5,
-        "toy routed": 7e-6, "3B sizes, 2 layers": 1.7e-4,
+        "toy routed": 7e-6, "toy sandwich": 3e-5, "3B sizes, 2 layers": 1.7e-4,
     },
     # bfloat16: products round their inputs to 8 bits of mantissa; the error grows with the number
     # of terms, layers and decoded tokens, and the largest of a vocabulary's worth of errors is
     # 4 to 5 times their standard deviation
     "bfloat16": {
         "A": 1.3e-1, "A long": 1.3e-1, "A runner": 1.2e-1, "B": 1.5e-1, "B unsharpened": 8e-2, "B runner": 1e-1,
-        "C": 8.5e-2, "D": 1.2e-1, "D runner": 1.1e-1, "a part alone": 8e-2, "toy models": 1.2e-1,
+        "C": 8.5e-2, "D": 1.2e-1, "D runner": 1.1e-1, "a part alone": 8e-2, "toy models": 1.2e-1, "toy sandwich": 1.5e-1,
         "3B sizes, 2 layers": 2.5e-1, "3B sizes, 36 layers": 4.5e-1,
     },
 }

@@ -174,3 +174,32 @@ def test_random_orders_keep_every_invariant(seed):
     cache.assert_invariants()
     assert cache.free_pages(0) == cache.total_pages(0) and cache.free_pages(1) == cache.total_pages(1)
     assert cache.stats()["requests"] == 0
+
+
+def test_page_counts_follow_what_a_group_can_use():
+    """A windowed group never needs more than requests x (window + step tokens) of pages; under a byte
+    budget what it does not need goes to the groups that keep everything."""
+    from cloud_inference_from_scratch_b200.cache.manager import GroupSpec
+    from cloud_inference_from_scratch_b200.cache.pools import plan_page_counts
+
+    full = GroupSpec(name="full", window=0, bytes_per_token=1024)
+    window = GroupSpec(name="window64", window=64, bytes_per_token=2048)
+    # page count given: the windowed group is capped, the full one is not
+    assert plan_page_counts([full, window], 16, max_requests=4, step_tokens=32, num_pages=1000) == [1000, 4 * 7]
+    assert plan_page_counts([full, window], 16, max_requests=4, step_tokens=0, num_pages=1000) == [1000, 1000]
+    assert plan_page_counts([full], 16, 4, 32, num_pages=77) == [77]
+    assert plan_page_counts([], 16, 4, 32, num_pages=5) == [1]
+    # bytes given: equal pages while both grow, then everything to the full group
+    budget = 10 * 16 * (1024 + 2048)
+    assert plan_page_counts([full, window], 16, 4, 32, kv_cache_bytes=budget) == [10, 10]
+    budget = 28 * 16 * 2048 + 500 * 16 * 1024
+    counts = plan_page_counts([full, window], 16, 4, 32, kv_cache_bytes=budget)
+    assert counts == [500, 28]
+    spent = sum(g.bytes_per_token * 16 * n for g, n in zip((full, window), counts))
+    assert spent <= budget < spent + 16 * 1024
+    only_windows = plan_page_counts([window], 16, 4, 32, kv_cache_bytes=1 << 40)
+    assert only_windows == [28]
+    with pytest.raises(ValueError):
+        plan_page_counts([full], 16, 4, 32, kv_cache_bytes=100)
+    with pytest.raises(ValueError):
+        plan_page_counts([full], 16, 4, 32)

@@ -180,3 +180,40 @@ def test_loader_tied_head_may_be_stored_and_duplicates_are_refused(tmp_path):
         SafetensorsSource(folder)
     with pytest.raises(FileNotFoundError):
         SafetensorsSource(tmp_path)
+
+
+def test_layer_spec_is_a_block_kind_and_a_named_map_of_parts():
+    from dataclasses import replace
+
+    from cloud_inference_from_scratch_b200.config import LayerSpec, PartSpec
+
+    norm = PartSpec("rmsnorm", dict(hidden_size=8, eps=1e-5))
+    layer = LayerSpec(prefix="l.", block=PartSpec("prenorm_residual"), mixer=PartSpec("attention"),
+                      feed_forward=PartSpec("swiglu"), mixer_norm=norm, feed_forward_norm=norm)
+    assert layer.mixer.family == "mixer" and layer.mixer_norm.family == "norm" and layer.feed_forward.family == "feed_forward"
+    assert set(layer.parts) == {"mixer", "feed_forward", "mixer_norm", "feed_forward_norm"}
+    # other slots are data too; a slot whose name does not say what it is names its family
+    sandwich = LayerSpec("l.", PartSpec("toy_sandwich"), parts=dict(layer.parts, mixer_post_norm=norm,
+                         second=PartSpec("swiglu", family="feed_forward")))
+    assert sandwich.mixer_post_norm.family == "norm" and sandwich.second.family == "feed_forward"
+    with pytest.raises(ValueError, match="family"):
+        LayerSpec("l.", PartSpec("x"), gadget=PartSpec("swiglu"))
+    with pytest.raises(AttributeError):
+        layer.nothing
+    swapped = replace(layer, mixer=PartSpec("other"))
+    assert swapped.mixer.kind == "other" and swapped.feed_forward == layer.feed_forward and swapped != layer
+
+
+def test_rotary_pairing_is_a_row_order_and_scales_are_constants():
+    from cloud_inference_from_scratch_b200.config import PartSpec
+    from cloud_inference_from_scratch_b200.parts import build_part
+
+    def rope(**extra):
+        return build_part("position", PartSpec("rope_neox", dict(head_dim=8, rotary_dim=6, theta=1e4, max_positions=64, **extra)))
+
+    assert rope().row_order() is None and rope().attention_factor == 1.0
+    assert rope(pairing="interleaved").row_order() == [0, 2, 4, 1, 3, 5, 6, 7]
+    with pytest.raises(ValueError):
+        rope(pairing="sideways")
+    with pytest.raises(ValueError):
+        rope(position_scale=0.0)

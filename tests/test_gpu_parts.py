@@ -145,7 +145,11 @@ def register_toy():
 
     class RunningMean(Mixer):
         """update[t] = W * mean(x[0..t]) over the request's tokens so far; the state is the running
-        sum of x and the token count (float32), one row per request slot."""
+        sum of x and the token count (float32), one row per request slot.  Everything runs on the
+        device from the device views of the step's metadata, and a row that only pads a captured
+        batch (request_active == 0) adds nothing to the state: steps may be captured in CUDA graphs."""
+
+        state_in_graphs = True
 
         def __init__(self, hidden_size):
             self.hidden_size = hidden_size
@@ -161,17 +165,20 @@ def register_toy():
             self.weight = tensors["mix.weight"]
 
         def forward(self, x, ctx, binding):
-            out = torch.empty_like(x)
-            starts = ctx.host.query_start
-            for index, slot in enumerate(ctx.host.slots.tolist()):
-                rows = x[starts[index]:starts[index + 1]].float()
-                state = binding.state[slot]
-                sums = state[:-1] + torch.cumsum(rows, 0)
-                counts = state[-1] + torch.arange(1, rows.shape[0] + 1, device=x.device)
-                mean = (sums / counts[:, None]).to(x.dtype)
-                out[starts[index]:starts[index + 1]] = mean @ self.weight.t()
-                state[:-1] = sums[-1]
-                state[-1] = counts[-1]
+            rows = x.double()
+            tokens = rows.shape[0]
+            before = torch.cat([torch.zeros_like(rows[:1]), torch.cumsum(rows, 0)])   # before[i]: sum of rows < i
+            start, end = ctx.query_start[:-1].long(), ctx.query_start[1:].long()
+            request = ctx.request_of_token.long()
+            slots = ctx.slots.long()
+            prior = binding.state[slots].double()                                      # [requests, hidden + 1]
+            sums = prior[request, :-1] + before[1:] - before[start][request]
+            counts = prior[request, -1] + (torch.arange(tokens, device=x.device) - start[request] + 1)
+            mean = (sums / counts[:, None]).to(x.dtype)
+            out = mean @ self.weight.t()
+            gained = torch.cat([before[end] - before[start], (end - start).double()[:, None]], 1)
+            gained = gained * ctx.request_active.double()[:, None]
+            binding.state.index_add_(0, slots, gained.float())
             return out
 
     register_part("mixer", "toy_running_mean", RunningMean, replace=True)
@@ -243,7 +250,6 @@ def toy_plain_forward(folder, tokens):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
-    from cloud_inference_from_scratch_b200 import generate
     from cloud_inference_from_scratch_b200.engine.core import build_core
     from cloud_inference_from_scratch_b200.weights import write_random_model
 
@@ -262,10 +268,20 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
             ref = toy_plain_forward(folder, tokens).numpy()
             mine = np.stack([got[rid][p] for p in range(len(tokens))])
             assert record("toy models", dtype, relative_error(mine, ref)) <= tolerance(dtype, "toy models"), (rid, relative_error(mine, ref))
-    # through the public entry point; CUDA graphs must stay off because of the per-request state
-    prompts = [requests["t1"], requests["t3"]]
-    results = generate(folder, prompts, max_output_tokens=5, dtype=dtype, block_size=8, kv_cache_blocks=40,
-                       prefill_chunk_size=7, max_batched_tokens=16)
+    # through the public entry point.  The mixer has declared that padded rows leave its state alone
+    # (state_in_graphs), so decode steps run from captured graphs: three requests make a batch of
+    # four with one padded row, and they end at different steps.
+    from cloud_inference_from_scratch_b200 import GenerationConfig, InferenceEngine, build_config
+
+    prompts = [requests["t1"], requests["t3"], requests["t0"][:9]]
+    config = build_config("ragged", dtype=dtype, block_size=8, kv_cache_blocks=40, prefill_chunk_size=7,
+                          max_batched_tokens=16, max_model_len=128, max_active_sequences=4)
+    with InferenceEngine(config, folder) as engine:
+        assert engine.runner.use_graphs
+        handles = [engine.submit(p, GenerationConfig(max_output_tokens=5 + 2 * i)) for i, p in enumerate(prompts)]
+        results = [h.wait() for h in handles]
+        # captured and padded, but never launched ahead of the host: a dropped step would have moved the state
+        assert engine.runner.cuda_graph_replays > 0 and engine.runner.steps_launched_ahead == 0
     for prompt, result in zip(prompts, results):
         tokens = list(prompt)
         for produced in result.token_ids:
@@ -507,3 +523,127 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
             mine = np.stack([got[rid][p] for p in range(len(tokens))])
             assert record("toy routed", "float32", relative_error(mine, ref.numpy())) <= tolerance("float32", "toy routed"), (rid, relative_error(mine, ref.numpy()))
     assert used == {0, 1}      # both experts took tokens
+
+
+# ------------------------------------------------------------------ another block, another pairing, scaled ends
+def register_toy_sandwich():
+    """A fourth toy architecture, registered from here alone: rotary pairs side by side (interleaved),
+    positions divided by a factor and a factor on the softmax scale, a partial rotary size; a block
+    with a norm on the mixer's output (its parts are data of the layer: one slot more); embeddings
+    times a constant; logits times a constant and softly capped."""
+    from cloud_inference_from_scratch_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture
+    from cloud_inference_from_scratch_b200.parts import register_part
+    from cloud_inference_from_scratch_b200.parts.base import Block
+
+    class Sandwich(Block):
+        """h += post_norm(mixer(norm(h))); h += feed_forward(norm(h))"""
+
+        slots = ("mixer", "feed_forward", "mixer_norm", "mixer_post_norm", "feed_forward_norm")
+
+        def forward(self, residual, pending, ctx, binding):
+            rt = self.mixer.runtime
+            x = self.mixer_norm.forward(residual, pending, ctx)
+            # the mixer's output is not for the stream yet: no projection may add itself into it
+            sink, ctx.residual_sink = ctx.residual_sink, None
+            mixed = self.mixer.forward(x, ctx, binding)
+            ctx.residual_sink = sink
+            mixed = rt.ops.resolve(mixed, torch.empty(residual.shape, dtype=torch.float32, device=residual.device))
+            tamed = self.mixer_post_norm.forward(mixed.float().clone(), None, ctx)
+            x = self.feed_forward_norm.forward(residual, tamed, ctx)
+            return self.feed_forward.forward(x, ctx)
+
+    register_part("block", "toy_sandwich", Sandwich, replace=True)
+
+    @dataclass(frozen=True)
+    class SandwichConfig:
+        hidden_size: int
+        intermediate_size: int
+        vocab_size: int
+        heads: int
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["hidden_size"], raw["intermediate_size"], raw["vocab_size"], raw["heads"])
+
+        def to_dict(self):
+            return dict(architectures=["ToySandwichForCausalLM"], model_type="toy_sandwich", hidden_size=self.hidden_size,
+                        intermediate_size=self.intermediate_size, vocab_size=self.vocab_size, heads=self.heads)
+
+    def spec(config):
+        head_dim = config.hidden_size // config.heads
+        norm = dict(hidden_size=config.hidden_size, eps=1e-5)
+        position = PartSpec("rope_neox", dict(head_dim=head_dim, rotary_dim=head_dim // 2, theta=1e4, max_positions=512,
+                                              pairing="interleaved", position_scale=2.0, attention_factor=1.3))
+        attention = PartSpec("attention", dict(hidden_size=config.hidden_size, num_heads=config.heads, num_kv_heads=config.heads,
+                                               head_dim=head_dim, qkv_bias=True, position=position), prefix="self_attn.")
+        dense = PartSpec("swiglu", dict(hidden_size=config.hidden_size, intermediate_size=config.intermediate_size), prefix="mlp.")
+        layers = tuple(
+            LayerSpec(prefix=f"model.layers.{index}.", block=PartSpec("toy_sandwich"), parts=dict(
+                mixer=attention, feed_forward=dense,
+                mixer_norm=PartSpec("rmsnorm", norm, prefix="input_layernorm."),
+                mixer_post_norm=PartSpec("rmsnorm", norm, prefix="post_mixer_layernorm."),
+                feed_forward_norm=PartSpec("rmsnorm", norm, prefix="post_attention_layernorm.")))
+            for index in range(2))
+        return ModelSpec(
+            architecture="ToySandwichForCausalLM", vocab_size=config.vocab_size, hidden_size=config.hidden_size,
+            embedding_tensor="model.embed_tokens.weight", layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)),
+            final_norm=PartSpec("rmsnorm", norm), final_norm_prefix="model.norm.", head_tensor="model.embed_tokens.weight",
+            max_positions=512, embedding_scale=float(config.hidden_size) ** 0.5, logit_scale=0.5, logit_softcap=2.0,
+        )
+
+    register_architecture("ToySandwichForCausalLM", "toy_sandwich", SandwichConfig.from_dict, spec, replace=True)
+    return SandwichConfig(hidden_size=128, intermediate_size=176, vocab_size=411, heads=2)
+
+
+def toy_sandwich_plain_forward(folder, tokens):
+    _, w = plain_model.read_model_folder(folder)
+    eps, heads, hidden = 1e-5, 2, 128
+    dim, rot = hidden // heads, hidden // heads // 2
+    count = len(tokens)
+    positions = torch.arange(count, dtype=torch.float32) / 2.0
+    inv_freq = 1.0 / (1e4 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    angles = positions[:, None] * inv_freq[None, :]
+    cos, sin = torch.cos(angles)[:, None, :], torch.sin(angles)[:, None, :]
+
+    def rotate_pairs(x):      # x: [T, heads, dim]; pairs (2j, 2j + 1) of the first `rot` elements
+        even, odd = x[..., 0:rot:2], x[..., 1:rot:2]
+        out = x.clone()
+        out[..., 0:rot:2] = even * cos - odd * sin
+        out[..., 1:rot:2] = odd * cos + even * sin
+        return out
+
+    h = plain_model.embedding(w["model.embed_tokens.weight"], tokens) * hidden ** 0.5
+    for index in range(2):
+        prefix = f"model.layers.{index}."
+        x = plain_model.rms_norm(h, w[prefix + "input_layernorm.weight"], eps)
+        q, k, v = (plain_model.linear(x, w[prefix + f"self_attn.{n}_proj.weight"], w[prefix + f"self_attn.{n}_proj.bias"])
+                   .view(count, heads, dim) for n in "qkv")
+        mixed = plain_model.attention(rotate_pairs(q), rotate_pairs(k), v, 1.3 / math.sqrt(dim))
+        mixed = plain_model.linear(mixed.reshape(count, hidden), w[prefix + "self_attn.o_proj.weight"])
+        h = h + plain_model.rms_norm(mixed, w[prefix + "post_mixer_layernorm.weight"], eps)
+        x = plain_model.rms_norm(h, w[prefix + "post_attention_layernorm.weight"], eps)
+        h = h + plain_model.swiglu(x, w[prefix + "mlp.gate_proj.weight"], w[prefix + "mlp.up_proj.weight"],
+                                   w[prefix + "mlp.down_proj.weight"])
+    logits = plain_model.rms_norm(h, w["model.norm.weight"], eps) @ w["model.embed_tokens.weight"].t()
+    return 2.0 * torch.tanh(logits * 0.5 / 2.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_block_with_a_post_norm_interleaved_rotary_and_scaled_ends(dtype, tmp_path):
+    from cloud_inference_from_scratch_b200.engine.core import build_core
+    from cloud_inference_from_scratch_b200.weights import write_random_model
+
+    config = register_toy_sandwich()
+    folder = write_random_model(tmp_path / "plain", config.to_dict(), 6)
+    folder = sharpen(folder, tmp_path / "sharp", score_std=3.0 if dtype == "float32" else 1.5)
+    core = build_core(folder, dtype=dtype, page_size=16, num_pages=24, max_requests=4, max_model_len=256)
+    assert core.architecture == "ToySandwichForCausalLM"
+    assert set(core.model.layers[0].parts) == {"mixer", "feed_forward", "mixer_norm", "mixer_post_norm", "feed_forward_norm"}
+    assert "model.layers.1.post_mixer_layernorm.weight" in core.model.tensor_table()
+    requests = {f"s{i}": random_tokens(411, n, 60 + i) for i, n in enumerate((45, 7, 80, 22))}
+    for steps in (trace_whole(requests), trace_portions(requests), trace_mixed(requests, seed=9)):
+        got = replay(core, steps)
+        for rid, tokens in requests.items():
+            ref = toy_sandwich_plain_forward(folder, tokens).numpy()
+            mine = np.stack([got[rid][p] for p in range(len(tokens))])
+            assert record("toy sandwich", dtype, relative_error(mine, ref)) <= tolerance(dtype, "toy sandwich"), (rid, relative_error(mine, ref))
