@@ -817,9 +817,13 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
 // a CTA is 4 warps and a ring of SPLIT_STAGES stages of 64 keys (K and V of a stage arrive by
 // one mbarrier; 16 KB of keys and 16 KB of values at head size 128), so two or three CTAs fit an
 // SM and every SM has work at small batches.  Warp w multiplies the w-th 16 keys of a stage.  A
-// CTA leaves its share (unnormalised output, maximum, sum of 16 head rows) in global memory and
-// draws a ticket; whoever draws the last ticket of a (request, kv head, 16 heads) unit adds the
-// shares up and writes the output.  Nobody waits for anybody.
+// The CTAs of a unit (request, kv head, 16 heads) that lie in one thread-block cluster divide the
+// head rows among themselves and send each other their shares of them (unnormalised output,
+// maximum, sum) with asynchronous stores into the owner's shared memory that complete on a barrier
+// there; every CTA adds up the rows it owns and writes them out.  A unit that spans several
+// clusters (or a launch without clusters) leaves the shares in global memory instead and draws a
+// ticket: whoever draws the last ticket of the unit adds the shares up.  Nobody waits for a CTA that
+// may not be running.
 //
 // Before `griddepcontrol.wait` a CTA already asks for the stages that do not hold the newest key:
 // block tables and context lengths come with the step's metadata and older keys and values are
@@ -834,10 +838,48 @@ constexpr int SPLIT_SHARE_ROW = D + 4;                // floats of a share's row
 constexpr int SPLIT_SHARE = 16 * SPLIT_SHARE_ROW;     // floats of a CTA's share
 constexpr int SPLIT_PAGE_SLOTS = 512;                 // the first block-table entries of a request, kept in shared memory
 constexpr size_t SPLIT_STAGE_BYTES = (size_t)SPLIT_STAGE * sizeof(bf16);
-constexpr size_t SPLIT_MERGE_BYTES = (size_t)SPLIT_WARPS * 16 * D * sizeof(float);
+constexpr size_t SPLIT_MERGE_BYTES = ((size_t)SPLIT_WARPS * 16 * D + 16 * (D + 4)) * sizeof(float);   // the warps' blocks, then the CTA's own rows
 constexpr int SPLIT_MIN_STAGES = (int)((SPLIT_MERGE_BYTES + SPLIT_STAGE_BYTES - 1) / SPLIT_STAGE_BYTES);   // the merge buffers reuse the ring
 static_assert(SPLIT_MAX_STAGES * SPLIT_WARPS <= 32, "one lane of the first warp per 16-key block in flight");
-constexpr size_t split_smem(int stages) { return 1024 + DECODE_Q_BYTES + (size_t)stages * SPLIT_STAGE_BYTES; }
+// A CTA that shares a unit of `rows` head rows with p - 1 others in its cluster owns at most
+// ceil(rows / p) of them and receives p - 1 shares of each; p is anything up to the cluster size
+// (the last cluster of a unit may be partly used).
+constexpr int split_inbox_rows(int rows, int cluster) {
+  int most = 0;
+  for (int p = 2; p <= cluster; ++p) {
+    const int need = (p - 1) * ((rows + p - 1) / p);
+    if (need > most) most = need;
+  }
+  return most;
+}
+// dynamic shared memory: alignment slack, the queries, the ring, and (with clusters) the inbox
+constexpr size_t split_smem(int stages, int cluster, int rows) {
+  return 1024 + DECODE_Q_BYTES + (size_t)stages * SPLIT_STAGE_BYTES +
+         (size_t)split_inbox_rows(rows, cluster) * SPLIT_SHARE_ROW * sizeof(float);
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the shared::cluster address, in CTA `rank` of the cluster, of what lies at `p` in this CTA
+__device__ __forceinline__ uint32_t map_to_rank(const void* p, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// asynchronous stores into another CTA's shared memory; the bytes count on the barrier `bar` there
+__device__ __forceinline__ void push_f4(uint32_t remote, float4 v, uint32_t bar) {
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(remote), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void push_f2(uint32_t remote, float a, float b, uint32_t bar) {
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];"
+               ::"r"(remote), "f"(a), "f"(b), "r"(bar) : "memory");
+}
 
 struct SplitArgs {
   const bf16* q;            // row b of q_stride elements: the request's single query token
@@ -852,7 +894,8 @@ struct SplitArgs {
   int splits;               // CTAs launched per unit (1 .. SPLIT_MAX)
   int min_keys;             // a request uses only as many of them as leave every CTA this many keys
   int stages;               // stages of the ring (SPLIT_MIN_STAGES .. SPLIT_MAX_STAGES)
-  float* shares;            // [unit][split][16][D + 4]
+  int cluster;              // CTAs of a thread-block cluster along the splits (1: no clusters)
+  float* shares;            // [unit][split / cluster][16][D + 4]
   int* tickets;             // [unit]; zero between launches
   float scale_log2;
   int window;
@@ -917,6 +960,7 @@ __device__ __forceinline__ void split_mark(int point) {
 #define SPLIT_MARK(point)
 #endif
 
+template <bool kCluster>
 __global__ void __launch_bounds__(SPLIT_WARPS * 32)
 decode_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     const SplitArgs a) {
@@ -929,7 +973,18 @@ decode_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   __shared__ int pages_s[SPLIT_PAGE_SLOTS];
   __shared__ float warp_max_s[SPLIT_WARPS][16], warp_sum_s[SPLIT_WARPS][16];
   __shared__ int last_s;
+  __shared__ __align__(8) uint64_t inbox_bar;   // cluster variant: counts the bytes of the peers' shares
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if constexpr (kCluster) {
+    // every CTA of the cluster sets its inbox up and says so, whether it has keys or not; a CTA
+    // that hands its share over first makes sure that everybody has said so
+    if (tid == 0) {
+      mbar_init(&inbox_bar, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    cluster_arrive();
+  }
   SPLIT_MARK(0);
   // the split is the slowest index of the grid: the CTAs a short request does not use come last
   const int split = blockIdx.z;
@@ -949,6 +1004,21 @@ decode_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   // the tables can hold, the request may be far shorter; the others leave at once
   const int used = max(1, min(a.splits, (length - first) / a.min_keys));
   if (split >= used) return;
+  // the CTAs of this unit that lie in this CTA's cluster, and the clusters the unit uses
+  const int rank = kCluster ? (int)cluster_rank() : 0;
+  const int cluster_index = split / a.cluster;
+  const int peers = min(a.cluster, used - cluster_index * a.cluster);   // working CTAs of this cluster
+  const int clusters_used = (used + a.cluster - 1) / a.cluster;
+  const int live_rows = min(16, a.group - h0);
+  // head row r of the unit is finished by the CTA of rank r % peers; this CTA owns rows rank,
+  // rank + peers, ... and keeps them at local index r / peers
+  const int rows_owned = rank < live_rows ? (live_rows - rank + peers - 1) / peers : 0;
+  const int rows_per_owner = (live_rows + peers - 1) / peers;
+  float* inbox = reinterpret_cast<float*>(smem_raw + DECODE_Q_BYTES + (size_t)a.stages * SPLIT_STAGE_BYTES);
+  if constexpr (kCluster) {
+    if (peers > 1 && rows_owned > 0 && tid == 0)
+      mbar_expect_tx(&inbox_bar, (uint32_t)((peers - 1) * rows_owned * (D + 2) * sizeof(float)));
+  }
   const int per_split = (blocks + used - 1) / used;        // in blocks
   const int begin = (first_block + split * per_split) * DN;
   const int end = min(length, begin + per_split * DN);
@@ -1127,10 +1197,16 @@ decode_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
   }
   __syncthreads();
   const int unit = request * gridDim.x + blockIdx.x;
-  float* unit_shares = a.shares + (size_t)unit * a.splits * SPLIT_SHARE;
-  float* share = unit_shares + (size_t)split * SPLIT_SHARE;
-  const int live_rows = min(16, a.group - h0);
+  const int shares_per_unit = a.splits / a.cluster;
+  float* unit_shares = a.shares + (size_t)unit * shares_per_unit * SPLIT_SHARE;
+  float* cluster_share = unit_shares + (size_t)cluster_index * SPLIT_SHARE;
   bf16* out_rows = a.out + (size_t)request * a.out_stride + (size_t)(kvh * a.group + h0) * D;
+  const bool exchange = kCluster && peers > 1;
+  // the rows this CTA owns, from itself: [rows_per_owner][SPLIT_SHARE_ROW] behind the warps' blocks
+  float* own_s = merge_s + SPLIT_WARPS * 16 * D;
+  if (exchange) cluster_wait();   // every CTA of the cluster has set its inbox up (they said so when they started)
+
+  // this CTA's share: every thread takes four columns of one head row and adds the warps up
   for (int idx = tid; idx < live_rows * (D / 4); idx += SPLIT_WARPS * 32) {
     const int r = idx / (D / 4), c4 = idx % (D / 4);
     float4 acc = *reinterpret_cast<const float4*>(merge_s + r * D + c4 * 4);
@@ -1148,30 +1224,90 @@ decode_split_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
       const float mw = warp_max_s[w][r];
       sum += warp_sum_s[w][r] * ((mw == -INFINITY) ? 0.f : exp2f(mw - m_all));
     }
-    if (used == 1) {   // the request is this CTA's alone: no share, the output itself
+    if (exchange) {
+      const int owner = r % peers, local = r / peers;
+      if (owner == rank) {
+        float* mine = own_s + local * SPLIT_SHARE_ROW;
+        *reinterpret_cast<float4*>(mine + c4 * 4) = acc;
+        if (c4 == 0) { mine[D] = m_all; mine[D + 1] = sum; }
+      } else {
+        // the owner keeps the shares of its peers in the order of their ranks, itself left out
+        const int slot = rank < owner ? rank : rank - 1;
+        const float* theirs = inbox + (size_t)(slot * rows_per_owner + local) * SPLIT_SHARE_ROW;
+        const uint32_t bar = map_to_rank(&inbox_bar, owner);
+        push_f4(map_to_rank(theirs + c4 * 4, owner), acc, bar);
+        if (c4 == 0) push_f2(map_to_rank(theirs + D, owner), m_all, sum, bar);
+      }
+    } else if (clusters_used == 1) {   // the request is this CTA's alone: the output itself
       const float inv = sum > 0.f ? 1.f / sum : 0.f;
       uint2 packed;
       packed.x = pack_bf16(acc.x * inv, acc.y * inv);
       packed.y = pack_bf16(acc.z * inv, acc.w * inv);
       *reinterpret_cast<uint2*>(out_rows + (size_t)r * D + c4 * 4) = packed;
     } else {
-      __stcg(reinterpret_cast<float4*>(share + r * SPLIT_SHARE_ROW + c4 * 4), acc);
+      __stcg(reinterpret_cast<float4*>(cluster_share + r * SPLIT_SHARE_ROW + c4 * 4), acc);
       if (c4 == 0) {
-        __stcg(share + r * SPLIT_SHARE_ROW + D, m_all);
-        __stcg(share + r * SPLIT_SHARE_ROW + D + 1, sum);
+        __stcg(cluster_share + r * SPLIT_SHARE_ROW + D, m_all);
+        __stcg(cluster_share + r * SPLIT_SHARE_ROW + D + 1, sum);
       }
     }
   }
-  if (used == 1) return;
+  if (!exchange && clusters_used == 1) return;
+  if (exchange) {
+    if (rows_owned == 0) return;          // more CTAs than head rows: nothing to finish here
+    __syncthreads();                      // this CTA's own rows are in own_s
+    if (!mbar_wait(&inbox_bar, 0, a.err)) return;   // and its peers' shares of them in the inbox
+    // the rows this CTA owns: its own share and its peers', in the order of their ranks
+    for (int idx = tid; idx < rows_owned * (D / 4); idx += SPLIT_WARPS * 32) {
+      const int local = idx / (D / 4), c4 = idx % (D / 4);
+      const int r = local * peers + rank;
+      float m_all = -INFINITY, sum = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int peer = 0; peer < peers; ++peer) {
+        const float* share = peer == rank ? own_s + local * SPLIT_SHARE_ROW
+                                          : inbox + (size_t)((peer < rank ? peer : peer - 1) * rows_per_owner + local) * SPLIT_SHARE_ROW;
+        const float m_theirs = share[D], sum_theirs = share[D + 1];
+        const float4 part = *reinterpret_cast<const float4*>(share + c4 * 4);
+        const float m_new = fmaxf(m_all, m_theirs);
+        const float keep = (m_all == -INFINITY) ? 0.f : exp2f(m_all - m_new);
+        const float take = (m_theirs == -INFINITY) ? 0.f : exp2f(m_theirs - m_new);
+        sum = sum * keep + sum_theirs * take;
+        acc.x = acc.x * keep + part.x * take; acc.y = acc.y * keep + part.y * take;
+        acc.z = acc.z * keep + part.z * take; acc.w = acc.w * keep + part.w * take;
+        m_all = m_new;
+      }
+      if (clusters_used == 1) {
+        const float inv = sum > 0.f ? 1.f / sum : 0.f;
+        uint2 packed;
+        packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+        packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out_rows + (size_t)r * D + c4 * 4) = packed;
+      } else {
+        __stcg(reinterpret_cast<float4*>(cluster_share + r * SPLIT_SHARE_ROW + c4 * 4), acc);
+        if (c4 == 0) {
+          __stcg(cluster_share + r * SPLIT_SHARE_ROW + D, m_all);
+          __stcg(cluster_share + r * SPLIT_SHARE_ROW + D + 1, sum);
+        }
+      }
+    }
+    if (clusters_used == 1) return;
+  }
+  // ---- several clusters share the unit: every CTA that wrote rows of its cluster's share draws a
+  // ticket; whoever draws the last one adds the clusters' shares up
+  int writers = 0;
+  for (int c = 0; c < clusters_used; ++c) {
+    const int in_cluster = min(a.cluster, used - c * a.cluster);
+    writers += kCluster && in_cluster > 1 ? min(in_cluster, live_rows) : 1;
+  }
   SPLIT_MARK(5);
   __threadfence();   // this thread's part of the share is visible before the ticket is drawn
   __syncthreads();
-  if (tid == 0) last_s = atomicAdd(&a.tickets[unit], 1) == used - 1;
+  if (tid == 0) last_s = atomicAdd(&a.tickets[unit], 1) == writers - 1;
   __syncthreads();
   SPLIT_MARK(6);
   if (!last_s) return;
   __threadfence();
-  merge_shares(unit_shares, used, out_rows, live_rows, tid);
+  merge_shares(unit_shares, clusters_used, out_rows, live_rows, tid);
   if (tid == 0) a.tickets[unit] = 0;   // ready for the next launch
   SPLIT_MARK(7);
 }
@@ -1322,24 +1458,28 @@ extern "C" int cie_attention_decode(const void* q, int q_stride, void* out, int 
   return launch_decode<false>(k_map, v_map, a, requests, (cudaStream_t)stream);
 }
 
-// How many CTAs of the split decode kernel with a ring of `stages` stages fit one SM (its shared
-// memory decides); 0 if the head size is not its kind or the ring is out of range, -1 on failure.
-extern "C" int cie_attention_decode_split_ctas_per_sm(int stages) {
-  if (D % 64 || stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES) return 0;
-  const size_t smem = split_smem(stages);
-  if (cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)split_smem(SPLIT_MAX_STAGES)) != cudaSuccess) {
+// How many CTAs of the split decode kernel with a ring of `stages` stages, clusters of `cluster`
+// CTAs and `rows` head rows a unit fit one SM (its shared memory decides); 0 if the head size is not its kind or the sizes are
+// out of range, -1 on failure.
+template <bool kCluster>
+static int split_ctas_per_sm(int stages, int cluster, int rows) {
+  const size_t smem = split_smem(stages, cluster, rows);
+  if (cudaFuncSetAttribute(decode_split_kernel<kCluster>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     cudaGetLastError();
-    if (cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-      cudaGetLastError();
-      return 0;
-    }
+    return 0;
   }
   int ctas = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, decode_split_kernel, SPLIT_WARPS * 32, smem) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, decode_split_kernel<kCluster>, SPLIT_WARPS * 32, smem) != cudaSuccess) {
     cudaGetLastError();
     return -1;
   }
   return ctas;
+}
+
+// rows: head rows of a unit (query heads per kv head, at most 16)
+extern "C" int cie_attention_decode_split_ctas_per_sm(int stages, int cluster, int rows) {
+  if (D % 64 || stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES || cluster < 1 || cluster > 8 || rows < 1 || rows > 16) return 0;
+  return cluster > 1 ? split_ctas_per_sm<true>(stages, cluster, rows) : split_ctas_per_sm<false>(stages, 1, rows);
 }
 
 extern "C" int cie_attention_decode_split_max() { return SPLIT_MAX; }
@@ -1353,6 +1493,8 @@ extern "C" int cie_attention_decode_split_trace(void* buffer) {
 
 // The split decode kernel.  splits: CTAs launched per (request, kv head, 16 heads) unit, 1 ..
 // cie_attention_decode_split_max(); a request uses as many of them as leave each `min_keys` keys.
+// cluster: 1, 2, 4 or 8 neighbouring splits of a unit form a thread-block cluster and hand their
+// shares to its first CTA through shared memory (splits must be a multiple of it).
 // shares: float32 [requests * kv_heads * ceil(group / 16)][splits][16][head size + 4]; tickets: one
 // int per unit, zero before the first launch (the kernel leaves them zero).  Needs pages of a power
 // of two >= 16 tokens, a head size that is a multiple of 64 and 16-byte-aligned pools (the caller
@@ -1361,8 +1503,8 @@ extern "C" int cie_attention_decode_split(const void* q, int q_stride, void* out
                                           const void* k_pool, const void* v_pool, const int* table,
                                           int table_width, int num_pages, const int* context_lens,
                                           int requests, int q_heads, int kv_heads, int page_size,
-                                          int splits, int min_keys, int stages, float* shares, int* tickets,
-                                          float scale, int window, int* err, void* stream) {
+                                          int splits, int min_keys, int stages, int cluster, float* shares,
+                                          int* tickets, float scale, int window, int* err, void* stream) {
   if (requests <= 0) return 0;
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_decode_split: %d query heads over %d kv heads", q_heads, kv_heads);
   if (splits < 1 || splits > SPLIT_MAX) CIE_FAIL("attention_decode_split: 1 to %d CTAs per request, got %d", SPLIT_MAX, splits);
@@ -1370,7 +1512,10 @@ extern "C" int cie_attention_decode_split(const void* q, int q_stride, void* out
   if (min_keys < 1) CIE_FAIL("attention_decode_split: min_keys must be positive");
   if (stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES)
     CIE_FAIL("attention_decode_split: %d to %d stages, got %d", SPLIT_MIN_STAGES, SPLIT_MAX_STAGES, stages);
-  if (splits > 1 && (!shares || !tickets)) CIE_FAIL("attention_decode_split: several CTAs per request need scratch memory");
+  if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8)
+    CIE_FAIL("attention_decode_split: clusters of 1, 2, 4 or 8 CTAs, got %d", cluster);
+  if (splits % cluster) CIE_FAIL("attention_decode_split: %d CTAs per request are no multiple of the cluster size %d", splits, cluster);
+  if (splits > cluster && (!shares || !tickets)) CIE_FAIL("attention_decode_split: several clusters per request need scratch memory");
   int page_shift = -1;
   for (int shift = 0; shift < 31; ++shift)
     if ((1 << shift) == page_size) page_shift = shift;
@@ -1382,7 +1527,8 @@ extern "C" int cie_attention_decode_split(const void* q, int q_stride, void* out
   a.q = (const bf16*)q; a.q_stride = q_stride; a.out = (bf16*)out; a.out_stride = out_stride;
   a.pools = Pools{(const bf16*)k_pool, (const bf16*)v_pool, table, table_width, num_pages, kv_heads, page_size};
   a.context_lens = context_lens; a.group = q_heads / kv_heads; a.head_chunks = (a.group + 15) / 16;
-  a.page_shift = page_shift; a.splits = splits; a.min_keys = min_keys; a.stages = stages; a.shares = shares; a.tickets = tickets;
+  a.page_shift = page_shift; a.splits = splits; a.min_keys = min_keys; a.stages = stages; a.cluster = cluster;
+  a.shares = shares; a.tickets = tickets;
   a.scale_log2 = scale * kLog2e; a.window = window; a.err = err;
   CUtensorMap k_map = {}, v_map = {};
   const long long rows = (long long)num_pages * kv_heads * page_size;
@@ -1390,15 +1536,40 @@ extern "C" int cie_attention_decode_split(const void* q, int q_stride, void* out
       ? bw::tensor_map_bf16_row_blocks(k_pool, rows, D, 16, &k_map) && bw::tensor_map_bf16_row_blocks(v_pool, rows, D, 16, &v_map)
       : bw::tensor_map_bf16(k_pool, rows, D, 16, &k_map) && bw::tensor_map_bf16(v_pool, rows, D, 16, &v_map);
   if (!mapped) CIE_FAIL("attention_decode_split: cuTensorMapEncodeTiled failed");
-  const size_t smem = split_smem(stages);
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t status = cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const size_t smem = split_smem(stages, cluster, a.group < 16 ? a.group : 16);
+  static size_t configured[2] = {0, 0};
+  const int variant = cluster > 1 ? 1 : 0;
+  if (smem > configured[variant]) {
+    cudaError_t status = variant
+        ? cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : cudaFuncSetAttribute(decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (status != cudaSuccess) CIE_FAIL("attention_decode_split: shared memory %zu: %s", smem, cudaGetErrorString(status));
-    configured = smem;
+    configured[variant] = smem;
   }
   if (requests > 65535) CIE_FAIL("attention_decode_split: at most 65535 requests a launch, got %d", requests);
-  dim3 grid(kv_heads * a.head_chunks, requests, splits);
-  CIE_LAUNCH("attention_decode_split", decode_split_kernel, grid, dim3(SPLIT_WARPS * 32), smem, (cudaStream_t)stream, k_map, v_map, a);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(kv_heads * a.head_chunks, requests, splits);
+  config.blockDim = dim3(SPLIT_WARPS * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  if (cluster > 1) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = 1;
+    attributes[count].val.clusterDim.y = 1;
+    attributes[count].val.clusterDim.z = cluster;
+    ++count;
+  }
+  if (pdl_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  cudaError_t status = cluster > 1 ? cudaLaunchKernelEx(&config, decode_split_kernel<true>, k_map, v_map, a)
+                                   : cudaLaunchKernelEx(&config, decode_split_kernel<false>, k_map, v_map, a);
+  if (status != cudaSuccess) CIE_FAIL("attention_decode_split: launch failed: %s", cudaGetErrorString(status));
   return 0;
 }

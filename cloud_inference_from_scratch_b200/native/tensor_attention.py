@@ -26,7 +26,7 @@ MIN_KEYS_PER_SPLIT = 128
 # the split decode kernel: a CTA keeps at least this many keys (four stages of 64), so that its
 # set-up and the hand-over of its share stay small beside the keys it streams
 MIN_KEYS_PER_SPLIT_CTA = int(os.environ.get("CIE_DECODE_SPLIT_KEYS", "256"))
-# "CTAs per unit,stages" to launch the split decode kernel with whatever the sizes (for measurements)
+# "CTAs per unit,stages[,cluster]" to launch the split decode kernel with whatever the sizes (for measurements)
 FORCE_SPLIT_PLAN = tuple(int(n) for n in os.environ["CIE_DECODE_SPLIT_PLAN"].split(",")) if os.environ.get("CIE_DECODE_SPLIT_PLAN") else None
 # several clusters per request only while each CTA keeps this many keys: handing the shares over
 # through global memory costs about as much as streaming a thousand keys
@@ -95,17 +95,17 @@ class TensorAttention:
         if head_dim % 64 == 0 and os.environ.get("CIE_DECODE_SPLIT", "1") != "0":
             self._decode_split = lib.function(
                 "cie_attention_decode_split",
-                [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, i, i, v, v, f, i, v, v],
+                [v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, i, i, i, v, v, f, i, v, v],
             )
             self.split_max = int(lib.handle.cie_attention_decode_split_max())
             self.split_tile = int(lib.handle.cie_attention_decode_split_tile())
             per_sm = lib.handle.cie_attention_decode_split_ctas_per_sm
-            per_sm.argtypes = [i]
+            per_sm.argtypes = [i, i, i]
             per_sm.restype = c_int
-            # ring depths the kernel can be launched with, and how many CTAs an SM then holds
-            self.split_rings = {stages: int(per_sm(stages)) for stages in range(1, 9)}
-            self.split_rings = {stages: ctas for stages, ctas in self.split_rings.items() if ctas >= 1}
-            if not self.split_rings:
+            self._split_per_sm = per_sm
+            self.split_cluster_max = int(os.environ.get("CIE_DECODE_SPLIT_CLUSTER", "8"))
+            self._split_rings: dict[tuple[int, int], dict[int, int]] = {}
+            if not self.split_rings(1, 1):
                 raise RuntimeError(f"the split decode kernel does not fit this device at head size {head_dim}")
             self.split_cta_limit = 4 * self.sm_count
             self._split_shares = ops.torch.zeros(self.split_cta_limit * 16 * (head_dim + 4), dtype=ops.torch.float32,
@@ -136,6 +136,24 @@ class TensorAttention:
             room = CLUSTERED_CTAS if clusters < 2 else min(SM_COUNT, (clusters - 1) * splits)
             self._cluster_room[splits] = room
         return room
+
+    def split_rings(self, cluster: int, rows: int) -> dict[int, int]:
+        """Ring depths the split decode kernel can be launched with for clusters of ``cluster`` CTAs
+        and ``rows`` head rows a unit, and how many CTAs an SM then holds (a CTA of a cluster keeps
+        room for its peers' shares of the rows it owns); asked of the device once."""
+        key = (cluster, min(16, rows))
+        if key not in self._split_rings:
+            rings = {stages: int(self._split_per_sm(stages, key[0], key[1])) for stages in range(1, 9)}
+            self._split_rings[key] = {stages: ctas for stages, ctas in rings.items() if ctas >= 1}
+        return self._split_rings[key]
+
+    def cluster_for(self, ctas: int) -> int:
+        """CTAs of a unit that form one thread-block cluster: the largest of 8, 4, 2 that the unit's
+        CTAs fill at least once (and the device has a ring for), else no cluster."""
+        for cluster in (8, 4, 2):
+            if cluster <= min(ctas, self.split_cluster_max):
+                return cluster
+        return 1
 
     @staticmethod
     def split_plan(units: int, max_keys: int, sm_count: int, rings: dict[int, int], limit: int, most: int,
@@ -206,14 +224,28 @@ class TensorAttention:
         if (self._decode_split is not None and page >= 16 and page & (page - 1) == 0
                 and (kv.k.data_ptr() | kv.v.data_ptr()) % 16 == 0):
             units = requests * kv_heads * -(-group // 16)
-            ctas, stages = self.split_plan(units, max_keys, self.sm_count, self.split_rings, self.split_cta_limit,
+            ctas, stages = self.split_plan(units, max_keys, self.sm_count, self.split_rings(1, group), self.split_cta_limit,
                                            self.split_max, self.split_tile, MIN_KEYS_PER_SPLIT_CTA)
+            cluster = self.cluster_for(ctas)
+            if cluster > 1:
+                # Neighbouring CTAs of a unit in one cluster: whole clusters, and the deepest ring with
+                # which an SM still holds two CTAs.  (A cluster starts only when all its CTAs find room in
+                # one part of the device; with one CTA an SM the 16th cluster of 8 waits for a second
+                # round, which costs more than the exchange through shared memory saves.)
+                ctas -= ctas % cluster
+                rings = self.split_rings(cluster, group)
+                paired = [depth for depth in rings if rings[depth] >= 2]
+                if paired:
+                    stages = max(paired)
+                else:
+                    cluster = 1
             if FORCE_SPLIT_PLAN:
-                ctas, stages = FORCE_SPLIT_PLAN
+                ctas, stages = FORCE_SPLIT_PLAN[:2]
+                cluster = FORCE_SPLIT_PLAN[2] if len(FORCE_SPLIT_PLAN) > 2 else self.cluster_for(ctas)
             self._decode_split(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                                kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
                                ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, page, ctas,
-                               MIN_KEYS_PER_SPLIT_CTA, stages, self._split_shares.data_ptr(),
+                               MIN_KEYS_PER_SPLIT_CTA, stages, cluster, self._split_shares.data_ptr(),
                                self._split_tickets.data_ptr(), scale, window, ops.error_word.data_ptr(),
                                ops.stream)
             return
