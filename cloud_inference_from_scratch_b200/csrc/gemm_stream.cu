@@ -67,6 +67,20 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// ---- exchange inside a cluster without meeting: asynchronous stores into a peer's shared memory
+// that count on a barrier there
+__device__ __forceinline__ uint32_t map_to_rank(const void* p, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ void push_f32(uint32_t remote, float v, uint32_t bar) {
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+               ::"r"(remote), "f"(v), "r"(bar) : "memory");
+}
+
 [[maybe_unused]] constexpr int kOutBF16 = 0;
 constexpr int kOutF32 = 1, kOutPartial = 2, kOutSiluMul = 3, kOutResidual = 4, kOutRope = 5;
 
@@ -79,6 +93,8 @@ struct StreamArgs {
   int k_per_split;     // multiple of BK
   int mode;
   int early_trigger;   // mode 4: let the next kernel start before this one has waited for its predecessor
+  int push;            // modes 4, 5: the K slices reach the CTA that finishes a row by asynchronous stores
+                       // into its shared memory (1) instead of loads from the others' after a cluster barrier (0)
   int* err;            // error word for a wait that ran out (TMA variant), may be null
   // row scale: with row_sq the result rows are multiplied by rstd[m] = rsqrt(sum over tiles of
   // row_sq[m][tile] / K + eps) before bias, partial-sum output or activation (x then holds
@@ -164,6 +180,10 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
   unsigned char* x_s = reinterpret_cast<unsigned char*>(w_s + STAGES * WSTAGE);   // [STAGES][XSTAGE]
   __shared__ __align__(8) uint64_t full[STAGES];
   __shared__ float rstd_s[MP];
+  // cluster epilogues with a.push: what the other CTAs of the cluster send of the rows this CTA
+  // finishes, [peer, itself left out][row of this CTA][32 columns]; never more than MP rows
+  __shared__ float inbox_s[MP * 32];
+  __shared__ __align__(8) uint64_t inbox_bar;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * BN;
   const int k_begin = blockIdx.y * a.k_per_split;
@@ -218,12 +238,26 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
   // The weights do not depend on the kernel before this one: the CTA requests its first weight
   // tiles before waiting for it, so the weight stream overlaps the tail of that kernel.
   // (Asking L2 for the whole weight slice at this point was tried and made the step slower.)
-  if constexpr (TMA) {
+  // the CTAs that share this block of weight rows (a cluster along grid.y), for the epilogues that
+  // add their K slices up
+  const bool gathers = (a.mode == kOutResidual || a.mode == kOutRope) && gridDim.y > 1;
+  const bool pushes = gathers && a.push;
+  const int size = gathers ? (int)gridDim.y : 1, rank = gathers ? (int)blockIdx.y : 0;
+  if (TMA || pushes) {
     if (tid == 0) {
-      for (int s = 0; s < STAGES; ++s) bw::mbar_init(&full[s], 1);
+      if constexpr (TMA)
+        for (int s = 0; s < STAGES; ++s) bw::mbar_init(&full[s], 1);
+      if (pushes) bw::mbar_init(&inbox_bar, 1);
       bw::mbar_init_fence();
     }
     __syncthreads();
+  }
+  if (pushes) {
+    // row m is finished by the CTA of rank m % size: this one expects the other CTAs' 32 values of
+    // each of its rows, and tells the cluster that its inbox is ready (nobody waits here)
+    const int rows_owned = rank < a.m ? (a.m - rank + size - 1) / size : 0;
+    if (tid == 0 && rows_owned > 0) bw::mbar_expect_tx(&inbox_bar, (uint32_t)(rows_owned * (size - 1) * 32 * sizeof(float)));
+    cluster_arrive();
   }
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s)
@@ -314,12 +348,34 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
     out_s[(m0 + 1) * (BN + 1) + r0 + 8] = acc[mt][3] * s1;
   }
   __syncthreads();
+  const int rows_per_owner = (MP + size - 1) / size;
+  if (pushes) {
+    if constexpr (BN == 32) {
+      // every row of this CTA's slice goes to the CTA that finishes it; then this CTA waits for the
+      // others' slices of its own rows.  Nobody meets: a CTA whose rows are done may leave.
+      cluster_wait();   // every inbox of the cluster is ready (they said so when they started)
+      for (int m = warp; m < a.m; m += THREADS / 32) {
+        const int owner = m % size;
+        if (owner == rank) continue;
+        const int slot = rank < owner ? rank : rank - 1;
+        push_f32(map_to_rank(inbox_s + (slot * rows_per_owner + m / size) * 32 + lane, owner),
+                 out_s[m * (BN + 1) + lane], map_to_rank(&inbox_bar, owner));
+      }
+      if (rank < a.m && !bw::mbar_wait(&inbox_bar, 0, a.err ? a.err : &timeout_sink)) return;
+    }
+  }
+  // slice `r` of the 32 values of row m (a row this CTA finishes), r in rank order
+  auto slice_of = [&](cg::cluster_group& cluster, int r, int m) -> float {
+    if (r >= size) return 0.f;
+    if (!pushes) return cluster.map_shared_rank(out_s, r)[m * (BN + 1) + lane];
+    if (r == rank) return out_s[m * (BN + 1) + lane];
+    return inbox_s[((r < rank ? r : r - 1) * rows_per_owner + m / size) * 32 + lane];
+  };
   if (a.mode == kOutResidual) {
     if constexpr (BN == 32) {
       // the CTAs of the cluster hold the K slices of the same [M x 32] block; row m is finished by
       // the CTA of rank m % size, whose first warp adds the slices in rank order
       cg::cluster_group cluster = cg::this_cluster();
-      const int size = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
       // this CTA's rows are rank, rank + size, ...: warp w takes every (THREADS / 32)-th of them;
       // what does not depend on the other CTAs is fetched before the cluster meets
       const int col = n0 + lane;
@@ -333,7 +389,7 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
         const int m = first + i * stride;
         old[i] = (m < a.m && col < a.n) ? a.residual[(size_t)m * a.n + col] : 0.f;
       }
-      cluster.sync();
+      if (!pushes) cluster.sync();
 #pragma unroll
       for (int i = 0; i < MAX_ROWS; ++i) {
         const int m = first + i * stride;
@@ -341,8 +397,7 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
         // all remote loads are issued before the first addition (a cluster has at most 8 CTAs)
         float part[8];
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-          part[r] = r < size ? cluster.map_shared_rank(out_s, r)[m * (BN + 1) + lane] : 0.f;
+        for (int r = 0; r < 8; ++r) part[r] = slice_of(cluster, r, m);
         float v = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) v += part[r];
@@ -356,14 +411,13 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
         square = warp_sum(square);
         if (lane == 0) a.sq[(size_t)m * gridDim.x + blockIdx.x] = square;
       }
-      cluster.sync();   // nobody leaves while its shared memory may still be read
+      if (!pushes) cluster.sync();   // nobody leaves while its shared memory may still be read
     }
     return;
   }
   if (a.mode == kOutRope) {
     if constexpr (BN == 32) {
       cg::cluster_group cluster = cg::this_cluster();
-      const int size = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
       const int first = rank + warp * size, stride = size * (THREADS / 32);
       constexpr int MAX_ROWS = (MP + THREADS / 32 - 1) / (THREADS / 32);
       // the 32 columns of this CTA lie in one head (D is a multiple of 32)
@@ -398,15 +452,14 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
           }
         }
       }
-      cluster.sync();
+      if (!pushes) cluster.sync();
 #pragma unroll
       for (int i = 0; i < MAX_ROWS; ++i) {
         const int m = first + i * stride;
         if (m >= a.m) break;
         float part[8];
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-          part[r] = r < size ? cluster.map_shared_rank(out_s, r)[m * (BN + 1) + lane] : 0.f;
+        for (int r = 0; r < 8; ++r) part[r] = slice_of(cluster, r, m);
         float v = 0.f;
 #pragma unroll
         for (int r = 0; r < 8; ++r) v += part[r];
@@ -426,7 +479,7 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
           pool[slot[i] + (long long)head * a.page_size * a.dim + d_out] = rounded;
         }
       }
-      cluster.sync();
+      if (!pushes) cluster.sync();
     }
     return;
   }
@@ -511,6 +564,16 @@ static int launch(const StreamArgs& a, int splits, cudaStream_t stream) {
   return launch_variant<MT, BN, false>(w_map, a, splits, stream);
 }
 
+// CIE_STREAM_PUSH=0 in the environment keeps the cluster epilogues on loads from the peers' shared
+// memory between two cluster barriers.
+static int push_enabled() {
+  static const int enabled = [] {
+    const char* value = getenv("CIE_STREAM_PUSH");
+    return !(value && value[0] == '0') ? 1 : 0;
+  }();
+  return enabled;
+}
+
 // Cuts K into `splits` slices of whole tiles and picks the kernel for the row count.
 static int dispatch(StreamArgs& a, int splits, int block_rows, cudaStream_t s) {
   const int k_tiles = (a.k + BK - 1) / BK;
@@ -561,6 +624,7 @@ extern "C" int cie_gemm_stream_ex(const void* x, const float* row_sq, int row_ti
   a.row_sq = row_sq; a.row_tiles = row_tiles; a.eps = eps;
   a.residual = residual; a.sq = sq; a.scaled = (bf16*)scaled; a.next_gain = next_gain;
   a.early_trigger = early_trigger;
+  a.push = push_enabled();
   return dispatch(a, splits, block_rows, (cudaStream_t)stream);
 }
 
@@ -594,6 +658,7 @@ extern "C" int cie_gemm_stream_rope(const void* x, const float* row_sq, int row_
   a.k_pool = (bf16*)k_pool; a.v_pool = (bf16*)v_pool; a.inv_freq = inv_freq;
   a.q_heads = q_heads; a.kv_heads = kv_heads; a.dim = dim; a.rot = rot; a.page_size = page_size;
   a.write_cache = write_cache;
+  a.push = push_enabled();
   return dispatch(a, splits, 32, (cudaStream_t)stream);
 }
 
