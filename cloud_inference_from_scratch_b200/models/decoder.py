@@ -93,6 +93,12 @@ class DecoderModel:
         norms = [self.final_norm] + [part for layer in self.layers for slot, part in layer.parts.items()
                                      if layer.families[slot] == "norm"]
         self.norms_accept_accumulated = all(getattr(norm, "accepts_accumulated", False) for norm in norms)
+        # A decode step may be recorded and run as one persistent kernel only if every kernel of every
+        # part is a method of ``Ops`` (which then keeps the order of recorded and launched work); a part
+        # says so itself, and a part that launches anything of its own (torch ops included) does not.
+        self.records_programs = all(
+            getattr(part, "kernels_through_ops", False)
+            for layer in self.layers for part in [layer.block, *layer.parts.values()])
         self.embedding: Any = None
         self.head: Any = None
         self.runtime: Any = None
@@ -163,6 +169,7 @@ class DecoderModel:
         sink = rt.ops.residual_sink(residual) if self.norms_accept_accumulated else None
         ctx.residual_sink = sink
         pending = None
+        recorded = self.records_programs and sink is not None and rt.ops.begin_program(ctx)
         for index, entry in enumerate(spec.schedule):
             if sink is not None:
                 # what the block after this layer wants to know of its first norm (the final norm
@@ -173,6 +180,8 @@ class DecoderModel:
             pending = self.layers[entry.layer].block.forward(
                 residual, pending, ctx, ctx.bindings[index]
             )
+        if recorded:
+            rt.ops.end_program()
         if ctx.num_logit_rows == 0:
             return None
         x = self.final_norm.forward(residual, pending, ctx, rows=ctx.logit_rows)

@@ -14,4 +14,5 @@ def all_libraries() -> list[tuple[str, dict]]:
     libraries: list[tuple[str, dict]] = [(source, {}) for source in GENERIC]
     libraries += [("attention_tensor.cu", {"HEAD_DIM": dim}) for dim in ATTENTION_HEAD_DIMS]
     libraries += [("attention_prefill_tc.cu", {"HEAD_DIM": dim}) for dim in ATTENTION_HEAD_DIMS]
+    libraries += [("decode_program.cu", {"HEAD_DIM": dim}) for dim in ATTENTION_HEAD_DIMS]
     return libraries

@@ -117,6 +117,7 @@ class Ops:
         self._partial_buffers: dict[str, Any] = {}
         self.scratch_frozen = False
         self.scratch_generation = 0   # counts scratch buffers replaced by larger ones
+        self.program = None           # recorder of decode programs (native/program.py), made on first use
         if self.code == BF16 and self.gemm_mode != "simt":
             st = _Lib(load_library("gemm_stream.cu"))
             self._gemm_stream = st.function("cie_gemm_stream", [v, v, v, v, i, i, i, i, i, i, v, v])
@@ -135,6 +136,37 @@ class Ops:
     @property
     def stream(self) -> int:
         return self.torch.cuda.current_stream(self.device).cuda_stream
+
+    # ------------------------------------------------------------------ decode programs
+    def begin_program(self, ctx: Any) -> bool:
+        """Starts recording the streaming products and the decode attention of this step instead of
+        launching them (see native/program.py), if the step is one the persistent kernel takes: a
+        bfloat16 step of at most 16 tokens, each the single next token of its request.  Everything
+        else that runs through ``Ops`` meanwhile flushes what was recorded first.  ``end_program``
+        runs the rest."""
+        from . import program
+
+        if (self.code != BF16 or self._gemm_stream is None or not self.fuse_norm or not program.enabled()
+                or ctx.num_tokens > program.MAX_ROWS or ctx.num_tokens != ctx.num_requests
+                or ctx.num_single != ctx.num_requests):
+            return False
+        if self.program is None:
+            self.program = program.DecodeProgram(self)
+        self.program.begin()
+        return True
+
+    def end_program(self) -> None:
+        if self.program is not None:
+            self.program.end()
+
+    def _flush(self) -> None:
+        """Before a kernel that is not recorded: what was recorded so far runs first."""
+        if self.program is not None and self.program.calls:
+            self.program.flush()
+
+    @property
+    def recording(self) -> bool:
+        return self.program is not None and self.program.recording
 
     def _code_of(self, tensor: Any) -> int:
         if tensor.dtype == self.torch.float32:
@@ -181,6 +213,7 @@ class Ops:
     # ------------------------------------------------------------------ kernels
     def embedding(self, token_ids: Any, table: Any, residual: Any, scale: float = 1.0) -> None:
         """residual[t] = table[token_ids[t]] * scale, float32."""
+        self._flush()
         tokens, hidden = residual.shape
         self.launches += 1
         self._embedding(_ptr(token_ids), _ptr(table), _ptr(residual), tokens, hidden,
@@ -188,6 +221,7 @@ class Ops:
 
     def shape_logits(self, logits: Any, scale: float = 1.0, softcap: float = 0.0) -> None:
         """logits = softcap * tanh(logits * scale / softcap) (or logits * scale), float32, in place."""
+        self._flush()
         if scale == 1.0 and softcap == 0.0:
             return
         self.launches += 1
@@ -200,6 +234,7 @@ class Ops:
     def add_rmsnorm(self, residual: Any, update: Any, gain: Any, eps: float, out: Any,
                     rows: Any = None) -> None:
         """``update``: None, a tensor [T, H] of the compute dtype, or ``Partials``."""
+        self._flush()
         count, hidden = out.shape
         self.launches += 1
         if isinstance(update, Accumulated):
@@ -251,12 +286,17 @@ class Ops:
 
     def _stream(self, x: Any, weight: Any, bias: Any, out: Any, m: int, n: int, k: int, splits: int,
                 mode: int, residual: Any = None, sq: Any = None, scaled: Any = None,
-                next_gain: Any = None, early_trigger: bool = False) -> None:
+                next_gain: Any = None, early_trigger: bool = False, tag: str = "linear") -> None:
         """One launch of the streaming kernel; ``x`` is a tensor or a ``NormedInput``."""
-        self.launches += 1
         row_sq, tiles, eps = None, 0, 0.0
         if isinstance(x, NormedInput):
             row_sq, tiles, eps, x = x.accumulated.sq, x.accumulated.tiles, x.eps, x.accumulated.scaled
+        if self.recording and mode != 2 and weight.data_ptr() % 16 == 0 and (mode != 3 or n % 32 == 0):
+            self.program.gemm(x, row_sq, tiles, eps, weight, bias, out, residual, sq, scaled, next_gain,
+                              m, n, k, mode, tag)
+            return
+        self._flush()
+        self.launches += 1
         self._gemm_stream_ex(_ptr(x), _ptr(row_sq), tiles, eps, _ptr(weight), _ptr(bias), _ptr(out),
                              _ptr(residual), _ptr(sq), _ptr(scaled), _ptr(next_gain), m, n, k, splits,
                              mode, 32, 1 if early_trigger else 0, _ptr(self.error_word), self.stream)
@@ -298,15 +338,18 @@ class Ops:
                                           reserve=STREAM_MAX_ROWS * n // 2)
                     scaled = scaled.view(self.torch.bfloat16)[: m * n].view(m, n)
                 self._stream(x, weight, bias, None, m, n, k, cluster, 4, residual=residual.tensor, sq=sq,
-                             scaled=scaled, next_gain=gain, early_trigger=residual.early_trigger)
+                             scaled=scaled, next_gain=gain, early_trigger=residual.early_trigger,
+                             tag=tag or "linear")
                 return Accumulated(residual.tensor, sq, tiles, scaled, gain)
             if splits > 1:
                 scratch = self.scratch("partials." + (tag or "linear"), splits * m * n,
                                        reserve=splits * STREAM_MAX_ROWS * n)
                 self._stream(x, weight, None, scratch, m, n, k, splits, 2)
                 return Partials(scratch, splits, m, n, bias)
-            self._stream(x, weight, bias, out, m, n, k, 1, 1 if out.dtype == self.torch.float32 else 0)
+            self._stream(x, weight, bias, out, m, n, k, 1, 1 if out.dtype == self.torch.float32 else 0,
+                         tag=tag or "linear")
             return out
+        self._flush()
         if self._tensor_gemm is not None and self._tensor_gemm.run(x, weight, bias, out):
             return out
         if self.gemm_mode == "cublas" and self.code == BF16:
@@ -334,6 +377,7 @@ class Ops:
         """Many rows on the persistent tcgen05 kernel where that saves a whole pass over the
         activations: a projection that adds itself into the residual stream, or a product whose
         input rows are still to be divided by their root mean square.  None: not its case."""
+        self._flush()
         gemm = self._fold_gemm()
         if k % 8 or weight.data_ptr() % 16:
             return None
@@ -356,6 +400,7 @@ class Ops:
 
     def resolve(self, value: Any, out: Any) -> Any:
         """A plain tensor for a part that cannot consume ``Partials`` itself."""
+        self._flush()
         if not isinstance(value, Partials):
             return value
         if value.splits == 0:
@@ -391,11 +436,12 @@ class Ops:
         if self.code == BF16 and weight.block == 16:
             plan = self.stream_plan(m, 2 * inter, k, False)
             if plan is not None:
-                self._stream(x, weight.weight, None, hidden_out, m, 2 * inter, k, 1, 3)
+                self._stream(x, weight.weight, None, hidden_out, m, 2 * inter, k, 1, 3, tag="gate_up")
                 return hidden_out
         if (isinstance(x, NormedInput) and self.code == BF16 and weight.block == 16 and self.fold_rows
                 and m >= self.fold_rows and k % 8 == 0):
             acc = x.accumulated
+            self._flush()
             self._fold_gemm().launch_fused(acc.scaled, weight.weight, None, hidden_out, 3, row_sq=acc.sq,
                                               row_tiles=acc.tiles, eps=x.eps)
             return hidden_out
@@ -409,6 +455,7 @@ class Ops:
     def _cublas_linear(self, x: Any, weight: Any, bias: Any, out: Any) -> None:
         """Library matrix product (cuBLAS through torch), as the reference uses for every
         projection; kept as a yardstick for the hand-written tensor-core kernel."""
+        self._flush()
         torch = self.torch
         if out.dtype == torch.float32:
             torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)   # float32 straight into the caller's buffer
@@ -424,6 +471,7 @@ class Ops:
         rotated q (head h of token t at [t, h * head_dim]).  ``qkv`` is a tensor (q is rotated in
         place) or ``Partials`` (then q goes to ``q_buffer``).  ``paired``: the q and k columns of
         ``qkv`` are in the paired layout of ``pair_rotary_rows``; q then always goes to ``q_buffer``."""
+        self._flush()
         rot = position.rotary_dim if position is not None else 0
         inv_freq = position.inv_freq if position is not None else None
         table = ctx.block_tables[kv.group]
@@ -497,6 +545,12 @@ class Ops:
         if isinstance(x, NormedInput):
             row_sq, row_tiles, eps, x = x.accumulated.sq, x.accumulated.tiles, x.eps, x.accumulated.scaled
         table = ctx.block_tables[kv.group]
+        if self.recording and weight.data_ptr() % 16 == 0:
+            self.program.rope(x, row_sq, row_tiles, eps, weight, bias, q_buffer, ctx.positions,
+                              ctx.request_of_token, table, kv.num_pages, kv.k, kv.v, position.inv_freq, m,
+                              q_heads, kv_heads, head_dim, position.rotary_dim, kv.page_size, write_cache, k)
+            return q_buffer
+        self._flush()
         self.launches += 1
         self._gemm_stream_rope(_ptr(x), _ptr(row_sq), row_tiles, eps, _ptr(weight), _ptr(bias),
                                _ptr(q_buffer), q_buffer.shape[1], _ptr(ctx.positions),
@@ -509,6 +563,8 @@ class Ops:
     def attention(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
                   head_dim: int, scale: float, window: int) -> None:
         fast = self._tensor_attention.get(head_dim)
+        if fast is None:
+            self._flush()
         if fast is not None:
             plan = ctx.extras.get(("attention", q_heads // kv_heads)) or None
             if fast.run(qkv, out, ctx, kv, q_heads, kv_heads, scale, window, plan):
@@ -517,6 +573,7 @@ class Ops:
 
     def attention_generic(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int,
                           kv_heads: int, head_dim: int, scale: float, window: int) -> None:
+        self._flush()
         table = ctx.block_tables[kv.group]
         self.launches += 1
         self._attention_generic(_ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k),
@@ -526,6 +583,7 @@ class Ops:
                                 self._code_of(qkv), _ptr(self.error_word), self.stream)
 
     def silu_mul(self, gate_up: Any, out: Any, block: int | None = None) -> None:
+        self._flush()
         tokens, inter = out.shape
         self.launches += 1
         self._silu_mul(_ptr(gate_up), _ptr(out), tokens, inter, inter if block is None else block,
@@ -533,6 +591,7 @@ class Ops:
 
     def sample(self, logits: Any, temperature: Any, keys: Any, out: Any) -> None:
         """logits float32 [R, V]; temperature float32 [R] or None (greedy); keys int64 [R]."""
+        self._flush()
         rows, vocab = logits.shape
         if self._sample is None:
             v, i = c_void_p, c_int

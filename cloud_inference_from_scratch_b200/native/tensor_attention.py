@@ -266,6 +266,14 @@ class TensorAttention:
         table = ctx.block_tables[kv.group]
         group = q_heads // kv_heads
         singles = ctx.num_single
+        program = ops.program
+        if (program is not None and singles == ctx.num_requests
+                and program.can_attend(self.head_dim, kv.page_size, singles, kv.k, kv.v)):
+            # a decode step that is being recorded: a phase of its program, not a launch
+            program.attention(qkv, out, kv.k, kv.v, table, kv.num_pages, ctx.context_lens, singles, q_heads,
+                              kv_heads, self.head_dim, kv.page_size, scale, window)
+            return True
+        ops._flush()
         if singles:
             self._run_decode(qkv, out, ctx, kv, table, singles, q_heads, kv_heads, scale, window)
             if singles == ctx.num_requests:

@@ -109,6 +109,7 @@ class Attention(Mixer):
         runtime.ops.require_attention(self.head_dim)
 
     takes_normed_input = True   # x goes to ops.linear only
+    kernels_through_ops = True  # every kernel of this part is a method of ``Ops``: a decode step may be recorded
 
     def forward(self, x, ctx, binding):
         rt = self.runtime

@@ -72,6 +72,12 @@ class StateSpec:
 class Part:
     """Common protocol: declare tensors, take them, run."""
 
+    # True says: every kernel this part launches is a method of ``runtime.ops`` (no torch operation, no
+    # library of its own).  A decode step of a model whose parts all say so may be recorded and run
+    # as one persistent kernel (``Ops.begin_program``); one part that does not keeps every step on
+    # separate launches.
+    kernels_through_ops = False
+
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}
 
@@ -134,6 +140,7 @@ class Block:
 
     slots: tuple[str, ...] = ()
     cache_slot: str = "mixer"
+    kernels_through_ops = False   # as for a part: True if the block launches nothing but methods of ``Ops``
 
     def __init__(self, parts: "dict[str, Part]", **params: Any) -> None:
         missing = [name for name in self.slots if name not in parts]

@@ -28,6 +28,7 @@ def _lazy_gain(norm, consumer):
 
 class PreNormResidual(Block):
     slots = ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+    kernels_through_ops = True   # the block itself launches nothing
 
     def entry_gain(self):
         return _lazy_gain(self.mixer_norm, self.mixer)

@@ -29,6 +29,7 @@ class SwiGLU(FeedForward):
         self.w_down = runtime.ops.prepare_weight(tensors["down_proj.weight"])
 
     takes_normed_input = True   # x goes to ops.gate_up only
+    kernels_through_ops = True  # every kernel of this part is a method of ``Ops``: a decode step may be recorded
 
     def forward(self, x, ctx):
         rt = self.runtime

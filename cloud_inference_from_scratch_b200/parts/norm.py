@@ -25,6 +25,7 @@ class RMSNorm(Norm):
         self.weight = tensors["weight"]
 
     accepts_accumulated = True   # ``update`` may be an ``Accumulated``: the sum is already in the stream
+    kernels_through_ops = True  # every kernel of this part is a method of ``Ops``: a decode step may be recorded
 
     def forward(self, residual, update, ctx, rows=None):
         rt = self.runtime
