@@ -43,7 +43,11 @@ CIE_DEFINE_LAST_ERROR()
 
 namespace cie {
 
-constexpr int PG_CONSUMERS = 4;
+#ifndef PG_GROUPS
+#define PG_GROUPS 2
+#endif
+constexpr int PG_BOXES = 4;                       // warps that share a stage: one 64-column box (or 16 keys) each
+constexpr int PG_CONSUMERS = PG_BOXES * PG_GROUPS;   // groups of four warps take the stages in turn
 constexpr int PG_THREADS = 32 * (1 + PG_CONSUMERS);
 constexpr int PG_STAGE_BYTES = 16384;
 constexpr int PG_MAX_STAGES = 12;
@@ -53,14 +57,20 @@ constexpr int PG_TILE_KEYS = 64;    // keys of an attention tile: four blocks of
 constexpr int PG_BLOCK_BYTES = 16 * D * 2;                  // one 16-key block of K (or V)
 constexpr int PG_KEY_STAGES = (2 * PG_TILE_KEYS * D * 2) / PG_STAGE_BYTES;   // stages of a tile: K and V
 constexpr int PG_RED_ROW = PG_BN + 1;
-constexpr int PG_RED_BYTES = 2 * PG_CONSUMERS * 16 * PG_RED_ROW * 4;          // two buffers of [warp][16 tokens][33]
-constexpr int PG_MERGE_BYTES = PG_CONSUMERS * 16 * D * 4;                      // [warp][16 heads][D]
-constexpr int PG_SCRATCH_BYTES = ((PG_RED_BYTES > PG_MERGE_BYTES ? PG_RED_BYTES : PG_MERGE_BYTES) + 1023) / 1024 * 1024;
+constexpr int PG_RED_BYTES = (PG_CONSUMERS * 16 * PG_RED_ROW * 4 + 1023) / 1024 * 1024;   // [warp][16 tokens][33]
+constexpr int PG_MERGE_BYTES = PG_BOXES * 16 * D * 4;                          // [warp of a group][16 heads][D]
+// Shared memory behind the ring: the sums' buffer of the products, then a region that holds the token
+// rows of a product (the "slab": [64-column group][8 or 16 rows][128 bytes], sized by the launch) or,
+// in an attention phase, the merge buffer.
+constexpr int region_bytes(int slab_bytes) {
+  return ((slab_bytes > PG_MERGE_BYTES ? slab_bytes : PG_MERGE_BYTES) + 1023) / 1024 * 1024;
+}
 constexpr int PG_Q_BYTES = 16 * ROW * 2;
 constexpr int PG_SHARE_ROW = D + 4;                          // floats of a share's row: outputs, maximum, sum, padding
 constexpr int PG_MAX_KEY_SPLITS = 64;
 static_assert(D == 64 || D == 128, "the decode program is built for head sizes 64 and 128");
 static_assert(PG_KEY_STAGES == 1 || PG_KEY_STAGES == 2, "a key tile is one or two stages");
+static_assert(16 % PG_CONSUMERS == 0 || PG_CONSUMERS > 16, "the merge phase gives a unit's 16 head rows to whole groups of warps");
 
 enum : int { kEnd = 0, kGemm = 1, kFinish = 2, kAttention = 3, kMerge = 4 };
 constexpr int kOutBF16 = 0, kOutF32 = 1, kOutSiluMul = 3, kOutResidual = 4, kOutRope = 5;
@@ -122,6 +132,40 @@ struct ProgramShared {
   volatile int dead;    // a wait ran out somewhere in this CTA
 };
 
+// Diagnostics: with a buffer set (cie_program_set_trace) the first consumer thread of every CTA leaves
+// the global timer when it begins a phase (0), at two points inside it (2, 3: a product's token rows are
+// in shared memory; its last stage is multiplied) and when it has done its share of it (1).
+__device__ long long* g_program_trace = nullptr;
+__device__ int g_program_trace_phases = 0;
+__device__ __forceinline__ void trace_mark(int phase, int which, int ctid) {
+  if (ctid == 0 && g_program_trace && phase < g_program_trace_phases) {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_program_trace[((size_t)phase * gridDim.x + blockIdx.x) * 4 + which] = t;
+  }
+}
+
+#ifdef PROGRAM_PROBE
+// Debug builds only (-DPROGRAM_PROBE): the first consumer warp of one CTA leaves the clock around
+// every stage it multiplies (before the wait, after it, after the stage is given back).
+__device__ long long* g_program_probe = nullptr;
+__device__ int g_program_probe_cta = 0;
+__device__ int g_program_probe_slots = 0;
+__device__ int g_program_probe_used = 0;
+#define PROBE_DECLARE() long long probe_t[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROBE_AT(i) probe_t[i] = clock64()
+#define PROBE_STORE()                                                                             \
+  if (g_program_probe && (int)blockIdx.x == g_program_probe_cta && c.cw == 0 && lane == 0 &&      \
+      g_program_probe_used < g_program_probe_slots) {                                             \
+    const int at = g_program_probe_used++;                                                        \
+    for (int i = 0; i < 8; ++i) g_program_probe[at * 8 + i] = probe_t[i];                         \
+  }
+#else
+#define PROBE_DECLARE()
+#define PROBE_AT(i)
+#define PROBE_STORE()
+#endif
+
 constexpr long long kWaitCycles = 4000000000ll;    // about two seconds
 constexpr long long kDrainCycles = 200000000ll;    // about a tenth of a second, per stage, at the very end
 
@@ -138,6 +182,8 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, long lo
 }
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(PG_CONSUMERS * 32) : "memory"); }
+// the four warps of one group (barriers 2, 3, ...)
+__device__ __forceinline__ void group_sync(int group) { asm volatile("bar.sync %0, %1;" ::"r"(group + 2), "n"(PG_BOXES * 32) : "memory"); }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ unsigned load_acquire(const unsigned* p) {
   unsigned v;
@@ -146,25 +192,44 @@ __device__ __forceinline__ unsigned load_acquire(const unsigned* p) {
 }
 
 // ---- which part of a phase a CTA takes (the producer and the consumers must agree on every line)
-struct GemmUnit {
-  int tile, split, first_chunk, count, rotate;
+//
+// A product of row_tiles tiles of 32 weight rows, its K cut into `splits` slices of whole 256-column
+// chunks.  CTA c works on ONE slice, c % splits, for the whole phase (so the token columns it needs
+// fit shared memory and are fetched once), together with the other CTAs of that slice: it is number
+// c / splits among them and takes the tiles rank, rank + peers, rank + 2 peers, ...  Inside a tile the
+// chunks are walked from a chunk that differs between the CTAs of a slice, so that they do not all
+// ask for the same lines at the same moment.
+struct ProductShare {
+  int first_chunk, count;   // the slice's chunks
+  int rotate;               // the chunk (relative) a tile's walk begins with
+  int rank, peers;          // tiles rank, rank + peers, ... < row_tiles
+  int tiles;                // how many that is
+  __device__ __forceinline__ int chunk(int i) const {   // the i-th stage of a tile
+    int c = i + rotate;
+    if (c >= count) c -= count;
+    return first_chunk + c;
+  }
 };
-__device__ __forceinline__ GemmUnit gemm_unit(const Phase& p, int u) {
-  GemmUnit g;
-  g.tile = u % p.row_tiles;
-  g.split = u / p.row_tiles;
-  g.first_chunk = (int)(((long long)g.split * p.chunks) / p.splits);
-  g.count = (int)(((long long)(g.split + 1) * p.chunks) / p.splits) - g.first_chunk;
-  // CTAs walk their K range from different chunks, so that they do not all ask L2 for the same
-  // token columns at the same moment
-  g.rotate = g.count > 0 ? (int)(blockIdx.x % (unsigned)g.count) : 0;
-  return g;
+__device__ __forceinline__ ProductShare product_share(const Phase& p) {
+  ProductShare s;
+  const int slice = (int)(blockIdx.x % (unsigned)p.splits);
+  s.rank = (int)(blockIdx.x / (unsigned)p.splits);
+  s.peers = ((int)gridDim.x - slice + p.splits - 1) / p.splits;
+  s.first_chunk = (slice * p.chunks) / p.splits;            // splits * chunks stays far below 2^31
+  s.count = ((slice + 1) * p.chunks) / p.splits - s.first_chunk;
+  s.rotate = s.count > 0 ? s.rank % s.count : 0;
+  s.tiles = s.rank < p.row_tiles ? (p.row_tiles - s.rank + s.peers - 1) / s.peers : 0;
+  if (s.count <= 0) s.tiles = 0;
+  return s;
 }
-__device__ __forceinline__ int gemm_chunk(const GemmUnit& g, int i) {
-  int c = i + g.rotate;
-  if (c >= g.count) c -= g.count;
-  return g.first_chunk + c;
-}
+// How the stages of a CTA's tiles reach the two groups of consumer warps.
+//  * Several tiles: they go to the groups in turn, whole (the CTA's tile number j to group j % 2), and
+//    the producer fills stages of the two groups' tiles alternately for as long as both have some
+//    left, so that both groups stream at the same time and each finishes its own tiles.
+//  * One tile: the two groups share it, stage i going to group i % 2, and add their sums up at its end.
+// Either way the ring's stages go to group 0 and group 1 in turn while both have stages left (group
+// 0 first), and to the one that has some left after that.
+static_assert(PG_GROUPS == 2, "the stages of a product are dealt to two groups of consumer warps");
 
 struct KeyUnit {
   int unit, split, request, kvh, h0;
@@ -204,6 +269,13 @@ struct Ring {
       parity ^= 1u;
     }
   }
+  __device__ __forceinline__ void skip(int count) {   // stages that somebody else takes
+    slot += count;
+    while (slot >= stages) {
+      slot -= stages;
+      parity ^= 1u;
+    }
+  }
 };
 
 __device__ void run_producer(const Phase* __restrict__ tape, Ring ring, int* err, int lane) {
@@ -222,20 +294,43 @@ __device__ void run_producer(const Phase* __restrict__ tape, Ring ring, int* err
     const int kind = p.kind;
     if (kind == kEnd) break;
     if (kind == kGemm) {
-      const int units = p.row_tiles * p.splits;
-      for (int u = blockIdx.x; u < units && alive; u += gridDim.x) {
-        const GemmUnit g = gemm_unit(p, u);
-        for (int i = 0; i < g.count; ++i) {
-          if (!acquire()) { alive = false; break; }
-          const int chunk = gemm_chunk(g, i);
-          uint64_t* bar = &sh.full[ring.slot];
-          if (lane == 0) bw::mbar_expect_tx(bar, PG_STAGE_BYTES);
-          __syncwarp();
-          if (lane < 4)
-            bw::tma_load_2d(ring.base + (size_t)ring.slot * PG_STAGE_BYTES + lane * 4096, &p.map0, bar,
-                            chunk * PG_KC + lane * 64, g.tile * PG_BN);
-          ring.advance();
-          ++issued;
+      auto issue = [&](int tile, int chunk) -> bool {
+        if (!acquire()) return false;
+        uint64_t* bar = &sh.full[ring.slot];
+        if (lane == 0) bw::mbar_expect_tx(bar, PG_STAGE_BYTES);
+        __syncwarp();
+        if (lane < 4)
+          bw::tma_load_2d(ring.base + (size_t)ring.slot * PG_STAGE_BYTES + lane * 4096, &p.map0, bar,
+                          chunk * PG_KC + lane * 64, tile * PG_BN);
+        ring.advance();
+        ++issued;
+        return true;
+      };
+      const ProductShare share = product_share(p);
+      if (share.tiles == 1) {
+        for (int i = 0; i < share.count && alive; ++i) alive = issue(share.rank, share.chunk(i));
+      } else if (share.tiles > 1) {
+        // two streams of tiles: rank, rank + 2 peers, ... and rank + peers, rank + 3 peers, ...
+        int tile0 = share.rank, tile1 = share.rank + share.peers, i0 = 0, i1 = 0, turn = 0;
+        bool live0 = true, live1 = tile1 < p.row_tiles;
+        while ((live0 || live1) && alive) {
+          if (live0 && (turn == 0 || !live1)) {
+            alive = issue(tile0, share.chunk(i0));
+            if (++i0 == share.count) {
+              i0 = 0;
+              tile0 += 2 * share.peers;
+              live0 = tile0 < p.row_tiles;
+            }
+            turn = 1;
+          } else {
+            alive = issue(tile1, share.chunk(i1));
+            if (++i1 == share.count) {
+              i1 = 0;
+              tile1 += 2 * share.peers;
+              live1 = tile1 < p.row_tiles;
+            }
+            turn = 0;
+          }
         }
       }
     } else if (kind == kAttention) {
@@ -318,11 +413,13 @@ __device__ void run_producer(const Phase* __restrict__ tape, Ring ring, int* err
 struct Consumer {
   Ring ring;
   float* scratch;
+  unsigned char* slab;   // the token rows of a product (behind the sums' buffer); attention's merge buffer
   bf16* q_s;
   int* err;
-  int cw, lane, ctid;
+  int phase_index;      // (for the trace)
+  int cw, lane, ctid;   // consumer warp 0 .. PG_CONSUMERS - 1, lane, thread among the consumers
+  int group, box;       // cw / 4: which stages it takes; cw % 4: which part of a stage
   bool alive;
-  int red_buffer;
   // waits for the stage at ring.slot to be full
   __device__ __forceinline__ void wait_full() {
     if (alive) {   // the same in every lane of the warp
@@ -344,6 +441,10 @@ struct Consumer {
 };
 
 __device__ __forceinline__ float load_cg(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ void ldsm_x4_at(uint32_t (&r)[4], uint32_t shared_address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(shared_address));
+}
 
 // The epilogue of one finished value: row m (token), column `col` = tile * 32 + lane of the product.
 // The whole warp calls this for one token row.
@@ -415,15 +516,54 @@ __device__ __forceinline__ void finish_value(const Phase& p, int m, int tile, in
   }
 }
 
+// The slices of a finished tile are in red[warp][token][weight row] (`slices` of them: a group's four,
+// or all consumers' when the groups shared the unit).  The warps taking part (number `part` of
+// `parts`) add them up for the token rows part, part + parts, ... and run the epilogue (or leave the
+// partial sums of a K slice).
+__device__ __noinline__ void tile_epilogue(const Phase& p, const Consumer& c, const float* red, int slices, int part,
+                                           int parts, int tile, int split) {
+  const int lane = c.lane;
+  for (int m = part; m < p.m; m += parts) {
+    float v = 0.f;
+    for (int w = 0; w < slices; ++w) v += red[(w * 16 + m) * PG_RED_ROW + lane];
+    if (p.row_sq) v *= c.ring.sh->rstd[m];
+    if (p.splits > 1) {
+      const int col = tile * PG_BN + lane;
+      if (col < p.n) __stcg(p.partial + ((size_t)split * p.m + m) * p.n + col, v);
+    } else {
+      finish_value(p, m, tile, lane, v, c.err);
+    }
+  }
+}
+
 template <int MT>
-__device__ void gemm_phase(const Phase& p, Consumer& c) {
+__device__ __noinline__ void gemm_phase(const Phase& p, Consumer& shared_state) {
+  Consumer c = shared_state;   // in registers while the phase runs
   constexpr int MP = MT * 8;
+  constexpr int XG = MP * 128;   // bytes of one 64-column group of the slab: MP rows of 128 bytes
   ProgramShared& sh = *c.ring.sh;
-  const int lane = c.lane, cw = c.cw;
+  const int lane = c.lane, box_index = c.box, group = c.group;
   const int g = lane >> 2, t4 = lane & 3;
+  const ProductShare share = product_share(p);
+  // ---- the token rows of this CTA's slice of K go to shared memory once, for the whole phase: the
+  // slab, [64-column group][MP rows][128 bytes], the 16-byte piece c of row r at position c ^ (r & 7)
+  // as in the weight boxes (rows beyond the step's and columns beyond K are zeros)
+  {
+    const int k_begin = share.first_chunk * PG_KC, k_total = p.k, rows = p.m, x_stride = p.x_stride;
+    const bf16* x = p.x;
+    const int pieces = share.tiles > 0 ? share.count * (PG_KC / 8) * MP : 0;
+    for (int index = c.ctid; index < pieces; index += PG_CONSUMERS * 32) {
+      const int piece = index & 7, row = (index >> 3) % MP, group64 = (index >> 3) / MP;
+      const int k0 = k_begin + group64 * 64 + piece * 8;
+      const bool ok = row < rows && k0 < k_total;
+      cp_async16(c.slab + group64 * XG + row * 128 + ((piece ^ (row & 7)) << 4),
+                 ok ? x + (size_t)row * x_stride + k0 : x, ok);
+    }
+    cp_async_commit();
+  }
   if (p.row_sq) {
     // rstd of the token rows from the sums of squares that an earlier phase left per 32 columns
-    for (int m = cw; m < MP; m += PG_CONSUMERS) {
+    for (int m = c.cw; m < MP; m += PG_CONSUMERS) {
       float sum = 0.f;
       if (m < p.m)
         for (int t = lane; t < p.sq_tiles; t += 32) sum += load_cg(p.row_sq + (size_t)m * p.sq_tiles + t);
@@ -431,91 +571,127 @@ __device__ void gemm_phase(const Phase& p, Consumer& c) {
       if (lane == 0) sh.rstd[m] = m < p.m ? rsqrtf(sum / (float)p.k + p.eps) : 0.f;
     }
   }
-  // this thread's token rows (one per 8-token tile) as the 8-wide operand
-  const uint32_t* xrow[MT];
+  // ---- this group's stages.  One tile: every second stage of it.  Several: every stage of every
+  // second tile.  The ring's stages go to the groups in turn while both have some left.
+  const bool shared = share.tiles == 1;
+  const int own_tiles = shared ? 1 : (share.tiles + 1 - group) / 2;
+  const int own_total = shared ? (share.count + 1 - group) / 2 : own_tiles * share.count;
+  const int other_total = shared ? share.count - own_total : (share.tiles - own_tiles) * share.count;
+  const int both = own_total < other_total ? own_total : other_total;
+  // per-lane offsets that do not change with the stage
+  int a_offset[4][2];   // of the A fragments inside this warp's box
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-    xrow[mt] = (mt * 8 + g < p.m) ? reinterpret_cast<const uint32_t*>(p.x + (size_t)(mt * 8 + g) * p.x_stride) : nullptr;
-  // B fragments of one chunk for this warp's box: k = chunk * 256 + cw * 64 + 16 i + {2 t4, 2 t4 + 8}
-  auto load_b = [&](uint32_t (&b)[MT][4][2], int chunk) {
-    const int kbase = chunk * PG_KC + cw * 64 + 2 * t4;
+  for (int i16 = 0; i16 < 4; ++i16)
+#pragma unroll
+    for (int rt = 0; rt < 2; ++rt) {
+      const int row = rt * 16 + (lane & 15), piece = 2 * i16 + (lane >> 4);
+      a_offset[i16][rt] = box_index * 4096 + row * 128 + ((piece ^ (row & 7)) << 4);
+    }
+  int b_offset[2][MT];  // of the B fragments inside a chunk of the slab (this warp's 64-column group)
+#pragma unroll
+  for (int pair = 0; pair < 2; ++pair)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
+      b_offset[pair][mt] = box_index * XG + (mt * 8 + (lane & 7)) * 128 + (((4 * pair + (lane >> 3)) ^ (lane & 7)) << 4);
+  // two accumulator sets a row tile (even and odd k-steps) halve the chains of dependent
+  // tensor-core instructions; they are added when the tile is complete
+  float acc[2][2][MT][4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int k0 = kbase + 16 * i;
-        b[mt][i][0] = (xrow[mt] && k0 < p.k) ? __ldcg(xrow[mt] + (k0 >> 1)) : 0u;
-        b[mt][i][1] = (xrow[mt] && k0 + 8 < p.k) ? __ldcg(xrow[mt] + ((k0 + 8) >> 1)) : 0u;
-      }
-  };
-  const int units = p.row_tiles * p.splits;
-  for (int u = blockIdx.x; u < units; u += gridDim.x) {
-    const GemmUnit unit = gemm_unit(p, u);
-    float acc[2][MT][4];
+  for (int e = 0; e < 2; ++e)
 #pragma unroll
     for (int rt = 0; rt < 2; ++rt)
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) acc[rt][mt][0] = acc[rt][mt][1] = acc[rt][mt][2] = acc[rt][mt][3] = 0.f;
-    uint32_t b_now[MT][4][2], b_next[MT][4][2];
-    if (unit.count > 0) load_b(b_now, gemm_chunk(unit, 0));
-    for (int i = 0; i < unit.count; ++i) {
-      if (i + 1 < unit.count) load_b(b_next, gemm_chunk(unit, i + 1));
-      c.wait_full();
-      const unsigned char* box = c.ring.base + (size_t)c.ring.slot * PG_STAGE_BYTES + cw * 4096;
-#pragma unroll
-      for (int i16 = 0; i16 < 4; ++i16) {
-#pragma unroll
-        for (int rt = 0; rt < 2; ++rt) {
-          const int row = rt * 16 + (lane & 15), piece = 2 * i16 + (lane >> 4);
-          uint32_t a[4];
-          ldsm_x4(a, box + row * 128 + ((piece ^ (row & 7)) << 4));
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) mma_bf16(acc[rt][mt], a, b_now[mt][i16][0], b_now[mt][i16][1]);
-        }
-      }
-      c.release(c.ring.slot);
-      c.ring.advance();
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i16 = 0; i16 < 4; ++i16) {
-          b_now[mt][i16][0] = b_next[mt][i16][0];
-          b_now[mt][i16][1] = b_next[mt][i16][1];
-        }
-    }
-    // ---- the four warps' slices of the tile meet in shared memory: red[warp][token][weight row]
-    float* red = c.scratch + c.red_buffer * (PG_CONSUMERS * 16 * PG_RED_ROW);
-    c.red_buffer ^= 1;
+      for (int mt = 0; mt < MT; ++mt) acc[e][rt][mt][0] = acc[e][rt][mt][1] = acc[e][rt][mt][2] = acc[e][rt][mt][3] = 0.f;
+  // sums of a tile: a group's own four slices, or all eight when the groups share the tile
+  float* red = shared ? c.scratch : c.scratch + group * (PG_BOXES * 16 * PG_RED_ROW);
+  const int slice = shared ? c.cw : box_index;
+  auto put_sums = [&]() {
 #pragma unroll
     for (int rt = 0; rt < 2; ++rt)
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int m0 = mt * 8 + 2 * t4, r0 = rt * 16 + g;
-        const float s0 = p.row_sq ? sh.rstd[m0] : 1.f, s1 = p.row_sq ? sh.rstd[m0 + 1] : 1.f;
-        float* mine = red + (cw * 16 + m0) * PG_RED_ROW + r0;
-        mine[0] = acc[rt][mt][0] * s0;
-        mine[PG_RED_ROW] = acc[rt][mt][1] * s1;
-        mine[8] = acc[rt][mt][2] * s0;
-        mine[PG_RED_ROW + 8] = acc[rt][mt][3] * s1;
-      }
-    c.sync();
-    for (int m = cw; m < p.m; m += PG_CONSUMERS) {
-      float v = 0.f;
+        float* mine = red + (slice * 16 + m0) * PG_RED_ROW + r0;
+        mine[0] = acc[0][rt][mt][0] + acc[1][rt][mt][0];
+        mine[PG_RED_ROW] = acc[0][rt][mt][1] + acc[1][rt][mt][1];
+        mine[8] = acc[0][rt][mt][2] + acc[1][rt][mt][2];
+        mine[PG_RED_ROW + 8] = acc[0][rt][mt][3] + acc[1][rt][mt][3];
 #pragma unroll
-      for (int w = 0; w < PG_CONSUMERS; ++w) v += red[(w * 16 + m) * PG_RED_ROW + lane];
-      if (p.splits > 1) {
-        const int col = unit.tile * PG_BN + lane;
-        if (col < p.n) __stcg(p.partial + ((size_t)unit.split * p.m + m) * p.n + col, v);
-      } else {
-        finish_value(p, m, unit.tile, lane, v, c.err);
+        for (int e = 0; e < 2; ++e)
+          acc[e][rt][mt][0] = acc[e][rt][mt][1] = acc[e][rt][mt][2] = acc[e][rt][mt][3] = 0.f;
       }
+  };
+  cp_async_wait<0>();
+  c.sync();   // the slab and rstd are there for everybody
+  trace_mark(c.phase_index, 2, c.ctid);
+  int tile = share.rank + (shared ? 0 : group * share.peers);
+  int in_tile = shared ? group : 0;          // stage of the tile that comes next for this group
+  const int in_tile_step = shared ? 2 : 1;
+  for (int done = 0; done < own_total; ++done) {
+    PROBE_DECLARE();
+    PROBE_AT(0);
+    if (group == 1 && done < both) c.ring.advance();   // the other group's stage lies in front of this one
+    PROBE_AT(1);
+    int relative = in_tile + share.rotate;             // the chunk of this stage, counted from the slice's first
+    if (relative >= share.count) relative -= share.count;
+    PROBE_AT(2);
+    c.wait_full();
+    PROBE_AT(3);
+    PROBE_AT(4);
+#ifndef PROGRAM_SKIP_MATH   // (debug builds may leave the products out to see what the rest costs)
+    const uint32_t box = smem_u32(c.ring.base) + c.ring.slot * PG_STAGE_BYTES;
+    const uint32_t xb = smem_u32(c.slab) + relative * (4 * XG);
+    // every fragment of the stage is asked for before the first product needs one
+    uint32_t bfrag[2][MT][4], afrag[4][2][4];
+#pragma unroll
+    for (int pair = 0; pair < 2; ++pair)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) ldsm_x4_at(bfrag[pair][mt], xb + b_offset[pair][mt]);
+#pragma unroll
+    for (int i16 = 0; i16 < 4; ++i16)
+#pragma unroll
+      for (int rt = 0; rt < 2; ++rt) ldsm_x4_at(afrag[i16][rt], box + a_offset[i16][rt]);
+#pragma unroll
+    for (int i16 = 0; i16 < 4; ++i16)
+#pragma unroll
+      for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          mma_bf16(acc[i16 & 1][rt][mt], afrag[i16][rt], bfrag[i16 >> 1][mt][2 * (i16 & 1)], bfrag[i16 >> 1][mt][2 * (i16 & 1) + 1]);
+#endif
+    PROBE_AT(5);
+    c.release(c.ring.slot);
+    c.ring.advance();
+    if (group == 0 && done < both) c.ring.advance();   // the other group's stage lies behind this one
+    PROBE_AT(6);
+    PROBE_STORE();
+    in_tile += in_tile_step;
+    if (!shared && in_tile == share.count) {
+      // ---- the group's tile is complete: its four slices meet in shared memory
+      group_sync(group);   // the group's tile before has been read
+      put_sums();
+      group_sync(group);
+      tile_epilogue(p, c, red, PG_BOXES, box_index, PG_BOXES, tile, (int)(blockIdx.x % (unsigned)p.splits));
+      in_tile = 0;
+      tile += 2 * share.peers;
     }
   }
+  trace_mark(c.phase_index, 3, c.ctid);
+  // what is left of the phase's stages in this CTA belongs to the other group
+  c.ring.skip(other_total - both);
+  if (shared) {
+    // ---- the tile the groups shared: all eight slices meet (a group without a stage brings zeros)
+    put_sums();
+    c.sync();
+    tile_epilogue(p, c, red, PG_CONSUMERS, c.cw, PG_CONSUMERS, tile, (int)(blockIdx.x % (unsigned)p.splits));
+  }
+  if (sh.dead) c.alive = false;
+  shared_state = c;
 }
 
 // The rstd scale of a product that was cut along K is applied to its partial sums (gemm_phase);
 // this phase adds the slices up in ascending order and runs the epilogue.
-__device__ void finish_phase(const Phase& p, Consumer& c) {
+__device__ __noinline__ void finish_phase(const Phase& p, Consumer& c) {
   const int lane = c.lane;
   for (int tile = blockIdx.x; tile < p.row_tiles; tile += gridDim.x) {
     const int col = tile * PG_BN + lane;
@@ -537,11 +713,12 @@ __device__ void finish_phase(const Phase& p, Consumer& c) {
   }
 }
 
-__device__ void attention_phase(const Phase& p, Consumer& c) {
+__device__ __noinline__ void attention_phase(const Phase& p, Consumer& shared_state) {
+  Consumer c = shared_state;   // in registers while the phase runs
   ProgramShared& sh = *c.ring.sh;
-  const int lane = c.lane, cw = c.cw;
+  const int lane = c.lane, cw = c.cw, box_index = c.box;
   const int g = lane >> 2, t4 = lane & 3;
-  float* merge_s = c.scratch;   // [warp][16][D]
+  float* merge_s = reinterpret_cast<float*>(c.slab);   // [warp of a group][16][D]
   const int units = p.m * p.kv_heads * p.head_chunks * p.key_splits;
   for (int u = blockIdx.x; u < units; u += gridDim.x) {
     const KeyUnit k = key_unit(p, u);
@@ -567,11 +744,16 @@ __device__ void attention_phase(const Phase& p, Consumer& c) {
     for (int i = 0; i < NTILES_D; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float mx[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     for (int tile = 0; tile < k.tiles; ++tile) {
-      const int k0 = k.begin + tile * PG_TILE_KEYS + cw * 16;   // this warp's 16 keys of the tile
+      if (tile % PG_GROUPS != c.group) {   // another group's tile
+#pragma unroll
+        for (int i = 0; i < PG_KEY_STAGES; ++i) c.ring.advance();
+        continue;
+      }
+      const int k0 = k.begin + tile * PG_TILE_KEYS + box_index * 16;   // this warp's 16 keys of the tile
       const bool mine = k0 < k.end;
       c.wait_full();
       const int k_slot = c.ring.slot;
-      const bf16* k_tile = reinterpret_cast<const bf16*>(c.ring.base + (size_t)k_slot * PG_STAGE_BYTES + cw * PG_BLOCK_BYTES);
+      const bf16* k_tile = reinterpret_cast<const bf16*>(c.ring.base + (size_t)k_slot * PG_STAGE_BYTES + box_index * PG_BLOCK_BYTES);
       float s[2][4];
       if (mine && c.alive) {
         scores<1, true>(q_frag, k_tile, s, lane);
@@ -597,7 +779,7 @@ __device__ void attention_phase(const Phase& p, Consumer& c) {
         c.release(k_slot);
         c.ring.advance();
         c.wait_full();
-        v_tile = reinterpret_cast<const bf16*>(c.ring.base + (size_t)c.ring.slot * PG_STAGE_BYTES + cw * PG_BLOCK_BYTES);
+        v_tile = reinterpret_cast<const bf16*>(c.ring.base + (size_t)c.ring.slot * PG_STAGE_BYTES + box_index * PG_BLOCK_BYTES);
       } else {
         v_tile = k_tile + 4 * PG_BLOCK_BYTES / 2;
       }
@@ -605,7 +787,10 @@ __device__ void attention_phase(const Phase& p, Consumer& c) {
       c.release(c.ring.slot);
       c.ring.advance();
     }
-    // ---- the warps of the CTA: maxima and sums first, then the outputs scaled to the CTA's maxima
+    // ---- the warps of the CTA: maxima and sums first, then the outputs scaled to the CTA's maxima.
+    // The warps of the other groups hand their outputs to the first group's warp with the same part
+    // of a tile (the same thread holds the same elements), which adds them to its own; then the
+    // first group's four slices meet in the merge buffer.
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const float total = quad_sum(l[h]);
@@ -615,7 +800,7 @@ __device__ void attention_phase(const Phase& p, Consumer& c) {
       }
     }
     c.sync();
-    float* my_merge = merge_s + cw * 16 * D;
+    float* my_merge = merge_s + box_index * 16 * D;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = g + h * 8;
@@ -624,9 +809,39 @@ __device__ void attention_phase(const Phase& p, Consumer& c) {
       for (int w = 0; w < PG_CONSUMERS; ++w) m_all = fmaxf(m_all, sh.warp_max[w][r]);
       const float scale_mine = (mx[h] == -INFINITY) ? 0.f : exp2f(mx[h] - m_all);
 #pragma unroll
-      for (int i = 0; i < NTILES_D; ++i)
-        *reinterpret_cast<float2*>(my_merge + r * D + i * 8 + 2 * t4) =
-            make_float2(o[i][2 * h] * scale_mine, o[i][2 * h + 1] * scale_mine);
+      for (int i = 0; i < NTILES_D; ++i) {
+        o[i][2 * h] *= scale_mine;
+        o[i][2 * h + 1] *= scale_mine;
+      }
+    }
+#pragma unroll
+    for (int other = 1; other < PG_GROUPS; ++other) {
+      if (c.group == other) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < NTILES_D; ++i)
+            *reinterpret_cast<float2*>(my_merge + (g + h * 8) * D + i * 8 + 2 * t4) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+      }
+      c.sync();
+      if (c.group == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < NTILES_D; ++i) {
+            const float2 theirs = *reinterpret_cast<const float2*>(my_merge + (g + h * 8) * D + i * 8 + 2 * t4);
+            o[i][2 * h] += theirs.x;
+            o[i][2 * h + 1] += theirs.y;
+          }
+      }
+      c.sync();
+    }
+    if (c.group == 0) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < NTILES_D; ++i)
+          *reinterpret_cast<float2*>(my_merge + (g + h * 8) * D + i * 8 + 2 * t4) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
     }
     c.sync();
     bf16* out_rows = p.attn_out + (size_t)k.request * p.out_stride + (size_t)(k.kvh * p.group + k.h0) * D;
@@ -635,7 +850,7 @@ __device__ void attention_phase(const Phase& p, Consumer& c) {
       const int r = idx / (D / 4), c4 = idx % (D / 4);
       float4 acc = *reinterpret_cast<const float4*>(merge_s + r * D + c4 * 4);
 #pragma unroll
-      for (int w = 1; w < PG_CONSUMERS; ++w) {
+      for (int w = 1; w < PG_BOXES; ++w) {
         const float4 part = *reinterpret_cast<const float4*>(merge_s + (w * 16 + r) * D + c4 * 4);
         acc.x += part.x; acc.y += part.y; acc.z += part.z; acc.w += part.w;
       }
@@ -663,16 +878,18 @@ __device__ void attention_phase(const Phase& p, Consumer& c) {
       }
     }
   }
+  shared_state = c;
 }
 
 // Joins the shares of the CTAs that divided a request's keys: a warp takes one head row and merges
 // the shares in the order of the key ranges, eight at a time, with a running maximum.
-__device__ void merge_phase(const Phase& p, Consumer& c) {
+__device__ __noinline__ void merge_phase(const Phase& p, Consumer& c) {
   const int lane = c.lane;
   const int base = p.m * p.kv_heads * p.head_chunks;
-  for (int u = blockIdx.x; u < base * 4; u += gridDim.x) {
-    const KeyUnit k = key_unit(p, u / 4);   // split 0 of the unit: lengths and the count of shares
-    const int r = (u % 4) * 4 + c.cw;
+  constexpr int PARTS = 16 / PG_CONSUMERS;   // a unit's 16 head rows: one a warp
+  for (int u = blockIdx.x; u < base * PARTS; u += gridDim.x) {
+    const KeyUnit k = key_unit(p, u / PARTS);   // split 0 of the unit: lengths and the count of shares
+    const int r = (u % PARTS) * PG_CONSUMERS + c.cw;
     const int live_rows = min(16, p.group - k.h0);
     if (k.used == 1 || r >= live_rows || lane >= D / 4) continue;
     const float* row = p.shares + ((size_t)k.unit * p.key_splits * 16 + r) * PG_SHARE_ROW;
@@ -717,8 +934,9 @@ __device__ void grid_barrier(Consumer& c, unsigned* counter, int passed) {
   ProgramShared& sh = *c.ring.sh;
   consumer_sync();
   if (c.ctid == 0) {
-    __threadfence();
-    atomicAdd(counter, 1u);
+    // a release at GPU scope: what the CTA's threads wrote before the barrier above is visible to
+    // whoever sees the count
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
     const unsigned target = (unsigned)(passed + 1) * gridDim.x;
     if (!sh.dead) {
       const long long start = clock64();
@@ -740,6 +958,8 @@ __device__ void run_consumers(const Phase* __restrict__ tape, Consumer c, unsign
     const Phase& p = tape[pi];
     const int kind = p.kind;
     if (kind == kEnd) break;
+    trace_mark(pi, 0, c.ctid);
+    c.phase_index = pi;
     if (kind == kGemm) {
       if (p.m <= 8) gemm_phase<1>(p, c);
       else gemm_phase<2>(p, c);
@@ -750,13 +970,14 @@ __device__ void run_consumers(const Phase* __restrict__ tape, Consumer c, unsign
     } else if (kind == kMerge) {
       merge_phase(p, c);
     }
+    trace_mark(pi, 1, c.ctid);
     if (tape[pi + 1].kind == kEnd) break;   // what the last phase wrote is visible when the kernel ends
     grid_barrier(c, counter, pi);
   }
 }
 
 __global__ void __launch_bounds__(PG_THREADS, 1)
-decode_program_kernel(const Phase* __restrict__ tape, unsigned* counter, int* err, int stages) {
+decode_program_kernel(const Phase* __restrict__ tape, unsigned* counter, int* err, int stages, int slab_bytes) {
   extern __shared__ __align__(16) unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~(uintptr_t)1023);
   __shared__ ProgramShared sh;
@@ -764,7 +985,7 @@ decode_program_kernel(const Phase* __restrict__ tape, unsigned* counter, int* er
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       bw::mbar_init(&sh.full[s], 1);
-      bw::mbar_init(&sh.empty[s], PG_CONSUMERS);
+      bw::mbar_init(&sh.empty[s], PG_BOXES);
     }
     sh.epoch = 0;
     sh.dead = 0;
@@ -784,13 +1005,15 @@ decode_program_kernel(const Phase* __restrict__ tape, unsigned* counter, int* er
     Consumer c;
     c.ring = ring;
     c.scratch = reinterpret_cast<float*>(smem + (size_t)stages * PG_STAGE_BYTES);
-    c.q_s = reinterpret_cast<bf16*>(smem + (size_t)stages * PG_STAGE_BYTES + PG_SCRATCH_BYTES);
+    c.slab = smem + (size_t)stages * PG_STAGE_BYTES + PG_RED_BYTES;
+    c.q_s = reinterpret_cast<bf16*>(smem + (size_t)stages * PG_STAGE_BYTES + PG_RED_BYTES + region_bytes(slab_bytes));
+    c.group = (warp - 1) / PG_BOXES;
+    c.box = (warp - 1) % PG_BOXES;
     c.err = err;
     c.cw = warp - 1;
     c.lane = lane;
     c.ctid = tid - 32;
     c.alive = true;
-    c.red_buffer = 0;
     run_consumers(tape, c, counter);
   }
 }
@@ -799,8 +1022,8 @@ decode_program_kernel(const Phase* __restrict__ tape, unsigned* counter, int* er
 struct LaunchPlan {
   int device = -1;
   int sms = 0;
-  int stages = 0;
-  size_t smem = 0;
+  long long room = 0;        // dynamic shared memory a CTA may have
+  size_t configured = 0;     // what the kernel has been allowed so far
   bool cooperative = true;
 };
 
@@ -818,26 +1041,26 @@ static int launch_plan(LaunchPlan** out) {
     cudaFuncAttributes attributes;
     status = cudaFuncGetAttributes(&attributes, decode_program_kernel);
     if (status != cudaSuccess) CIE_FAIL("decode_program: cudaFuncGetAttributes: %s", cudaGetErrorString(status));
-    const long long fixed = 1024 + PG_SCRATCH_BYTES + PG_Q_BYTES;
-    long long stages = ((long long)optin - (long long)attributes.sharedSizeBytes - fixed) / PG_STAGE_BYTES;
-    if (stages > PG_MAX_STAGES) stages = PG_MAX_STAGES;
-    const char* forced = getenv("CIE_PROGRAM_STAGES");
-    if (forced && atoi(forced) >= 3 && atoi(forced) < stages) stages = atoi(forced);
-    if (stages < 3) CIE_FAIL("decode_program: the device leaves room for %lld stages only", stages);
-    const size_t smem = (size_t)(fixed + stages * PG_STAGE_BYTES);
-    status = cudaFuncSetAttribute(decode_program_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (status != cudaSuccess) CIE_FAIL("decode_program: shared memory %zu: %s", smem, cudaGetErrorString(status));
-    int resident = 0;
-    status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, decode_program_kernel, PG_THREADS, smem);
-    if (status != cudaSuccess || resident < 1) CIE_FAIL("decode_program: the kernel does not fit an SM");
+    plan.room = (long long)optin - (long long)attributes.sharedSizeBytes;
     const char* plain = getenv("CIE_PROGRAM_COOPERATIVE");
     plan.cooperative = !(plain && plain[0] == '0');
     plan.sms = sms;
-    plan.stages = (int)stages;
-    plan.smem = smem;
     plan.device = device;
   }
   *out = &plan;
+  return 0;
+}
+
+// Stages of the ring and bytes of dynamic shared memory for a slab of `slab_bytes`.
+static int ring_for(const LaunchPlan& plan, int slab_bytes, int* stages, size_t* smem) {
+  const long long fixed = 1024 + PG_RED_BYTES + region_bytes(slab_bytes) + PG_Q_BYTES;
+  long long count = (plan.room - fixed) / PG_STAGE_BYTES;
+  if (count > PG_MAX_STAGES) count = PG_MAX_STAGES;
+  const char* forced = getenv("CIE_PROGRAM_STAGES");
+  if (forced && atoi(forced) >= 3 && atoi(forced) < count) count = atoi(forced);
+  if (count < 3) CIE_FAIL("decode_program: a slab of %d bytes leaves room for %lld stages only", slab_bytes, count);
+  *stages = (int)count;
+  *smem = (size_t)(fixed + count * PG_STAGE_BYTES);
   return 0;
 }
 
@@ -852,15 +1075,38 @@ static int page_shift_of(int page_size) {
 using namespace cie;
 
 extern "C" int cie_program_head_dim() { return D; }
+
+#ifdef PROGRAM_PROBE
+extern "C" int cie_program_set_probe(void* buffer, int slots, int cta) {
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_program_probe, &buffer, sizeof(buffer)) != cudaSuccess ||
+      cudaMemcpyToSymbol(g_program_probe_slots, &slots, sizeof(slots)) != cudaSuccess ||
+      cudaMemcpyToSymbol(g_program_probe_cta, &cta, sizeof(cta)) != cudaSuccess ||
+      cudaMemcpyToSymbol(g_program_probe_used, &zero, sizeof(zero)) != cudaSuccess)
+    CIE_FAIL("decode_program: cudaMemcpyToSymbol failed");
+  return 0;
+}
+#endif
+
+// Diagnostics: `buffer` (device memory, 4 * phases * CTAs 64-bit words, zeroed, or null to stop)
+// receives the global timer at the points of trace_mark for the first `phases` phases.
+extern "C" int cie_program_set_trace(void* buffer, int phases) {
+  if (cudaMemcpyToSymbol(g_program_trace, &buffer, sizeof(buffer)) != cudaSuccess ||
+      cudaMemcpyToSymbol(g_program_trace_phases, &phases, sizeof(phases)) != cudaSuccess)
+    CIE_FAIL("decode_program: cudaMemcpyToSymbol failed");
+  return 0;
+}
 extern "C" int cie_program_phase_bytes() { return (int)sizeof(Phase); }
 extern "C" int cie_program_max_key_splits() { return PG_MAX_KEY_SPLITS; }
 
-// CTAs of a launch (one per SM) and stages of the ring on the current device.
-extern "C" int cie_program_geometry(int* ctas, int* stages) {
+// CTAs of a launch (one per SM), and the largest slab of token rows (bytes) that still leaves the
+// ring `least_stages` stages, on the current device.
+extern "C" int cie_program_geometry(int least_stages, int* ctas, int* slab_limit) {
   LaunchPlan* plan = nullptr;
   if (launch_plan(&plan) != 0) return 1;
   *ctas = plan->sms;
-  *stages = plan->stages;
+  const long long left = plan->room - 1024 - PG_RED_BYTES - PG_Q_BYTES - (long long)least_stages * PG_STAGE_BYTES;
+  *slab_limit = left < 0 ? 0 : (int)(left / 1024 * 1024);
   return 0;
 }
 
@@ -875,11 +1121,16 @@ extern "C" int cie_program_geometry(int* ctas, int* stages) {
 static int fill_gemm(Phase* phases, int* count, Phase& p, const void* w, int splits, float* partial) {
   if (p.m <= 0 || p.m > 16) CIE_FAIL("decode_program: a product takes 1 to 16 rows, got %d", p.m);
   if (p.n <= 0 || p.k < 8 || p.k % 8) CIE_FAIL("decode_program: product [%d x %d]: K must be a multiple of 8", p.n, p.k);
-  if (!p.x || !w || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(p.x) & 3) || p.x_stride % 2)
-    CIE_FAIL("decode_program: operands must be present and aligned (weight 16 bytes, rows 4 bytes)");
+  if (!p.x || !w || (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(p.x) & 15) || p.x_stride % 8)
+    CIE_FAIL("decode_program: operands must be present and their rows 16-byte aligned");
   p.row_tiles = (p.n + PG_BN - 1) / PG_BN;
   p.chunks = (p.k + PG_KC - 1) / PG_KC;
   if (splits < 1 || splits > p.chunks) CIE_FAIL("decode_program: %d slices of %d chunks of K", splits, p.chunks);
+  {
+    LaunchPlan* plan = nullptr;
+    if (launch_plan(&plan) != 0) return 1;
+    if (splits > plan->sms) CIE_FAIL("decode_program: %d slices of K on %d CTAs", splits, plan->sms);
+  }
   if (splits > 1 && !partial) CIE_FAIL("decode_program: slices of K need memory for their partial sums");
   if (p.row_sq && p.sq_tiles < 1) CIE_FAIL("decode_program: %d tiles of sums of squares", p.sq_tiles);
   p.splits = splits;
@@ -1013,11 +1264,14 @@ extern "C" int cie_program_free(void* device) {
 }
 
 // Runs a program: `tape` is device memory holding `phases` phases followed by one zeroed phase
-// (the end mark); `counter` one 32-bit word of device memory for the barriers (zeroed here, on the
+// (the end mark); `slab_bytes` the most shared memory any of its products needs for its token rows
+// (8 or 16 rows x the columns of the longest K slice x 2 bytes; the ring gets what is left);
+// `counter` one 32-bit word of device memory for the barriers (zeroed here, on the
 // stream).  One CTA per SM, launched cooperatively so that all of them are resident at one time.
-extern "C" int cie_program_launch(const void* tape, int phases, void* counter, int* err, void* stream) {
+extern "C" int cie_program_launch(const void* tape, int phases, int slab_bytes, void* counter, int* err, void* stream) {
   if (phases <= 0) return 0;
   if (!tape || !counter || !err) CIE_FAIL("decode_program: null argument");
+  if (slab_bytes < 0) CIE_FAIL("decode_program: slab of %d bytes", slab_bytes);
   if (reinterpret_cast<uintptr_t>(tape) & 127) CIE_FAIL("decode_program: the phases must be 128-byte aligned");
   LaunchPlan* plan = nullptr;
   if (launch_plan(&plan) != 0) return 1;
@@ -1026,7 +1280,15 @@ extern "C" int cie_program_launch(const void* tape, int phases, void* counter, i
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(plan->sms);
   config.blockDim = dim3(PG_THREADS);
-  config.dynamicSmemBytes = plan->smem;
+  int stages = 0;
+  size_t smem = 0;
+  if (ring_for(*plan, slab_bytes, &stages, &smem) != 0) return 1;
+  if (smem > plan->configured) {
+    status = cudaFuncSetAttribute(decode_program_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (status != cudaSuccess) CIE_FAIL("decode_program: shared memory %zu: %s", smem, cudaGetErrorString(status));
+    plan->configured = smem;
+  }
+  config.dynamicSmemBytes = smem;
   config.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attributes[1];
   attributes[0].id = cudaLaunchAttributeCooperative;
@@ -1034,7 +1296,7 @@ extern "C" int cie_program_launch(const void* tape, int phases, void* counter, i
   config.attrs = attributes;
   config.numAttrs = plan->cooperative ? 1 : 0;
   status = cudaLaunchKernelEx(&config, decode_program_kernel, static_cast<const Phase*>(tape),
-                              static_cast<unsigned*>(counter), err, plan->stages);
+                              static_cast<unsigned*>(counter), err, stages, slab_bytes);
   if (status != cudaSuccess) CIE_FAIL("decode_program: launch failed: %s", cudaGetErrorString(status));
   return 0;
 }

@@ -291,7 +291,8 @@ class Ops:
         row_sq, tiles, eps = None, 0, 0.0
         if isinstance(x, NormedInput):
             row_sq, tiles, eps, x = x.accumulated.sq, x.accumulated.tiles, x.eps, x.accumulated.scaled
-        if self.recording and mode != 2 and weight.data_ptr() % 16 == 0 and (mode != 3 or n % 32 == 0):
+        if (self.recording and mode != 2 and weight.data_ptr() % 16 == 0 and (mode != 3 or n % 32 == 0)
+                and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0):
             self.program.gemm(x, row_sq, tiles, eps, weight, bias, out, residual, sq, scaled, next_gain,
                               m, n, k, mode, tag)
             return
@@ -545,7 +546,7 @@ class Ops:
         if isinstance(x, NormedInput):
             row_sq, row_tiles, eps, x = x.accumulated.sq, x.accumulated.tiles, x.eps, x.accumulated.scaled
         table = ctx.block_tables[kv.group]
-        if self.recording and weight.data_ptr() % 16 == 0:
+        if self.recording and weight.data_ptr() % 16 == 0 and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0:
             self.program.rope(x, row_sq, row_tiles, eps, weight, bias, q_buffer, ctx.positions,
                               ctx.request_of_token, table, kv.num_pages, kv.k, kv.v, position.inv_freq, m,
                               q_heads, kv_heads, head_dim, position.rotary_dim, kv.page_size, write_cache, k)

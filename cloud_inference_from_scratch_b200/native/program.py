@@ -24,6 +24,7 @@ from .build import load_library
 HEAD_DIMS = (64, 128)      # head sizes the kernel is built for
 MAX_ROWS = 16              # token rows of a recorded step
 MAX_SPLITS = 16            # most slices of K a product is cut into
+LEAST_STAGES = 6           # the ring keeps at least this many 16 KB stages, whatever the token rows need
 KEPT_TAPES = 32            # device copies kept for steps outside CUDA graphs
 MIN_KEYS_PER_CTA = int(os.environ.get("CIE_PROGRAM_MIN_KEYS", "256"))
 
@@ -32,15 +33,20 @@ def enabled() -> bool:
     return os.environ.get("CIE_PROGRAM", "1") != "0"
 
 
-def product_splits(tiles: int, chunks: int, ctas: int) -> int:
+def product_splits(tiles: int, chunks: int, ctas: int, most_chunks: int = 1 << 30) -> int:
     """Slices of K for a product of ``tiles`` 32-row weight tiles and ``chunks`` 256-column chunks on
-    ``ctas`` CTAs.  One slice (every tile finished by the CTA that streams it, no finish phase)
-    unless cutting K shortens the longest CTA's share by more than the finish phase and its barrier
-    cost (about eight stages of streaming, and a little more with every slice it has to add up)."""
-    whole = -(-tiles // ctas) * chunks
-    best, best_cost = 1, float(whole)
-    for splits in range(2, min(chunks, MAX_SPLITS) + 1):
-        cost = -(-tiles * splits // ctas) * -(-chunks // splits) + 8 + splits / 4
+    ``ctas`` CTAs.  A CTA works on one slice (CTA c on slice c % slices) and shares its tiles with the
+    other CTAs of that slice.  One slice (every tile finished by the CTA that streams it, no finish
+    phase) unless cutting K shortens the longest CTA's share by more than the finish phase and its
+    barrier cost (about eight stages of streaming, and a little more with every slice it has to add
+    up), or a slice may have ``most_chunks`` chunks at most (its token rows must fit shared memory)."""
+    def stages(splits: int) -> int:
+        return -(-tiles // (ctas // splits)) * -(-chunks // splits)
+
+    least = max(1, -(-chunks // most_chunks))
+    best, best_cost = least, float(stages(least)) + (0 if least == 1 else 8 + least / 4)
+    for splits in range(max(2, least), min(chunks, MAX_SPLITS, ctas) + 1):
+        cost = stages(splits) + 8 + splits / 4
         if cost < best_cost:
             best, best_cost = splits, cost
     return best
@@ -60,13 +66,13 @@ class _Library:
             [v, v, v, i, v, i, f, v, v, v, v, i, v, v, v, i, i, v, v, v, i, i, i, i, i, i, i, i, i])
         self.attention = lib.function(
             "cie_program_attention", [v, v, v, i, v, i, v, v, v, i, i, v, i, i, i, i, i, i, v, f, i])
-        self.launch = lib.function("cie_program_launch", [v, i, v, v, v])
+        self.launch = lib.function("cie_program_launch", [v, i, i, v, v, v])
         self.upload = lib.function("cie_program_upload", [v, ll, v])
         self.free = lib.function("cie_program_free", [v])
-        geometry = lib.function("cie_program_geometry", [v, v])
-        ctas, stages = c_int(0), c_int(0)
-        geometry(ctypes.byref(ctas), ctypes.byref(stages))
-        self.ctas, self.stages = ctas.value, stages.value
+        geometry = lib.function("cie_program_geometry", [i, v, v])
+        ctas, slab_limit = c_int(0), c_int(0)
+        geometry(LEAST_STAGES, ctypes.byref(ctas), ctypes.byref(slab_limit))
+        self.ctas, self.slab_limit = ctas.value, slab_limit.value
 
 
 def _ptr(tensor: Any) -> int | None:
@@ -130,19 +136,30 @@ class DecodeProgram:
                            q_heads, kv_heads, page_size, scale, window))
 
     # ------------------------------------------------------------------ running
-    def _encode(self, lib: _Library) -> tuple[bytes, int]:
+    def _encode(self, lib: _Library) -> tuple[bytes, int, int]:
         ops = self.ops
         size = lib.phase_bytes
         room = ctypes.create_string_buffer(2 * size)
         count = c_int(0)
         tape = bytearray()
         phases = 0
+        slab = 0
+
+        def cut(m: int, n: int, k: int) -> int:
+            """Slices of K for a product, and the shared memory its token rows then need."""
+            nonlocal slab
+            padded = 8 if m <= 8 else 16
+            chunks = -(-k // 256)
+            splits = product_splits(-(-n // 32), chunks, lib.ctas, max(1, lib.slab_limit // (padded * 512)))
+            slab = max(slab, padded * 512 * -(-chunks // splits))
+            return splits
+
         for call in self.calls:
             kind = call[0]
             if kind == "gemm":
                 (_, x, row_sq, sq_tiles, eps, weight, bias, out, residual, sq, scaled, next_gain, m, n, k, mode,
                  tag) = call
-                splits = product_splits(-(-n // 32), -(-k // 256), lib.ctas)
+                splits = cut(m, n, k)
                 partial = None
                 if splits > 1:
                     partial = ops.scratch("program.partial." + tag, splits * m * n, reserve=MAX_SPLITS * MAX_ROWS * n)
@@ -153,7 +170,7 @@ class DecodeProgram:
                 (_, x, row_sq, sq_tiles, eps, weight, bias, q_out, positions, request_of_token, table, num_pages,
                  k_pool, v_pool, inv_freq, m, q_heads, kv_heads, dim, rot, page_size, write_cache, k) = call
                 n = (q_heads + 2 * kv_heads) * dim
-                splits = product_splits(-(-n // 32), -(-k // 256), lib.ctas)
+                splits = cut(m, n, k)
                 partial = None
                 if splits > 1:
                     partial = ops.scratch("program.partial.qkv", splits * m * n, reserve=MAX_SPLITS * MAX_ROWS * n)
@@ -181,7 +198,7 @@ class DecodeProgram:
             tape += room.raw[: count.value * size]
             phases += count.value
         tape += bytes(size)   # the end mark: a phase of kind 0
-        return bytes(tape), phases
+        return bytes(tape), phases, slab
 
     def flush(self) -> None:
         """Runs what was recorded since the last flush (nothing, if nothing was)."""
@@ -189,7 +206,7 @@ class DecodeProgram:
             return
         ops = self.ops
         lib = self.library(self.head_dim or HEAD_DIMS[-1])
-        tape, phases = self._encode(lib)
+        tape, phases, slab = self._encode(lib)
         self.calls = []
         self.head_dim = None
         capturing = ops.torch.cuda.is_current_stream_capturing()
@@ -206,7 +223,7 @@ class DecodeProgram:
         ops.launches += 1
         self.programs_run += 1
         self.phases_run += phases
-        lib.launch(held[0], phases, self.counter.data_ptr(), ops.error_word.data_ptr(), ops.stream)
+        lib.launch(held[0], phases, slab, self.counter.data_ptr(), ops.error_word.data_ptr(), ops.stream)
 
     def _trim(self, lib: _Library) -> None:
         """Forgets the oldest device copies that no CUDA graph holds."""
