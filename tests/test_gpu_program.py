@@ -302,3 +302,33 @@ def test_two_layers_in_one_launch(item):
         torch.testing.assert_close(vb.float(), va.float(), rtol=2e-2, atol=2e-2)
     again, _ = run(True)
     assert torch.equal(again, together), "the same program twice gives the same bits"
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_generation_with_recorded_decode_steps(sharp_models, name, monkeypatch):
+    """The whole path with the switch on: decode steps of the scheduler's runner (CUDA graphs, padded
+    buckets, steps launched ahead and dropped, a request joining, a small pool) run as programs, and
+    every sampled row's logits are the plain model's."""
+    from helpers import check_trace_rows
+    from test_gpu_runner import _drive
+
+    monkeypatch.setenv("CIE_PROGRAM", "1")
+    folder = sharp_models.get(name, "bfloat16")
+    programs = []
+    from cloud_inference_from_scratch_b200.native import program as program_module
+
+    launched = program_module.DecodeProgram.flush
+
+    def counting(self):
+        before = self.programs_run
+        launched(self)
+        programs.append(self.programs_run - before)
+
+    monkeypatch.setattr(program_module.DecodeProgram, "flush", counting)
+    requests, trace, counters, most_pages = _drive(folder, name, "bfloat16", blocks=64)
+    check_trace_rows(folder, requests, trace, "bfloat16", f"{name} runner")
+    assert sum(programs) > 0, "no decode step was recorded"
+    assert counters["replays"] > 0 and counters["adopted"] > 0
+    requests, trace, counters, _ = _drive(folder, name, "bfloat16", blocks=most_pages - 2)
+    check_trace_rows(folder, requests, trace, "bfloat16", f"{name} runner")
+    assert counters["preempted"] >= 1
