@@ -157,11 +157,26 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
   }
 }
 
+// token_ids[i] = sampled[min(i, real - 1)]: the step that follows a decode step takes its token ids
+// from what that step sampled, on the device; rows that only pad the batch repeat the last real one.
+__global__ void feed_tokens_kernel(const int* __restrict__ sampled, int* __restrict__ token_ids, int rows, int real) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows) token_ids[i] = sampled[min(i, real - 1)];
+}
+
 }  // namespace cie
 
 using namespace cie;
 
 extern "C" int cie_sample_slices() { return kSlices; }
+
+extern "C" int cie_feed_tokens(const int* sampled, int* token_ids, int rows, int real, void* stream) {
+  if (rows <= 0) return 0;
+  if (!sampled || !token_ids || real < 1 || real > rows) CIE_FAIL("feed_tokens: %d real rows of %d", real, rows);
+  feed_tokens_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sampled, token_ids, rows, real);
+  CIE_CHECK_LAUNCH("feed_tokens");
+  return 0;
+}
 
 // temperature may be null (all rows greedy); keys may be null only then.  scratch: room for
 // rows * cie_sample_slices() floats and as many ints, or null (then one CTA a row finds the

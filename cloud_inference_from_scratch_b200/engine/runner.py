@@ -37,8 +37,6 @@ class _DecodeGraph:
         self.result_host = torch.zeros(1 + bucket, dtype=torch.int32, pin_memory=True)
         self.token_ids = ctx.token_ids          # device view: where the step reads its token ids
         self.event = torch.cuda.Event()
-        self.feed_index = torch.zeros(bucket, dtype=torch.int64, device=result_dev.device)
-        self.feed_real = -1
         self.logits: Any = None                 # the float32 logits buffer the captured step writes
 
 
@@ -283,12 +281,8 @@ class EngineRunner:
         else:
             step.upload(host, cached.meta)
             if feed is not None:
-                if cached.feed_real != real:
-                    index = np.minimum(np.arange(bucket), real - 1).astype(np.int64)
-                    cached.feed_index.copy_(torch.from_numpy(index))
-                    cached.feed_real = real
-                # row i reads the token that row i of the step before it is sampling
-                torch.index_select(feed.result_dev[1:], 0, cached.feed_index, out=cached.token_ids)
+                # row i reads the token that row i of the step before it is sampling (pad rows the last one's)
+                self.ops.feed_tokens(feed.result_dev[1:], cached.token_ids, real)
         cached.graph.replay()
         self.cuda_graph_replays += 1
         step.steps_run += 1

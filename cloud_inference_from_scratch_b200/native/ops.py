@@ -590,16 +590,28 @@ class Ops:
         self._silu_mul(_ptr(gate_up), _ptr(out), tokens, inter, inter if block is None else block,
                        self._code_of(out), self.stream)
 
-    def sample(self, logits: Any, temperature: Any, keys: Any, out: Any) -> None:
-        """logits float32 [R, V]; temperature float32 [R] or None (greedy); keys int64 [R]."""
-        self._flush()
-        rows, vocab = logits.shape
+    def _load_sampling(self) -> None:
         if self._sample is None:
             v, i = c_void_p, c_int
             lib = _Lib(load_library("sampling.cu"))
             self._sample = lib.function("cie_sample", [v, i, i, v, v, v, v, v])
+            self._feed_tokens = lib.function("cie_feed_tokens", [v, v, i, i, v])
             self._sample_slices = int(lib.handle.cie_sample_slices())
+
+    def sample(self, logits: Any, temperature: Any, keys: Any, out: Any) -> None:
+        """logits float32 [R, V]; temperature float32 [R] or None (greedy); keys int64 [R]."""
+        self._flush()
+        rows, vocab = logits.shape
+        self._load_sampling()
         # the row maxima are searched by several CTAs a row first (two launches)
         scratch = self.scratch("sample.maxima", 2 * rows * self._sample_slices, reserve=2 * 1024 * self._sample_slices)
         self.launches += 2 if vocab >= 4096 else 1
         self._sample(_ptr(logits), rows, vocab, _ptr(temperature), _ptr(keys), _ptr(out), _ptr(scratch), self.stream)
+
+    def feed_tokens(self, sampled: Any, token_ids: Any, real: int) -> None:
+        """token_ids[i] = sampled[min(i, real - 1)] (int32, on the device): the token ids of a decode step
+        that is launched before the step before it has been read back."""
+        self._flush()
+        self._load_sampling()
+        self.launches += 1
+        self._feed_tokens(_ptr(sampled), _ptr(token_ids), token_ids.shape[0], real, self.stream)
