@@ -88,10 +88,10 @@ class TensorAttention:
         # where clusters of one request leave their shares (at most one CTA an SM takes part), and
         # the tickets that tell the last one; the kernel leaves the tickets at zero
         torch = ops.torch
-        self._chunk_shares = torch.zeros(SM_COUNT * 16 * (head_dim + 2), dtype=torch.float32, device=ops.device)
-        self._chunk_tickets = torch.zeros(SM_COUNT, dtype=torch.int32, device=ops.device)
-        self._decode_split = None
         self.sm_count = ops.torch.cuda.get_device_properties(ops.device).multi_processor_count
+        self._chunk_shares = torch.zeros(self.sm_count * 16 * (head_dim + 2), dtype=torch.float32, device=ops.device)
+        self._chunk_tickets = torch.zeros(self.sm_count, dtype=torch.int32, device=ops.device)
+        self._decode_split = None
         if head_dim % 64 == 0 and os.environ.get("CIE_DECODE_SPLIT", "1") != "0":
             self._decode_split = lib.function(
                 "cie_attention_decode_split",
@@ -133,7 +133,7 @@ class TensorAttention:
         room = self._cluster_room.get(splits)
         if room is None:
             clusters = int(self._decode_clusters(splits, self.use_tma))
-            room = CLUSTERED_CTAS if clusters < 2 else min(SM_COUNT, (clusters - 1) * splits)
+            room = CLUSTERED_CTAS if clusters < 2 else min(self.sm_count, (clusters - 1) * splits)
             self._cluster_room[splits] = room
         return room
 
@@ -185,15 +185,15 @@ class TensorAttention:
         return splits, stages
 
     @staticmethod
-    def splits_for(requests: int, kv_heads: int, group: int, max_keys: int) -> int:
+    def splits_for(requests: int, kv_heads: int, group: int, max_keys: int, sm_count: int = SM_COUNT) -> int:
         """CTAs (of one cluster) that share a request's keys: enough to put work on every SM,
         at least MIN_KEYS_PER_SPLIT keys each, a power of two up to 8."""
         ctas = requests * kv_heads * -(-group // 16)
         limit = max(1, max_keys // MIN_KEYS_PER_SPLIT)
         splits = 1
-        while splits < 8 and ctas * splits * 2 <= SM_COUNT and splits * 2 <= limit:
+        while splits < 8 and ctas * splits * 2 <= sm_count and splits * 2 <= limit:
             splits *= 2
-        if splits == 8 and ctas * splits > SM_COUNT // 2:
+        if splits == 8 and ctas * splits > sm_count // 2:
             splits = 4   # big clusters cost more than they bring once half the SMs have work
         return splits
 
@@ -249,7 +249,7 @@ class TensorAttention:
                                self._split_tickets.data_ptr(), scale, window, ops.error_word.data_ptr(),
                                ops.stream)
             return
-        splits = self.splits_for(requests, kv_heads, group, max_keys)
+        splits = self.splits_for(requests, kv_heads, group, max_keys, self.sm_count)
         chunks = self.chunks_for(requests, kv_heads, group, max_keys, splits, self.cluster_room(splits))
         self._decode(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                      kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
