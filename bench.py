@@ -195,6 +195,17 @@ def _timed_steps(scheduler, steps: int) -> tuple[float, float]:
     return start.elapsed_time(stop), time.perf_counter() - wall
 
 
+def _until_decoding(scheduler, handles) -> None:
+    """Steps until every request has its first token; a request that ended instead (a failed step)
+    ends the benchmark with its reason rather than a loop that never ends."""
+    while any(h.request.generated_count < 1 for h in handles):
+        ended = [h.request for h in handles if h.request.is_terminal and h.request.generated_count < 1]
+        if ended:
+            raise RuntimeError(f"request {ended[0].request_id} ended before its first token: "
+                               f"{ended[0].finish_reason} {ended[0].error_detail}")
+        scheduler.step()
+
+
 def time_decode(engine, cfg: dict, batch: int, steps: int, warmup: int, sample_clocks: bool) -> dict:
     """Prefills ``batch`` prompts through the public API, then times decode iterations: exactly
     ``steps`` of them, and after those as many more as make the region at least MIN_TIMED_MS long."""
@@ -206,8 +217,7 @@ def time_decode(engine, cfg: dict, batch: int, steps: int, warmup: int, sample_c
     prompts = random_prompts(batch, PROMPT_TOKENS, cfg["vocab_size"], seed=batch)
     gen = GenerationConfig(max_output_tokens=CONTEXT - PROMPT_TOKENS, eos_token_id=None)
     handles = [engine.submit(prompt, gen) for prompt in prompts]
-    while any(h.request.generated_count < 1 for h in handles):
-        scheduler.step()
+    _until_decoding(scheduler, handles)
     runner = engine.runner
     ops = engine.core.runtime.ops
     for _ in range(warmup):
@@ -300,8 +310,7 @@ def run_mixed_7b(layers: int | None = None, decoding: int = 32, decode_context: 
     scheduler = engine.scheduler
     residents = [engine.submit(p, GenerationConfig(max_output_tokens=room, eos_token_id=None))
                  for p in random_prompts(decoding, decode_context, cfg["vocab_size"], seed=7)]
-    while any(h.request.generated_count < 1 for h in residents):
-        scheduler.step()
+    _until_decoding(scheduler, residents)
     times: list[float] = []
     contexts: list[int] = []
     for index, tokens in enumerate(random_prompts(prompts, prompt, cfg["vocab_size"], seed=70)):

@@ -36,6 +36,9 @@ MIN_KEYS_PER_CHUNKED_CTA = int(os.environ.get("CIE_DECODE_CHUNK_KEYS", "1024"))
 # clusters of 8 (a 16th waits for a second round, which costs more than the cut brings)
 CLUSTERED_CTAS = 112
 MAX_CHUNKS = 16                  # must match DECODE_MAX_CHUNKS of the kernel
+# the split decode kernel: from this many keys a CTA on, the CTAs of a unit form no cluster (8 requests of
+# 32,000 keys: 3.42 ms a step with 18 CTAs a unit and tickets against 3.85 with two clusters of 8)
+LONG_RANGE_KEYS = 1024
 
 
 def supports(head_dim: int) -> bool:
@@ -162,8 +165,9 @@ class TensorAttention:
         head, 16 heads) triples; ``rings``: ring depth -> CTAs an SM holds with it.
 
         Few units (half the SMs or fewer): one CTA an SM with the deepest ring, so that a CTA can ask
-        for its whole range of keys at once, even before the kernel before it has finished.  More
-        units: two CTAs an SM with the deepest ring that allows it (a CTA is four warps, and four
+        for its whole range of keys at once, even before the kernel before it has finished; unless
+        two CTAs an SM let a unit have more CTAs that each still keep ``min_keys`` keys (long
+        contexts).  More units: two CTAs an SM with the deepest ring that allows it (a CTA is four warps, and four
         warps alone do not keep an SM's tensor pipe and copy engine busy), every CTA of the launch
         resident at one time.  Every CTA keeps at least ``min_keys`` keys of the longest context the
         tables hold; a launch stays within ``limit`` CTAs (the scratch is sized for that) and a unit
@@ -171,11 +175,17 @@ class TensorAttention:
         (9, 6) against 10.4 with (8, 3); 64 requests 26.8 us with (2, 3) against 37 with (1, 6)."""
         depths = sorted(rings, reverse=True)
         paired = [depth for depth in depths if rings[depth] >= 2]
-        if units * 2 <= sm_count or not paired:
+        by_keys = max(1, max_keys // min_keys)
+        alone = max(1, min(by_keys, sm_count // max(1, units), most))          # CTAs a unit gets at one CTA an SM
+        doubled = max(1, min(by_keys, 2 * sm_count // max(1, units), most))    # ... at two
+        if units * 2 <= sm_count and paired and doubled > alone:
+            # long contexts: more CTAs a unit, each still with its keys, stream more than a deep ring
+            # does (8 requests of 32,000 keys: 3.42 ms a step with (18, 3) against 4.25 with (9, 6))
+            stages, slots = paired[0], 2 * sm_count
+        elif units * 2 <= sm_count or not paired:
             stages, slots = depths[0], sm_count
         else:
             stages, slots = paired[0], 2 * sm_count
-        by_keys = max(1, max_keys // min_keys)
         splits = max(1, min(by_keys, slots // max(1, units), most))
         while splits > 1 and units * splits > limit:
             splits -= 1
@@ -227,6 +237,8 @@ class TensorAttention:
             ctas, stages = self.split_plan(units, max_keys, self.sm_count, self.split_rings(1, group), self.split_cta_limit,
                                            self.split_max, self.split_tile, MIN_KEYS_PER_SPLIT_CTA)
             cluster = self.cluster_for(ctas)
+            if max_keys // max(1, ctas) >= LONG_RANGE_KEYS:
+                cluster = 1   # ranges this long hide the hand-over through global memory; clusters only bind the placement
             if cluster > 1:
                 # Neighbouring CTAs of a unit in one cluster: whole clusters, and the deepest ring with
                 # which an SM still holds two CTAs.  (A cluster starts only when all its CTAs find room in

@@ -62,7 +62,10 @@ def test_split_decode_plan_fills_the_device_and_keeps_every_cta_keys(requests, k
 
 def test_split_decode_plan_of_the_measured_batches():
     rings = {1: 3, 2: 3, 3: 2, 4: 1, 5: 1, 6: 1}
-    assert TensorAttention.split_plan(16, 4096, 148, rings, 592, 64) == (9, 6)     # batch 8, two kv heads
+    assert TensorAttention.split_plan(16, 4096, 148, rings, 592, 64) == (16, 3)    # batch 8, two kv heads: two clusters of 8
+    assert TensorAttention.split_plan(16, 2048, 148, rings, 592, 64) == (8, 4)     # ... tables that end at 2,048 keys
+    assert TensorAttention.split_plan(16, 32768, 148, rings, 592, 64) == (18, 3)   # ... and long contexts
+    assert TensorAttention.split_plan(64, 4096, 148, rings, 592, 64) == (4, 3)     # batch 32
     assert TensorAttention.split_plan(128, 4096, 148, rings, 592, 64) == (2, 3)    # batch 64
     assert TensorAttention.split_plan(2, 4096, 148, rings, 592, 64) == (16, 4)     # batch 1
     assert TensorAttention.split_plan(2, 32768, 148, rings, 592, 64) == (64, 6)    # one long request
