@@ -46,6 +46,23 @@ constexpr int WROW = BK + 8;
 // otherwise cost an SM one resident CTA (and a wide product a second wave).
 template <int MT>
 constexpr int stages_for() { return MT == 1 ? 4 : 3; }
+// A CTA's tile is divided among more warps than its 16-row halves: the small products of a step are
+// chains of dependent instructions of a few warps an SM, so the work of ONE warp, not the weight
+// stream, sets their time (measured on a B200 at 13 cycles an instruction and 7 % of the issue slots
+// in use).  A warp takes 16 weight rows, one 8-token tile and every second pair of k-steps of a
+// tile: four warps a CTA up to 8 tokens, eight for 9 to 16; the shares of K meet in shared memory
+// before the epilogue, whose rows are then divided among all warps too.  (Four shares of K at up to
+// 8 tokens were slower again: 1.82 ms a step against 1.77.)
+template <int MT>
+constexpr int token_split_for() { return MT; }
+#ifndef STREAM_K_SPLIT_1
+#define STREAM_K_SPLIT_1 2
+#endif
+#ifndef STREAM_K_SPLIT_2
+#define STREAM_K_SPLIT_2 2
+#endif
+template <int MT>
+constexpr int k_split_for() { return MT == 1 ? STREAM_K_SPLIT_1 : STREAM_K_SPLIT_2; }
 constexpr int KSTEPS = BK / 16;
 
 using bw::smem_u32;
@@ -166,9 +183,12 @@ template <int BN, bool TMA>
 constexpr int w_stage_elems() { return TMA ? BN * BK : BN * WROW; }
 
 template <int MT, int BN, bool TMA>
-__global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map,
-                                                              const StreamArgs a) {
-  constexpr int THREADS = BN * 2;   // one warp per 16 weight rows
+__global__ void __launch_bounds__(BN * 2 * token_split_for<MT>() * k_split_for<MT>())
+gemm_stream_kernel(const __grid_constant__ CUtensorMap w_map, const StreamArgs a) {
+  constexpr int TS = token_split_for<MT>(), KS = k_split_for<MT>();
+  constexpr int ROW_WARPS = BN / 16;
+  constexpr int THREADS = BN * 2 * TS * KS;   // a warp per 16 weight rows, per token tile(s), per share of the k-steps
+  constexpr int MTW = MT / TS;      // 8-token tiles of a warp
   constexpr int MP = MT * 8;        // padded token count
   constexpr int WSTAGE = w_stage_elems<BN, TMA>();
   constexpr int XSTAGE = MP * WROW * 2;
@@ -185,6 +205,8 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
   __shared__ float inbox_s[MP * 32];
   __shared__ __align__(8) uint64_t inbox_bar;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // which 16 weight rows, which token tiles and which k-steps of a tile this warp takes
+  const int warp_row = warp % ROW_WARPS, warp_tok = (warp / ROW_WARPS) % TS, warp_k = warp / (ROW_WARPS * TS);
   const int n0 = blockIdx.x * BN;
   const int k_begin = blockIdx.y * a.k_per_split;
   const int k_end = min(a.k, k_begin + a.k_per_split);
@@ -283,9 +305,9 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
     else row_rstd<MP, THREADS, 8>(a, rstd_s, warp, lane);
   }
 
-  float acc[MT][4];
+  float acc[MTW][4];
 #pragma unroll
-  for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < MTW; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
   bool alive = true;
   for (int it = 0; it < steps; ++it) {
@@ -300,9 +322,10 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
     cp_async_commit();
     const bf16* ws = w_s + (it % STAGES) * WSTAGE;
     const unsigned char* xt_raw = x_s + (it % STAGES) * XSTAGE;
-    const int wr = warp * 16 + (lane & 15);
+    const int wr = warp_row * 16 + (lane & 15);
 #pragma unroll
-    for (int kp = 0; kp < KSTEPS / 2; ++kp) {
+    for (int kq = 0; kq < KSTEPS / 2 / KS; ++kq) {
+      const int kp = kq * KS + warp_k;
       uint32_t a0[4], a1[4];
       if constexpr (TMA) {
         // 16-byte piece c of row wr: box c / 8, position (c % 8) ^ (wr % 8) in the 128-byte row
@@ -314,11 +337,11 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
         ldsm_x4(a1, ws + wr * WROW + (2 * kp + 1) * 16 + (lane >> 4) * 8);
       }
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        uint32_t b[4];  // tokens mt*8.., k = kp*32 + {0, 8, 16, 24}
+      for (int mt = 0; mt < MTW; ++mt) {
+        uint32_t b[4];  // tokens (warp_tok * MTW + mt) * 8 .., k = kp*32 + {0, 8, 16, 24}
         {
           const bf16* xt = reinterpret_cast<const bf16*>(xt_raw);
-          ldsm_x4(b, xt + (mt * 8 + (lane & 7)) * WROW + kp * 32 + (lane >> 3) * 8);
+          ldsm_x4(b, xt + ((warp_tok * MTW + mt) * 8 + (lane & 7)) * WROW + kp * 32 + (lane >> 3) * 8);
         }
         mma_bf16(acc[mt], a0, b[0], b[1]);
         mma_bf16(acc[mt], a1, b[2], b[3]);
@@ -338,14 +361,46 @@ __global__ void __launch_bounds__(BN * 2) gemm_stream_kernel(const __grid_consta
   // ---- epilogue through shared memory: out_s[token][weight row]
   float* out_s = reinterpret_cast<float*>(smem_base);  // [MP][BN + 1]
   const int g = lane >> 2, t4 = lane & 3;
+  if constexpr (KS > 1) {
+    // the warps with the other k-steps put their sums down first (a copy of the staging tile each);
+    // the first ones add them to their own, in the order of the shares
+    if (warp_k > 0) {
+      float* mine = out_s + warp_k * (MP * (BN + 1));
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
-    const int m0 = mt * 8 + 2 * t4, r0 = warp * 16 + g;
-    const float s0 = a.row_sq ? rstd_s[m0] : 1.f, s1 = a.row_sq ? rstd_s[m0 + 1] : 1.f;
-    out_s[m0 * (BN + 1) + r0] = acc[mt][0] * s0;
-    out_s[(m0 + 1) * (BN + 1) + r0] = acc[mt][1] * s1;
-    out_s[m0 * (BN + 1) + r0 + 8] = acc[mt][2] * s0;
-    out_s[(m0 + 1) * (BN + 1) + r0 + 8] = acc[mt][3] * s1;
+      for (int mt = 0; mt < MTW; ++mt) {
+        const int m0 = (warp_tok * MTW + mt) * 8 + 2 * t4, r0 = warp_row * 16 + g;
+        mine[m0 * (BN + 1) + r0] = acc[mt][0];
+        mine[(m0 + 1) * (BN + 1) + r0] = acc[mt][1];
+        mine[m0 * (BN + 1) + r0 + 8] = acc[mt][2];
+        mine[(m0 + 1) * (BN + 1) + r0 + 8] = acc[mt][3];
+      }
+    }
+    __syncthreads();
+    if (warp_k == 0) {
+#pragma unroll
+      for (int share = 1; share < KS; ++share) {
+        const float* theirs = out_s + share * (MP * (BN + 1));
+#pragma unroll
+        for (int mt = 0; mt < MTW; ++mt) {
+          const int m0 = (warp_tok * MTW + mt) * 8 + 2 * t4, r0 = warp_row * 16 + g;
+          acc[mt][0] += theirs[m0 * (BN + 1) + r0];
+          acc[mt][1] += theirs[(m0 + 1) * (BN + 1) + r0];
+          acc[mt][2] += theirs[m0 * (BN + 1) + r0 + 8];
+          acc[mt][3] += theirs[(m0 + 1) * (BN + 1) + r0 + 8];
+        }
+      }
+    }
+  }
+  if (warp_k == 0) {
+#pragma unroll
+    for (int mt = 0; mt < MTW; ++mt) {
+      const int m0 = (warp_tok * MTW + mt) * 8 + 2 * t4, r0 = warp_row * 16 + g;
+      const float s0 = a.row_sq ? rstd_s[m0] : 1.f, s1 = a.row_sq ? rstd_s[m0 + 1] : 1.f;
+      out_s[m0 * (BN + 1) + r0] = acc[mt][0] * s0;
+      out_s[(m0 + 1) * (BN + 1) + r0] = acc[mt][1] * s1;
+      out_s[m0 * (BN + 1) + r0 + 8] = acc[mt][2] * s0;
+      out_s[(m0 + 1) * (BN + 1) + r0 + 8] = acc[mt][3] * s1;
+    }
   }
   __syncthreads();
   const int rows_per_owner = (MP + size - 1) / size;
@@ -514,7 +569,7 @@ template <int MT, int BN, bool TMA>
 static int launch_variant(const CUtensorMap& w_map, const StreamArgs& a, int splits, cudaStream_t stream) {
   constexpr int MP = MT * 8;
   constexpr size_t pipeline = (size_t)stages_for<MT>() * (w_stage_elems<BN, TMA>() + MP * WROW) * sizeof(bf16);
-  constexpr size_t staging = (size_t)MP * (BN + 1) * sizeof(float);
+  constexpr size_t staging = (size_t)k_split_for<MT>() * MP * (BN + 1) * sizeof(float);
   constexpr size_t smem = (pipeline > staging ? pipeline : staging) + (TMA ? 1024 : 0);
   static bool configured = false;
   if (!configured) {
@@ -525,7 +580,7 @@ static int launch_variant(const CUtensorMap& w_map, const StreamArgs& a, int spl
   }
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((a.n + BN - 1) / BN, splits);
-  config.blockDim = dim3(BN * 2);
+  config.blockDim = dim3(BN * 2 * token_split_for<MT>() * k_split_for<MT>());
   config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attributes[2];
