@@ -31,7 +31,7 @@ MIN_KEYS_PER_CTA = int(os.environ.get("CIE_PROGRAM_MIN_KEYS", "256"))
 
 def enabled() -> bool:
     """Off unless CIE_PROGRAM=1: measured on a B200 the one-kernel step is slower than the separate
-    kernels with their programmatic overlap (3.0 ms against 1.85 ms a step at batch 8): seven
+    kernels with their programmatic overlap (2.8 ms against 1.8 ms a step at batch 8): seven
     barriers in global memory a layer at 1.5 us each, and phases of a few microseconds that one CTA
     per SM runs as chains of dependent loads."""
     return os.environ.get("CIE_PROGRAM", "0") == "1"
