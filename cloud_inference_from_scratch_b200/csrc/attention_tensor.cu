@@ -613,7 +613,7 @@ decode_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__
 
 // ------------------------------------------------------------------------------------ decode, split over CTAs
 // The decode kernel for pools that TMA can read (pages of a power of two >= 16 tokens, head size a
-// multiple of 64).  A request's keys are cut into `splits` ranges, one CTA each, with no cluster:
+// multiple of 64).  A request's keys are cut into `splits` ranges, one CTA each:
 // a CTA is 4 warps and a ring of SPLIT_STAGES stages of 64 keys (K and V of a stage arrive by
 // one mbarrier; 16 KB of keys and 16 KB of values at head size 128), so two or three CTAs fit an
 // SM and every SM has work at small batches.  Warp w multiplies the w-th 16 keys of a stage.  A
@@ -1278,8 +1278,39 @@ static int split_ctas_per_sm(int stages, int cluster, int rows) {
 
 // rows: head rows of a unit (query heads per kv head, at most 16)
 extern "C" int cie_attention_decode_split_ctas_per_sm(int stages, int cluster, int rows) {
-  if (D % 64 || stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES || cluster < 1 || cluster > 8 || rows < 1 || rows > 16) return 0;
+  if (D % 64 || stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES || cluster < 1 || cluster > 16 || rows < 1 || rows > 16) return 0;
   return cluster > 1 ? split_ctas_per_sm<true>(stages, cluster, rows) : split_ctas_per_sm<false>(stages, 1, rows);
+}
+
+// How many clusters of `cluster` CTAs of the split decode kernel the device runs at one time with a
+// ring of `stages` stages and `rows` head rows a unit (a cluster stays inside one GPC); -1 if the
+// query fails, 0 if the sizes are not the kernel's.
+extern "C" int cie_attention_decode_split_clusters(int stages, int cluster, int rows) {
+  if (D % 64 || stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES || rows < 1 || rows > 16) return 0;
+  if (cluster != 2 && cluster != 4 && cluster != 8 && cluster != 16) return 0;
+  const size_t smem = split_smem(stages, cluster, rows);
+  if (cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+      (cluster > 8 && cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)) {
+    cudaGetLastError();
+    return -1;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(1, 1, cluster);
+  config.blockDim = dim3(SPLIT_WARPS * 32);
+  config.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 1;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = cluster;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, decode_split_kernel<true>, &config) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return clusters;
 }
 
 extern "C" int cie_attention_decode_split_max() { return SPLIT_MAX; }
@@ -1293,7 +1324,7 @@ extern "C" int cie_attention_decode_split_trace(void* buffer) {
 
 // The split decode kernel.  splits: CTAs launched per (request, kv head, 16 heads) unit, 1 ..
 // cie_attention_decode_split_max(); a request uses as many of them as leave each `min_keys` keys.
-// cluster: 1, 2, 4 or 8 neighbouring splits of a unit form a thread-block cluster and hand their
+// cluster: 1, 2, 4, 8 or 16 neighbouring splits of a unit form a thread-block cluster and hand their
 // shares to its first CTA through shared memory (splits must be a multiple of it).
 // shares: float32 [requests * kv_heads * ceil(group / 16)][splits][16][head size + 4]; tickets: one
 // int per unit, zero before the first launch (the kernel leaves them zero).  Needs pages of a power
@@ -1312,8 +1343,8 @@ extern "C" int cie_attention_decode_split(const void* q, int q_stride, void* out
   if (min_keys < 1) CIE_FAIL("attention_decode_split: min_keys must be positive");
   if (stages < SPLIT_MIN_STAGES || stages > SPLIT_MAX_STAGES)
     CIE_FAIL("attention_decode_split: %d to %d stages, got %d", SPLIT_MIN_STAGES, SPLIT_MAX_STAGES, stages);
-  if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8)
-    CIE_FAIL("attention_decode_split: clusters of 1, 2, 4 or 8 CTAs, got %d", cluster);
+  if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8 && cluster != 16)
+    CIE_FAIL("attention_decode_split: clusters of 1, 2, 4, 8 or 16 CTAs, got %d", cluster);
   if (splits % cluster) CIE_FAIL("attention_decode_split: %d CTAs per request are no multiple of the cluster size %d", splits, cluster);
   if (splits > cluster && (!shares || !tickets)) CIE_FAIL("attention_decode_split: several clusters per request need scratch memory");
   int page_shift = -1;
@@ -1345,6 +1376,15 @@ extern "C" int cie_attention_decode_split(const void* q, int q_stride, void* out
         : cudaFuncSetAttribute(decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (status != cudaSuccess) CIE_FAIL("attention_decode_split: shared memory %zu: %s", smem, cudaGetErrorString(status));
     configured[variant] = smem;
+  }
+  if (cluster > 8) {
+    // clusters of more than 8 CTAs need the kernel's consent
+    static bool allowed = false;
+    if (!allowed) {
+      cudaError_t status = cudaFuncSetAttribute(decode_split_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (status != cudaSuccess) CIE_FAIL("attention_decode_split: clusters of %d: %s", cluster, cudaGetErrorString(status));
+      allowed = true;
+    }
   }
   if (requests > 65535) CIE_FAIL("attention_decode_split: at most 65535 requests a launch, got %d", requests);
   cudaLaunchConfig_t config = {};

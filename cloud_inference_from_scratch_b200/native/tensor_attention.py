@@ -23,10 +23,23 @@ from .build import load_library
 BM = 128           # query rows of a prefill tile (must match the kernel)
 SM_COUNT = 148     # only where the device cannot be asked (the planners take the device's own count)
 MIN_KEYS_PER_SPLIT = 128
-# the split decode kernel: a CTA keeps at least this many keys (four stages of 64), so that its
-# set-up and the hand-over of its share stay small beside the keys it streams
-MIN_KEYS_PER_SPLIT_CTA = int(os.environ.get("CIE_DECODE_SPLIT_KEYS", "256"))
-# "CTAs per unit,stages[,cluster]" to launch the split decode kernel with whatever the sizes (for measurements)
+# the split decode kernel: where several shares of a unit meet in global memory, a CTA keeps at
+# least this many keys (four tiles of 64), so that its set-up and the hand-over stay small beside
+# the keys it streams; None: the plan's own figure
+MIN_KEYS_PER_SPLIT_CTA = 256
+FORCE_SPLIT_KEYS = int(os.environ["CIE_DECODE_SPLIT_KEYS"]) if os.environ.get("CIE_DECODE_SPLIT_KEYS") else None
+# ... and where the CTAs of a unit are one thread-block cluster, whose shares meet in shared memory
+MIN_KEYS_PER_CLUSTERED_CTA = 128
+# a unit stays one cluster while a CTA's range stays within this many keys of the longest context
+# (16 units in a whole step: clusters of 8 win at 3,800 keys, 1.91 against 1.96 ms, and lose at
+# 6,000, 2.08 against 2.06)
+ONE_CLUSTER_KEYS = 640
+# this many shares of a unit the CTA with the last ticket adds up by itself; a unit that has room
+# for twice as many CTAs gets clusters of 8 that add up eight of them each first (2 units of
+# 32,000 keys: 21.8 us with 64 CTAs in clusters of 8 against 30.7 without; 16 units of 8,192: a
+# step of 2.16 ms with 16 CTAs and no clusters, 2.21 with 18, 2.27 with one cluster of 8)
+MOST_TICKETS = 16
+# "CTAs per unit,stages,cluster" to launch the split decode kernel with whatever the sizes (for measurements)
 FORCE_SPLIT_PLAN = tuple(int(n) for n in os.environ["CIE_DECODE_SPLIT_PLAN"].split(",")) if os.environ.get("CIE_DECODE_SPLIT_PLAN") else None
 # several clusters per request only while each CTA keeps this many keys: handing the shares over
 # through global memory costs about as much as streaming a thousand keys
@@ -36,9 +49,6 @@ MIN_KEYS_PER_CHUNKED_CTA = int(os.environ.get("CIE_DECODE_CHUNK_KEYS", "1024"))
 # clusters of 8 (a 16th waits for a second round, which costs more than the cut brings)
 CLUSTERED_CTAS = 112
 MAX_CHUNKS = 16                  # must match DECODE_MAX_CHUNKS of the kernel
-# the split decode kernel: from this many keys a CTA on, the CTAs of a unit form no cluster (8 requests of
-# 32,000 keys: 3.42 ms a step with 18 CTAs a unit and tickets against 3.85 with two clusters of 8)
-LONG_RANGE_KEYS = 1024
 
 
 def supports(head_dim: int) -> bool:
@@ -106,8 +116,13 @@ class TensorAttention:
             per_sm.argtypes = [i, i, i]
             per_sm.restype = c_int
             self._split_per_sm = per_sm
-            self.split_cluster_max = int(os.environ.get("CIE_DECODE_SPLIT_CLUSTER", "8"))
+            at_once = lib.handle.cie_attention_decode_split_clusters
+            at_once.argtypes = [i, i, i]
+            at_once.restype = c_int
+            self._split_at_once = at_once
+            self.split_cluster_max = int(os.environ.get("CIE_DECODE_SPLIT_CLUSTER", "16"))
             self._split_rings: dict[tuple[int, int], dict[int, int]] = {}
+            self._split_plans: dict[int, tuple[dict[int, dict[int, int]], dict[int, int]]] = {}
             if not self.split_rings(1, 1):
                 raise RuntimeError(f"the split decode kernel does not fit this device at head size {head_dim}")
             self.split_cta_limit = 4 * self.sm_count
@@ -150,49 +165,81 @@ class TensorAttention:
             self._split_rings[key] = {stages: ctas for stages, ctas in rings.items() if ctas >= 1}
         return self._split_rings[key]
 
-    def cluster_for(self, ctas: int) -> int:
-        """CTAs of a unit that form one thread-block cluster: the largest of 8, 4, 2 that the unit's
-        CTAs fill at least once (and the device has a ring for), else no cluster."""
-        for cluster in (8, 4, 2):
-            if cluster <= min(ctas, self.split_cluster_max):
-                return cluster
-        return 1
+    def split_choices(self, rows: int) -> tuple[dict[int, dict[int, int]], dict[int, int]]:
+        """What the split decode kernel can be launched with for ``rows`` head rows a unit, asked of
+        the device once: cluster size -> (ring depth -> CTAs an SM holds), and cluster size -> how
+        many such clusters run at one time with the deepest ring that leaves an SM two CTAs."""
+        rows = min(16, rows)
+        if rows not in self._split_plans:
+            rings = {1: self.split_rings(1, rows)}
+            room: dict[int, int] = {}
+            for cluster in (2, 4, 8, 16):
+                if cluster > self.split_cluster_max:
+                    continue
+                paired = [depth for depth, ctas in self.split_rings(cluster, rows).items() if ctas >= 2]
+                at_once = int(self._split_at_once(max(paired), cluster, rows)) if paired else 0
+                if at_once >= 1:
+                    rings[cluster] = self.split_rings(cluster, rows)
+                    room[cluster] = at_once
+            self._split_plans[rows] = (rings, room)
+        return self._split_plans[rows]
 
     @staticmethod
-    def split_plan(units: int, max_keys: int, sm_count: int, rings: dict[int, int], limit: int, most: int,
-                   tile: int = 64, min_keys: int = MIN_KEYS_PER_SPLIT_CTA) -> tuple[int, int]:
-        """(CTAs per unit, stages of the ring) for the split decode kernel.  ``units``: (request, kv
-        head, 16 heads) triples; ``rings``: ring depth -> CTAs an SM holds with it.
+    def split_plan(units: int, max_keys: int, sm_count: int, rings: dict[int, dict[int, int]], room: dict[int, int],
+                   limit: int, most: int, tile: int = 64) -> tuple[int, int, int, int]:
+        """(CTAs per unit, stages of the ring, CTAs of a cluster, least keys of a CTA) for the split
+        decode kernel.  ``units``: (request, kv head, 16 heads) triples; ``rings``: cluster size ->
+        (ring depth -> CTAs an SM holds with it), 1 for no clusters; ``room``: cluster size -> how
+        many such clusters the device runs at one time.
 
-        Few units (half the SMs or fewer): one CTA an SM with the deepest ring, so that a CTA can ask
-        for its whole range of keys at once, even before the kernel before it has finished; unless
-        two CTAs an SM let a unit have more CTAs that each still keep ``min_keys`` keys (long
-        contexts).  More units: two CTAs an SM with the deepest ring that allows it (a CTA is four warps, and four
-        warps alone do not keep an SM's tensor pipe and copy engine busy), every CTA of the launch
-        resident at one time.  Every CTA keeps at least ``min_keys`` keys of the longest context the
-        tables hold; a launch stays within ``limit`` CTAs (the scratch is sized for that) and a unit
-        within ``most``.  Measured on a B200 at head size 128: 8 requests of 2,048 keys 9.8 us with
-        (9, 6) against 10.4 with (8, 3); 64 requests 26.8 us with (2, 3) against 37 with (1, 6)."""
-        depths = sorted(rings, reverse=True)
-        paired = [depth for depth in depths if rings[depth] >= 2]
-        by_keys = max(1, max_keys // min_keys)
-        alone = max(1, min(by_keys, sm_count // max(1, units), most))          # CTAs a unit gets at one CTA an SM
-        doubled = max(1, min(by_keys, 2 * sm_count // max(1, units), most))    # ... at two
-        if units * 2 <= sm_count and paired and doubled > alone:
-            # long contexts: more CTAs a unit, each still with its keys, stream more than a deep ring
-            # does (8 requests of 32,000 keys: 3.42 ms a step with (18, 3) against 4.25 with (9, 6))
-            stages, slots = paired[0], 2 * sm_count
-        elif units * 2 <= sm_count or not paired:
-            stages, slots = depths[0], sm_count
+        The CTAs of a unit are one thread-block cluster wherever that works out: the largest of 16,
+        8, 4, 2 of which the device runs one per unit at one time, since shares that meet in shared
+        memory cost a few hundred cycles and shares that meet in global memory a few microseconds.
+        Only where a CTA's range of the longest context then passes ``ONE_CLUSTER_KEYS`` and the
+        device has room for twice as many CTAs does a unit get more of them (each with
+        ``MIN_KEYS_PER_SPLIT_CTA`` keys at least, all resident at one time, at most two an SM): up to
+        ``MOST_TICKETS`` without clusters, or, with room for twice that, clusters of 8.  The ring is the deepest that leaves an SM two
+        CTAs (the kernel before this one still holds its own shared memory when this one starts),
+        but no deeper than the longest range a CTA can get.  A launch stays within ``limit`` shares
+        (the scratch is sized for that) and a unit within ``most`` CTAs.
+
+        Measured on a B200 at head size 128, 8 head rows a unit, in microseconds a launch
+        (units x keys: this plan against the best other):
+        2 x 2,100: 5.9 with (16, 3, 16) against 7.6 with (8, 3, 8);  2 x 4,000: 7.1 against 11.2;
+        8 x 4,000: 9.0 with (16, 3, 16) against 11.5 with (8, 3, 8);
+        16 x 4,000: 12.8 with (8, 3, 8) against 18.1 with (16, 3, 8) and 17.7 with (16, 3, 16);
+        16 x 8,000: 19.1 with (16, 3, 1) against 22.2 with (8, 3, 8);
+        32 x 4,000: 16.7 with (8, 3, 8) against 21.3 with (4, 3, 4);
+        64 x 4,000: 25.0 with (4, 3, 4) against 32.3 with (8, 3, 8) and 38.2 with (2, 3, 2)."""
+        plain = rings[1]
+        paired = [depth for depth in plain if plain[depth] >= 2]
+        slots = (2 if paired else 1) * sm_count
+        one = 1
+        for cluster in (16, 8, 4, 2):
+            if (cluster <= most and units <= room.get(cluster, 0) and cluster in rings
+                    and max_keys // cluster >= MIN_KEYS_PER_CLUSTERED_CTA):
+                one = cluster
+                break
+        ctas, cluster, min_keys = one, one, MIN_KEYS_PER_CLUSTERED_CTA
+        many = max(1, min(max_keys // MIN_KEYS_PER_SPLIT_CTA, slots // max(1, units), most))
+        if max_keys // one > ONE_CLUSTER_KEYS and many >= 2 * one:
+            min_keys = MIN_KEYS_PER_SPLIT_CTA
+            clusters = min(many // 8, room.get(8, 0) // max(1, units))
+            if many >= 2 * MOST_TICKETS and clusters >= 3:
+                ctas, cluster = 8 * clusters, 8
+            else:
+                ctas, cluster = min(many, MOST_TICKETS), 1
+            while ctas > cluster and units * ctas // cluster > limit:
+                ctas -= cluster
+        depths = rings[cluster]
+        if cluster > 1 or paired:
+            stages = max(depth for depth in depths if depths[depth] >= 2)
         else:
-            stages, slots = paired[0], 2 * sm_count
-        splits = max(1, min(by_keys, slots // max(1, units), most))
-        while splits > 1 and units * splits > limit:
-            splits -= 1
+            stages = max(depths)
         # no deeper than the longest range a CTA can get
-        wanted = max(min(depths), min(stages, -(-(-(-max_keys // splits)) // tile)))
+        wanted = max(min(depths), min(stages, -(-(-(-max_keys // ctas)) // tile)))
         stages = min(depth for depth in depths if depth >= wanted)
-        return splits, stages
+        return ctas, stages, cluster, min_keys
 
     @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int, sm_count: int = SM_COUNT) -> int:
@@ -234,30 +281,17 @@ class TensorAttention:
         if (self._decode_split is not None and page >= 16 and page & (page - 1) == 0
                 and (kv.k.data_ptr() | kv.v.data_ptr()) % 16 == 0):
             units = requests * kv_heads * -(-group // 16)
-            ctas, stages = self.split_plan(units, max_keys, self.sm_count, self.split_rings(1, group), self.split_cta_limit,
-                                           self.split_max, self.split_tile, MIN_KEYS_PER_SPLIT_CTA)
-            cluster = self.cluster_for(ctas)
-            if max_keys // max(1, ctas) >= LONG_RANGE_KEYS:
-                cluster = 1   # ranges this long hide the hand-over through global memory; clusters only bind the placement
-            if cluster > 1:
-                # Neighbouring CTAs of a unit in one cluster: whole clusters, and the deepest ring with
-                # which an SM still holds two CTAs.  (A cluster starts only when all its CTAs find room in
-                # one part of the device; with one CTA an SM the 16th cluster of 8 waits for a second
-                # round, which costs more than the exchange through shared memory saves.)
-                ctas -= ctas % cluster
-                rings = self.split_rings(cluster, group)
-                paired = [depth for depth in rings if rings[depth] >= 2]
-                if paired:
-                    stages = max(paired)
-                else:
-                    cluster = 1
+            rings, room = self.split_choices(group)
+            ctas, stages, cluster, min_keys = self.split_plan(units, max_keys, self.sm_count, rings, room,
+                                                              self.split_cta_limit, self.split_max, self.split_tile)
             if FORCE_SPLIT_PLAN:
-                ctas, stages = FORCE_SPLIT_PLAN[:2]
-                cluster = FORCE_SPLIT_PLAN[2] if len(FORCE_SPLIT_PLAN) > 2 else self.cluster_for(ctas)
+                ctas, stages, cluster = FORCE_SPLIT_PLAN
+            if FORCE_SPLIT_KEYS:
+                min_keys = FORCE_SPLIT_KEYS
             self._decode_split(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                                kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
                                ctx.context_lens.data_ptr(), requests, q_heads, kv_heads, page, ctas,
-                               MIN_KEYS_PER_SPLIT_CTA, stages, cluster, self._split_shares.data_ptr(),
+                               min_keys, stages, cluster, self._split_shares.data_ptr(),
                                self._split_tickets.data_ptr(), scale, window, ops.error_word.data_ptr(),
                                ops.stream)
             return

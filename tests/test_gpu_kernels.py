@@ -405,8 +405,8 @@ def test_tensor_attention_decode_of_a_long_context_in_several_clusters(ops, monk
 
 
 def test_split_decode_kernel(ops):
-    """The decode kernel that cuts a request's keys over CTAs without a cluster (head sizes that are
-    multiples of 64, pages of a power of two >= 16): 64 requests of very different lengths in one
+    """The decode kernel that cuts a request's keys over CTAs, in clusters or without (head sizes that
+    are multiples of 64, pages of a power of two >= 16): 64 requests of very different lengths in one
     launch; a window whose first key lies inside a page; more than 16 heads on a kv head; head size
     192; planted keys in the first, a middle and the last CTA's range; and the same object again and
     again (the tickets must be back at zero after every launch)."""
@@ -428,6 +428,53 @@ def test_split_decode_kernel(ops):
     tensor_case(ops, 256, [5000], [1], 2, 1, 256, 16, seed=30, plant=(0, 2500, 4.0))
     # a mixed step: single tokens lead, a prompt portion follows (two launches)
     tensor_case(ops, 128, [1500, 16, 700, 40], [1, 1, 1, 300], 16, 2, 128, 16, seed=31, plant=(0, 750, 4.0))
+
+
+@pytest.mark.parametrize("plan,min_keys", [
+    ((16, 3, 16), 128), ((16, 2, 16), 64), ((32, 3, 16), 128), ((8, 3, 8), 128), ((24, 3, 8), 256),
+    ((4, 3, 4), 128), ((2, 3, 2), 128), ((16, 3, 1), 256), ((5, 6, 1), 64), ((1, 3, 1), 128),
+])
+def test_split_decode_kernel_with_every_kind_of_plan(ops, monkeypatch, plan, min_keys):
+    """Whatever (CTAs a unit, ring depth, cluster size, least keys of a CTA) the planner may pick:
+    one cluster of 16 a unit (more CTAs than head rows, so some own no row), several clusters whose
+    shares meet in global memory, no clusters; requests so short that only some CTAs of a cluster
+    work, or one, beside long ones; 1, 7 and 20 head rows on a kv head; a planted key in the first,
+    a middle and the last range; one launch after the other on the same object (tickets and
+    inboxes are left clean)."""
+    from cloud_inference_from_scratch_b200.native import tensor_attention
+
+    item = ops[torch.bfloat16]
+    item.require_attention(128)
+    fast = item._tensor_attention[128]
+    rings, room = fast.split_choices(8)
+    ctas, stages, cluster = plan
+    if cluster > 1 and (cluster not in rings or stages not in rings[cluster]):
+        pytest.skip(f"this device does not run clusters of {cluster} with a ring of {stages}")
+    monkeypatch.setattr(tensor_attention, "FORCE_SPLIT_PLAN", plan)
+    monkeypatch.setattr(tensor_attention, "FORCE_SPLIT_KEYS", min_keys)
+    contexts = [4000, 0, 130, 700, 2047, 63, 1029]
+    for seed, planted in enumerate([(0, 5, 4.0), (0, 2200, 4.0), (0, 3999, 4.0), (4, 1100, 4.0)]):
+        tensor_case(ops, 128, contexts, [1] * len(contexts), 16, 2, 128, 16, seed=40 + seed, plant=planted)
+    tensor_case(ops, 128, [3000, 77], [1, 1], 7, 7, 128, 16, seed=45, plant=(0, 1500, 4.0))      # one head row a unit
+    tensor_case(ops, 128, [3000, 300], [1, 1], 14, 2, 128, 32, seed=46, plant=(0, 2999, 4.0))    # seven
+    tensor_case(ops, 64, [2500, 9], [1, 1], 20, 1, 64, 16, seed=47, plant=(0, 1250, 4.0))        # twenty: two units a kv head
+
+
+def test_split_decode_plans_of_this_device(ops):
+    """What the planner picks from the device's own answers can be launched: every cluster it names
+    has a ring for it and runs at one time."""
+    item = ops[torch.bfloat16]
+    item.require_attention(128)
+    fast = item._tensor_attention[128]
+    rings, room = fast.split_choices(8)
+    assert 1 in rings and all(cluster in rings and at_once >= 1 for cluster, at_once in room.items())
+    for units in (1, 2, 3, 8, 14, 15, 16, 31, 32, 33, 64, 128, 147, 300, 1000):
+        for keys in (16, 128, 500, 2048, 4096, 5120, 8192, 40000, 131072):
+            ctas, stages, cluster, min_keys = fast.split_plan(units, keys, fast.sm_count, rings, room,
+                                                              fast.split_cta_limit, fast.split_max, fast.split_tile)
+            assert stages in rings[cluster] and ctas % cluster == 0 and 1 <= ctas <= fast.split_max
+            assert cluster == 1 or units * (ctas // cluster) <= room[cluster]
+            assert ctas == cluster or units * ctas // cluster <= fast.split_cta_limit
 
 
 def test_tensor_attention_long_prompt_whole(ops):

@@ -41,34 +41,59 @@ def test_the_headline_batch_keeps_one_cluster_a_request():
         assert TensorAttention.chunks_for(8, 2, 8, keys, splits) == 1
 
 
-RINGS = [{1: 3, 2: 3, 3: 2, 4: 1, 5: 1, 6: 1}, {1: 1, 2: 1, 3: 1}, {2: 6, 4: 3, 6: 2, 8: 1}]
+# what a device may answer: cluster size -> (ring depth -> CTAs an SM holds), and cluster size -> clusters at one time
+CHOICES = [
+    ({1: {1: 3, 2: 3, 3: 2, 4: 1, 5: 1, 6: 1}, 2: {1: 3, 2: 3, 3: 2, 4: 1}, 4: {1: 3, 2: 2, 3: 2, 4: 1},
+      8: {1: 3, 2: 2, 3: 2, 4: 1}, 16: {1: 3, 2: 2, 3: 2}}, {2: 148, 4: 72, 8: 32, 16: 8}),
+    ({1: {1: 1, 2: 1, 3: 1}}, {}),                                   # no room for two CTAs an SM, no clusters
+    ({1: {2: 6, 4: 3, 6: 2, 8: 1}, 8: {2: 4, 4: 2}}, {8: 30}),       # clusters of 8 only
+]
 
 
-@pytest.mark.parametrize("rings", RINGS)
+@pytest.mark.parametrize("rings,room", CHOICES)
 @pytest.mark.parametrize("sm_count", [148, 132, 16])
 @pytest.mark.parametrize("requests,kv_heads,group,keys", SHAPES)
-def test_split_decode_plan_fills_the_device_and_keeps_every_cta_keys(requests, kv_heads, group, keys, sm_count, rings):
+def test_split_decode_plan_fills_the_device_and_keeps_every_cta_keys(requests, kv_heads, group, keys, sm_count, rings, room):
     units = requests * kv_heads * -(-group // 16)
     limit, most = 4 * sm_count, 64
-    splits, stages = TensorAttention.split_plan(units, keys, sm_count, rings, limit, most, 64, 256)
-    assert 1 <= splits <= most and stages in rings
-    assert splits == 1 or keys // splits >= 256                    # every CTA keeps its keys
-    assert splits == 1 or units * splits <= limit                  # the scratch holds every share
-    assert splits == 1 or units * splits <= sm_count * min(2, rings[stages])   # one wave
+    room = {cluster: min(at_once, 2 * sm_count // cluster) for cluster, at_once in room.items()}
+    ctas, stages, cluster, min_keys = TensorAttention.split_plan(units, keys, sm_count, rings, room, limit, most, 64)
+    assert 1 <= ctas <= most and cluster in rings and stages in rings[cluster]
+    assert ctas % cluster == 0
+    assert ctas == 1 or keys // ctas >= min_keys                   # every CTA keeps its keys
+    if cluster > 1:
+        assert units * (ctas // cluster) <= room[cluster]          # every cluster runs at once
+        assert rings[cluster][stages] >= 2
+    if ctas > cluster:                                             # shares that meet in global memory
+        assert min_keys == ta.MIN_KEYS_PER_SPLIT_CTA
+        assert units * ctas // cluster <= limit                    # the scratch holds every share
+        assert units * ctas <= sm_count * min(2, rings[cluster][stages])   # one wave
+        assert ctas <= ta.MOST_TICKETS if cluster == 1 else cluster == 8 and ctas >= 24
+    else:
+        assert ctas == cluster
     # a ring is no deeper than the longest range a CTA can get (but a ring the kernel can be launched with)
-    longest = -(-(-(-keys // splits)) // 64)
-    assert stages == min(d for d in rings if d >= max(min(rings), min(stages, longest)))
+    longest = -(-(-(-keys // ctas)) // 64)
+    depths = rings[cluster]
+    assert stages == min(d for d in depths if d >= max(min(depths), min(stages, longest)))
 
 
 def test_split_decode_plan_of_the_measured_batches():
-    rings = {1: 3, 2: 3, 3: 2, 4: 1, 5: 1, 6: 1}
-    assert TensorAttention.split_plan(16, 4096, 148, rings, 592, 64) == (16, 3)    # batch 8, two kv heads: two clusters of 8
-    assert TensorAttention.split_plan(16, 2048, 148, rings, 592, 64) == (8, 4)     # ... tables that end at 2,048 keys
-    assert TensorAttention.split_plan(16, 32768, 148, rings, 592, 64) == (18, 3)   # ... and long contexts
-    assert TensorAttention.split_plan(64, 4096, 148, rings, 592, 64) == (4, 3)     # batch 32
-    assert TensorAttention.split_plan(128, 4096, 148, rings, 592, 64) == (2, 3)    # batch 64
-    assert TensorAttention.split_plan(2, 4096, 148, rings, 592, 64) == (16, 4)     # batch 1
-    assert TensorAttention.split_plan(2, 32768, 148, rings, 592, 64) == (64, 6)    # one long request
+    rings, room = CHOICES[0]
+    plan = lambda units, keys: TensorAttention.split_plan(units, keys, 148, rings, room, 592, 64)
+    assert plan(2, 4096) == (16, 3, 16, 128)      # batch 1, two kv heads: one cluster of 16 a unit
+    assert plan(8, 4096) == (16, 3, 16, 128)      # batch 4
+    assert plan(16, 4096) == (8, 3, 8, 128)       # batch 8: 16 clusters of 16 would not run at one time
+    assert plan(16, 2048) == (8, 3, 8, 128)
+    assert plan(16, 5120) == (8, 3, 8, 128)
+    assert plan(16, 8192) == (16, 3, 1, 256)      # ... longer contexts: more CTAs, shares through global memory
+    assert plan(16, 32768) == (16, 3, 1, 256)
+    assert plan(32, 8192) == (8, 3, 8, 128)       # batch 16: no room for twice the CTAs
+    assert plan(64, 4096) == (4, 3, 4, 128)       # batch 32
+    assert plan(128, 4096) == (2, 3, 2, 128)      # batch 64
+    assert plan(300, 4096) == (1, 3, 1, 128)
+    assert plan(2, 32768) == (64, 3, 8, 256)      # one long request: 8 clusters of 8 a unit
+    assert plan(8, 32768) == (32, 3, 8, 256)
+    assert plan(2, 512) == (4, 2, 4, 128)         # short tables: no more CTAs than have 128 keys, no deeper ring than their range
 
 
 @pytest.mark.parametrize("group", [1, 2, 7, 8, 16, 40, 128, 200])
