@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-GENERIC = ("elementwise.cu", "gemm_simt.cu", "gemm_stream.cu", "gemm_tcgen05.cu", "attention_generic.cu", "sampling.cu")
+GENERIC = ("elementwise.cu", "gemm_simt.cu", "gemm_stream.cu", "gemm_tcgen05.cu", "gemm_skinny.cu", "attention_generic.cu", "sampling.cu")
 
 
 # head sizes the tensor-core attention library is built for ahead of time; any other multiple of

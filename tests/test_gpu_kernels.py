@@ -482,6 +482,61 @@ def test_tensor_attention_long_prompt_whole(ops):
     tensor_case(ops, 64, [300, 0], [700, 64], 14, 2, 64, 16, seed=10)
 
 
+# ------------------------------------------------------------------ weight-streaming tcgen05 product (17 to 256 rows)
+@pytest.mark.parametrize("m,n,k,mode,plan", [
+    (64, 256, 256, 1, (32, 1, 2)), (17, 200, 136, 1, (48, 1, 2)), (100, 1000, 1000, 0, (112, 4, 3)),
+    (33, 331, 96, 0, (16, 1, 2)), (128, 2560, 2048, 0, (176, 8, 4)), (64, 2048, 1408, 3, (64, 2, 6)),
+    (200, 1000, 520, 1, (160, 2, 4)), (256, 704, 2048, 3, (160, 1, 4)), (130, 1000, 520, 1, (256, 1, 2)),
+    (64, 2048, 11008, 0, None), (48, 22016, 2048, 3, None), (129, 2560, 2048, 0, None), (256, 3000, 136, 1, None),
+])
+def test_gemm_skinny(ops, monkeypatch, m, n, k, mode, plan):
+    """The tcgen05 product whose CTAs take a chosen number of weight rows each and, in clusters, a K
+    range each: one and two token tiles, rows and K that are no multiple of anything but 8, the last
+    CTA ragged, bias, float32 and bfloat16 rows and the SiLU epilogue, with 1, 2, 4 and 8 K ranges;
+    and the plans the planner picks for this device."""
+    from cloud_inference_from_scratch_b200.native import skinny
+
+    item = ops[torch.bfloat16]
+    gemm = item._skinny_gemm()
+    x = rand(m, k, dtype=torch.bfloat16, scale=0.5, seed=m)
+    w = rand(n, k, dtype=torch.bfloat16, scale=0.05, seed=n)
+    bias = rand(n, seed=k) if mode != 3 else None
+    want = plain_model.linear(x.float().cpu(), w.float().cpu(), None if bias is None else bias.cpu())
+    if mode == 3:
+        blocks = want.view(m, n // 32, 2, 16)
+        want = (torch.nn.functional.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(m, n // 2)
+    out = torch.full(tuple(want.shape), 7.0, dtype=torch.float32 if mode == 1 else torch.bfloat16).cuda()
+    monkeypatch.setattr(skinny, "FORCE_PLAN", plan)
+    assert gemm.supports(x, w, m, n, k, mode == 3)
+    before = item.launches
+    gemm.launch(x, w, bias, out, mode)
+    torch.cuda.synchronize()
+    item.check_errors()
+    assert item.launches == before + 1
+    scale = float(want.abs().max())
+    if mode == 1:
+        torch.testing.assert_close(out.cpu(), want, rtol=2e-3, atol=2e-3 * max(1.0, scale))
+    else:
+        torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2 * max(1.0, scale / 4))
+
+
+def test_gemm_skinny_refuses_what_it_cannot_run(ops):
+    from cloud_inference_from_scratch_b200.native import skinny
+    from cloud_inference_from_scratch_b200.native.ops import KernelError
+
+    item = ops[torch.bfloat16]
+    gemm = item._skinny_gemm()
+    x = rand(64, 256, dtype=torch.bfloat16)
+    w = rand(256, 256, dtype=torch.bfloat16)
+    out = torch.empty(64, 256, dtype=torch.bfloat16).cuda()
+    for plan in [(24, 1, 2), (272, 1, 2), (32, 3, 2), (32, 8, 2), (32, 1, 1), (256, 1, 12), (256, 4, 2)]:
+        with pytest.raises(KernelError):
+            gemm._gemm(x.data_ptr(), w.data_ptr(), None, out.data_ptr(), 64, 256, 256, 0, *plan,
+                       item.error_word.data_ptr(), item.stream)
+    assert not gemm.supports(x, w, 300, 256, 256, False) and not gemm.supports(x, w, 16, 256, 256, False)
+    assert gemm._smem(64, 160, 6) == skinny.smem_bytes(64, 160, 6) and gemm._smem(200, 96, 3) == skinny.smem_bytes(200, 96, 3)
+
+
 # ------------------------------------------------------------------ streaming matrix product (decode)
 @pytest.mark.parametrize("m", [1, 2, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(331, 96), (2560, 2048), (2048, 11008), (1000, 136)])

@@ -110,3 +110,35 @@ def test_prefill_tiles_cover_every_token_once(group):
         covered[int(request)][q0:min(n, q0 + per_tile)] += 1
     for r, marks in covered.items():
         assert (marks == 1).all(), (r, marks)
+
+
+# ------------------------------------------------------------------ weight-streaming tcgen05 product
+@pytest.mark.parametrize("m", [17, 64, 128, 129, 256])
+@pytest.mark.parametrize("n,k,silu", [(2560, 2048, False), (2048, 2048, False), (22016, 2048, True), (2048, 11008, False),
+                                      (151936, 2048, False), (331, 96, False), (64, 4096, True), (37888, 3584, True)])
+def test_skinny_plan_fits_the_kernel(m, n, k, silu):
+    from cloud_inference_from_scratch_b200.native import skinny
+
+    room = {2: 74, 4: 36, 8: 15}
+    limit = 232448
+    rows, k_parts, stages = skinny.plan(m, n, k, silu, 148, lambda rows, k_parts, stages: room[k_parts], limit)
+    assert rows % (32 if silu else 16) == 0 and 16 <= rows <= 256 and k_parts in (1, 2, 4, 8)
+    assert 2 <= stages <= skinny.MAX_STAGES and skinny.smem_bytes(m, rows, stages) <= limit
+    k_blocks = -(-k // 64)
+    assert k_parts == 1 or k_blocks // k_parts >= skinny.MIN_K_BLOCKS
+    assert stages <= -(-k_blocks // k_parts)                     # no deeper than the K range of a CTA
+    if k_parts > 1:                                              # the ring holds the sums a cluster exchanges
+        assert (2 if m > 128 else 1) * 128 * (rows + 4) * 4 <= skinny.smem_bytes(m, rows, stages) - 1024
+        assert -(-n // rows) <= room[k_parts] or n > 256 * room[k_parts]
+
+
+def test_skinny_plan_deals_the_weight_rows_out_evenly():
+    from cloud_inference_from_scratch_b200.native import skinny
+
+    room = {2: 74, 4: 36, 8: 15}
+    at_once = lambda rows, k_parts, stages: room[k_parts]
+    rows, k_parts, _ = skinny.plan(64, 22016, 2048, True, 148, at_once, 232448)
+    assert k_parts == 1 and -(-22016 // rows) <= 148 and rows * 148 < 22016 * 1.1   # one round, within a tenth of even
+    rows, k_parts, _ = skinny.plan(64, 2048, 11008, False, 148, at_once, 232448)
+    assert k_parts > 1                                                              # few rows, long K: cut along K
+    assert skinny.plan(64, 2048, 64, False, 148, lambda *a: 0, 232448) is None      # one block of K cannot fill a ring of two
