@@ -110,9 +110,9 @@ class Ops:
         # kernels (0: never)
         self.fold_rows = int(os.environ.get("CIE_FOLD_ROWS", "0"))
         # which products of 17 to 256 rows go to the weight-streaming tcgen05 kernel instead of the
-        # library: "0" none, "gate_up" the gate/up product with its activation (up to 128 rows; the
-        # default: 64 requests decode in 3.24 instead of 3.31 ms a step, 32 in 2.80 instead of 2.88),
-        # "all" every product up to 256 rows (for measurements)
+        # library: "0" none, "gate_up" the gate/up product with its activation (the default: 64
+        # requests decode in 3.23 instead of 3.31 ms a step, 32 in 2.80 instead of 2.88; a prompt in
+        # 256-token portions takes 24.7 instead of 25.0 ms), "all" every product (for measurements)
         self.skinny_products = os.environ.get("CIE_SKINNY", "gate_up")
         if self.skinny_products == "0":
             self.skinny_products = ""
@@ -468,8 +468,7 @@ class Ops:
             return hidden_out
         if isinstance(x, NormedInput):
             x = x.materialize()
-        if (self.skinny_products and self.code == BF16 and weight.block == 16 and x.dtype == self.torch.bfloat16
-                and (m <= 128 or self.skinny_products == "all")):
+        if self.skinny_products and self.code == BF16 and weight.block == 16 and x.dtype == self.torch.bfloat16:
             skinny = self._skinny_gemm()
             if skinny.supports(x, weight.weight, m, 2 * inter, k, True):
                 self._flush()
