@@ -19,6 +19,11 @@
 //                 maximum of some row of its warp grew by more than 2^8 (the result does not
 //                 depend on when).
 //
+// A launch with few query tiles (a prompt portion over a long context) may cut the keys of a query
+// tile into ranges, one CTA each (grid.z): such a CTA leaves its unnormalised output, maximum and
+// sum in global memory, and whichever CTA of the tile draws the last ticket adds the shares up.
+// Nobody waits for anybody.
+//
 // S of tile j+1 is computed while the softmax of tile j runs; O += P V of tile j runs while the
 // maximum of tile j+1 is searched.  Every wait is bounded (about two seconds, then an error bit).
 //
@@ -108,7 +113,15 @@ struct Args {
   int* err;
   // one copy per tile when the pages of a tile follow each other in the pool (0: never):
   int run_pages;           // pages a tile spans (1 if a page holds several tiles)
+  // key ranges: up to `splits` CTAs (grid.z) share the keys of a query tile, each with at least
+  // `min_tiles` key tiles; shares: [query tile][kv head, head chunk][split][D + 2][128] float32;
+  // tickets: one int per (query tile, kv head, head chunk), zero between launches
+  int splits, min_tiles;
+  float* shares;
+  int* tickets;
 };
+constexpr int SHARE_FLOATS = (D + 2) * BM;
+constexpr int MAX_RANGES = 4;          // most key ranges of a query tile (the CTA that adds them up holds 32 columns of each)
 
 __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
                                                                  const __grid_constant__ CUtensorMap v_map,
@@ -124,6 +137,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   __shared__ __align__(8) uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES], s_full[2], s_free[2], p_full, pv_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int pages_s[TABLE_SLOTS];   // the block-table entries this CTA's keys need
+  __shared__ int last_s;                 // key ranges: did this CTA draw the tile's last ticket?
 
   pdl_wait();
   pdl_trigger();
@@ -137,11 +151,19 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   const int* table_row = a.table + (size_t)request * a.table_width;
   const int pos_lo = context + q0;
   const int valid_hi = context + q0 + ntok;          // keys [0, valid_hi) are visible to some row
-  const int tiles = (valid_hi + BN - 1) / BN;
+  const int all_tiles = (valid_hi + BN - 1) / BN;
+  // how many of the launched key ranges this query tile uses (the launch is sized for the longest
+  // context the tables hold); the CTAs of the others leave before they set anything up
+  // (adding shares up costs about as much as walking six key tiles: not below three ranges' worth of keys)
+  const int used = a.splits > 1 && all_tiles >= 3 * a.min_tiles ? min(a.splits, all_tiles / a.min_tiles) : 1;
+  const int split = blockIdx.z;
+  if (split >= used) return;
+  const int tile_begin = split * (all_tiles / used) + min(split, all_tiles % used);
+  const int tiles = all_tiles / used + (split < all_tiles % used ? 1 : 0);
   // CTAs that share keys walk them from different starting tiles (the running-maximum softmax does
   // not care about the order), so that they do not all ask L2 for the same lines at the same time
   const int first_tile = tiles > 0 ? (int)((blockIdx.x * 5u + blockIdx.y * 3u) % (unsigned)tiles) : 0;
-  auto tile_of = [&](int j) { const int t = j + first_tile; return t >= tiles ? t - tiles : t; };
+  auto tile_of = [&](int j) { const int t = j + first_tile; return tile_begin + (t >= tiles ? t - tiles : t); };
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -393,11 +415,93 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
       tc_fence_before();
       mbar_arrive(&p_full);
     }
+    bf16* dst = a.out + (size_t)(first_token + tok) * a.out_stride + (size_t)(kvh * a.group + hh) * D;
+    if (used > 1) {
+      // ---- one key range of several: leave the share, draw a ticket, and add all shares up if it
+      // was the last one.  A share is stored column by column, so that the 128 threads write and
+      // read neighbouring words.
+      const int unit = blockIdx.x * gridDim.y + blockIdx.y;
+      float* unit_shares = a.shares + (size_t)unit * a.splits * SHARE_FLOATS;
+      float* share = unit_shares + (size_t)split * SHARE_FLOATS;
+      const bool finished = alive && tiles > 0 && mbar_wait(&pv_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, a.err);
+      if (finished) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t raw[32];
+          tmem_ld32(tmem + lane_base + COL_O + c * 32, raw);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) __stcg(share + (c * 32 + i) * BM + r, __uint_as_float(raw[i]));
+        }
+        __stcg(share + D * BM + r, m_used);
+        __stcg(share + (D + 1) * BM + r, l);
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four softmax warps
+      if (tid == 0) {
+        const int drawn = atomicAdd(a.tickets + unit, 1);
+        last_s = drawn == used - 1 ? 1 : 0;
+        if (drawn == used - 1) a.tickets[unit] = 0;     // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (last_s && finished) {
+        __threadfence();
+        float m_all = -INFINITY;
+        for (int s = 0; s < used; ++s) m_all = fmaxf(m_all, __ldcg(unit_shares + (size_t)s * SHARE_FLOATS + D * BM + r));
+        float weight[MAX_RANGES];
+        float sum = 0.f;
+#pragma unroll
+        for (int s = 0; s < MAX_RANGES; ++s) {
+          weight[s] = 0.f;
+          if (s < used) {
+            const float m_s = __ldcg(unit_shares + (size_t)s * SHARE_FLOATS + D * BM + r);
+            weight[s] = m_s == -INFINITY ? 0.f : exp2f(m_s - m_all);
+            sum += weight[s] * __ldcg(unit_shares + (size_t)s * SHARE_FLOATS + (D + 1) * BM + r);
+          }
+        }
+        const float inv = sum > 0.f ? 1.f / sum : 0.f;
+        if (row_used) {
+          // 32 columns at a time, every load of them asked for before the first addition
+#pragma unroll 1
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            float acc32[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc32[i] = 0.f;
+            float part[MAX_RANGES][32];
+#pragma unroll
+            for (int s = 0; s < MAX_RANGES; ++s) {
+              if (s < used) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) part[s][i] = __ldcg(unit_shares + (size_t)s * SHARE_FLOATS + (c0 + i) * BM + r);
+              }
+            }
+#pragma unroll
+            for (int s = 0; s < MAX_RANGES; ++s) {
+              if (s < used) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc32[i] += weight[s] * part[s][i];
+              }
+            }
+#pragma unroll
+            for (int c = c0; c < c0 + 32; c += 8) {
+            const float* acc = acc32 + (c - c0);
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              __nv_bfloat162 pair = __floats2bfloat162_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+              packed[i] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+          }
+        }
+      }
+    } else
     // ---- write out
     if (alive && tiles > 0 && mbar_wait(&pv_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, a.err)) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = a.out + (size_t)(first_token + tok) * a.out_stride + (size_t)(kvh * a.group + hh) * D;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t raw[32];
@@ -432,14 +536,22 @@ extern "C" int cie_attention_prefill_tc_head_dim() { return D; }
 
 // Same arguments as the mma.sync prefill kernel's entry point, without a window: the caller keeps
 // windowed layers, other head sizes and pages that are no multiple of 16 tokens on that kernel.
+// splits: key ranges launched per query tile (1 .. 4); a tile uses as many as leave each min_tiles
+// key tiles.  shares: float32 [num_tiles * kv_heads * head chunks][splits][head size + 2][128];
+// tickets: one int per (query tile, kv head, head chunk), zero before the first launch.
+extern "C" int cie_attention_prefill_tc_key_tile() { return BN; }
+extern "C" int cie_attention_prefill_tc_max_ranges() { return MAX_RANGES; }
+
 extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride,
                                         const void* k_pool, const void* v_pool, const int* table,
                                         int table_width, int num_pages, const int* tile_request,
                                         const int* tile_q0, int num_tiles, const int* context_lens,
                                         const int* query_lens, const int* query_start, int q_heads,
-                                        int kv_heads, int page_size, int hpt, float scale, int* err,
-                                        void* stream) {
+                                        int kv_heads, int page_size, int hpt, float scale, int splits,
+                                        int min_tiles, float* shares, int* tickets, int* err, void* stream) {
   if (num_tiles <= 0) return 0;
+  if (splits < 1 || splits > MAX_RANGES) CIE_FAIL("attention_prefill_tc: 1 to %d key ranges, got %d", MAX_RANGES, splits);
+  if (splits > 1 && (min_tiles < 1 || !shares || !tickets)) CIE_FAIL("attention_prefill_tc: key ranges need scratch memory and a least number of key tiles each");
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_prefill_tc: %d query heads over %d kv heads", q_heads, kv_heads);
   const int group = q_heads / kv_heads;
   if (hpt < 1 || hpt > BM || hpt > group) CIE_FAIL("attention_prefill_tc: %d heads per tile with a group of %d", hpt, group);
@@ -455,6 +567,7 @@ extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, 
   a.query_lens = query_lens; a.query_start = query_start;
   a.group = group; a.hpt = hpt; a.tpt = BM / hpt; a.head_chunks = (group + hpt - 1) / hpt;
   a.scale_log2 = scale * 1.4426950408889634f; a.err = err;
+  a.splits = splits; a.min_tiles = min_tiles; a.shares = shares; a.tickets = tickets;
   CUtensorMap k_map, v_map;
   const long long rows = (long long)num_pages * kv_heads * page_size;
   // the pools as matrices [pages * kv_heads * page_size, D], read in blocks of 16 whole rows
@@ -481,7 +594,7 @@ extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, 
     if (status != cudaSuccess) CIE_FAIL("attention_prefill_tc: shared memory %d: %s", SMEM_BYTES, cudaGetErrorString(status));
     configured = true;
   }
-  dim3 grid(num_tiles, kv_heads * a.head_chunks);
+  dim3 grid(num_tiles, kv_heads * a.head_chunks, splits);
   CIE_LAUNCH("attention_prefill_tc", prefill_tc_kernel, grid, dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)stream, k_map, v_map, k_run, v_run, a);
   return 0;
 }

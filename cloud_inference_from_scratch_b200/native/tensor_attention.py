@@ -39,6 +39,9 @@ ONE_CLUSTER_KEYS = 640
 # 32,000 keys: 21.8 us with 64 CTAs in clusters of 8 against 30.7 without; 16 units of 8,192: a
 # step of 2.16 ms with 16 CTAs and no clusters, 2.21 with 18, 2.27 with one cluster of 8)
 MOST_TICKETS = 16
+# the tcgen05 prompt kernel: a key range of a query tile keeps at least this many tiles of 128 keys
+MAX_KEY_RANGES = 4   # must match MAX_RANGES of the kernel
+MIN_KEY_TILES_PER_RANGE = int(os.environ.get("CIE_PREFILL_RANGE_TILES", "4"))
 # "CTAs per unit,stages,cluster" to launch the split decode kernel with whatever the sizes (for measurements)
 FORCE_SPLIT_PLAN = tuple(int(n) for n in os.environ["CIE_DECODE_SPLIT_PLAN"].split(",")) if os.environ.get("CIE_DECODE_SPLIT_PLAN") else None
 # several clusters per request only while each CTA keeps this many keys: handing the shares over
@@ -142,8 +145,15 @@ class TensorAttention:
             tc = _Lib(load_library("attention_prefill_tc.cu", defines))
             self._prefill_tc = tc.function(
                 "cie_attention_prefill_tc",
-                [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, v, v],
+                [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, i, i, v, v, v, v],
             )
+            # key ranges of a query tile (few query tiles over a long context): where the CTAs of a
+            # tile leave their shares, and the tickets that tell the last one; a launch with key
+            # ranges has at most one CTA an SM
+            self.prefill_key_tile = int(tc.handle.cie_attention_prefill_tc_key_tile())
+            self.prefill_ranges = os.environ.get("CIE_PREFILL_RANGES", "1") != "0"
+            self._prefill_shares = torch.zeros(self.sm_count * BM * (head_dim + 2), dtype=torch.float32, device=ops.device)
+            self._prefill_tickets = torch.zeros(self.sm_count, dtype=torch.int32, device=ops.device)
 
     def cluster_room(self, splits: int) -> int:
         """CTAs in clusters of ``splits`` that run at one time, one cluster held back for whatever
@@ -242,6 +252,17 @@ class TensorAttention:
         return ctas, stages, cluster, min_keys
 
     @staticmethod
+    def key_ranges(ctas: int, max_keys: int, sm_count: int, key_tile: int) -> int:
+        """Key ranges per query tile of the tcgen05 prompt kernel: a launch of ``ctas`` query tiles
+        (times kv heads) that leaves most SMs idle cuts the keys of a tile over up to 4 CTAs, as
+        long as the launch stays within one CTA an SM and every range keeps
+        ``MIN_KEY_TILES_PER_RANGE`` key tiles of the longest context the tables hold (a tile of
+        128 keys takes a CTA about a microsecond, setting a CTA up and adding its share up several)."""
+        if ctas < 1 or ctas * 2 > sm_count:
+            return 1
+        return max(1, min(MAX_KEY_RANGES, sm_count // ctas, max_keys // (key_tile * MIN_KEY_TILES_PER_RANGE)))
+
+    @staticmethod
     def splits_for(requests: int, kv_heads: int, group: int, max_keys: int, sm_count: int = SM_COUNT) -> int:
         """CTAs (of one cluster) that share a request's keys: enough to put work on every SM,
         at least MIN_KEYS_PER_SPLIT keys each, a power of two up to 8."""
@@ -331,12 +352,18 @@ class TensorAttention:
         ops.launches += 1
         if (self._prefill_tc is not None and window <= 0 and kv.page_size % 16 == 0
                 and qkv.shape[1] % 8 == 0 and out.shape[1] % 8 == 0):
+            ranges = 1
+            if self.prefill_ranges:
+                ctas = num_tiles * kv_heads * -(-group // heads_per_tile(group))
+                ranges = self.key_ranges(ctas, table.shape[1] * kv.page_size, self.sm_count, self.prefill_key_tile)
             self._prefill_tc(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                              kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,
                              plan["tile_request"].data_ptr(), plan["tile_q0"].data_ptr(), num_tiles,
                              ctx.context_lens.data_ptr(), ctx.query_lens.data_ptr(),
                              ctx.query_start.data_ptr(), q_heads, kv_heads, kv.page_size,
-                             heads_per_tile(group), scale, ops.error_word.data_ptr(), ops.stream)
+                             heads_per_tile(group), scale, ranges, MIN_KEY_TILES_PER_RANGE,
+                             self._prefill_shares.data_ptr(), self._prefill_tickets.data_ptr(),
+                             ops.error_word.data_ptr(), ops.stream)
             return True
         self._prefill(qkv.data_ptr(), qkv.shape[1], out.data_ptr(), out.shape[1], kv.k.data_ptr(),
                       kv.v.data_ptr(), table.data_ptr(), table.shape[1], kv.num_pages,

@@ -477,6 +477,32 @@ def test_split_decode_plans_of_this_device(ops):
             assert ctas == cluster or units * ctas // cluster <= fast.split_cta_limit
 
 
+@pytest.mark.parametrize("min_tiles", [1, 2, 4])
+def test_prompt_attention_with_key_ranges(ops, monkeypatch, min_tiles):
+    """A prompt portion over a long context makes few query tiles: the keys of a tile are then cut
+    into ranges, one CTA each, whose shares the CTA with the last ticket adds up.  A planted key in
+    the first, a middle and the last range; a short request beside a long one (its tiles use one
+    range of those launched); head size 64; seven heads on a kv head; single tokens beside the
+    portion; and one launch after the other on the same object (the tickets are left at zero)."""
+    from cloud_inference_from_scratch_b200.native import tensor_attention
+    from cloud_inference_from_scratch_b200.native.tensor_attention import TensorAttention
+
+    monkeypatch.setattr(tensor_attention, "MIN_KEY_TILES_PER_RANGE", min_tiles)
+    assert TensorAttention.key_ranges(26, 2048, 148, 128) == min(4, 2048 // (128 * min_tiles))
+    assert TensorAttention.key_ranges(80, 8192, 148, 128) == 1 and TensorAttention.key_ranges(8, 65536, 148, 128) == 4
+    item = ops[torch.bfloat16]
+    item.require_attention(128)
+    assert item._tensor_attention[128]._prefill_tc is not None
+    for seed, planted in enumerate([(0, 3, 4.0), (0, 900, 4.0), (0, 1699, 4.0)]):
+        tensor_case(ops, 128, [1500], [200], 16, 2, 128, 16, seed=50 + seed, plant=planted)
+    tensor_case(ops, 128, [1800, 0, 40], [150, 100, 30], 16, 2, 128, 16, seed=54, plant=(0, 1000, 4.0))
+    tensor_case(ops, 128, [3000, 700, 16, 1200], [1, 1, 1, 64], 14, 2, 128, 32, seed=55, plant=(3, 600, 4.0))
+    tensor_case(ops, 64, [2500], [90], 4, 1, 64, 16, seed=56, plant=(0, 1250, 4.0))
+    tensor_case(ops, 128, [4000], [17], 16, 2, 128, 16, seed=57, plant=(0, 2047, 4.0))
+    tensor_case(ops, 128, [9000, 500], [40, 300], 16, 2, 128, 16, seed=58, plant=(0, 8999, 4.0))
+    assert int(item._tensor_attention[128]._prefill_tickets.abs().sum()) == 0
+
+
 def test_tensor_attention_long_prompt_whole(ops):
     tensor_case(ops, 128, [0], [1500], 16, 2, 128, 16, seed=9)
     tensor_case(ops, 64, [300, 0], [700, 64], 14, 2, 64, 16, seed=10)
