@@ -139,8 +139,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   __shared__ int pages_s[TABLE_SLOTS];   // the block-table entries this CTA's keys need
   __shared__ int last_s;                 // key ranges: did this CTA draw the tile's last ticket?
 
-  pdl_wait();
-  pdl_trigger();
+  // Before `griddepcontrol.wait`: only what the kernel before this one does not write.  Lengths and
+  // block tables come with the step's metadata, and keys and values below a request's context
+  // were written by earlier steps (the kernel before writes this step's tokens only).
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;   // the list puts the tiles with the most keys first
   const int kvh = blockIdx.y / a.head_chunks, h0 = (blockIdx.y % a.head_chunks) * a.hpt;
@@ -178,17 +179,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   }
   if (warp == MMA_WARP) tmem_alloc<TMEM_COLS>(&tmem_slot);
 
-  // ---- Q tile, swizzled by hand: row r is token r / hpt, head h0 + r % hpt of the group.
   // Value stages start as zeros: rows that no copy fills must not hold NaN or Inf bits.
-  for (int idx = tid; idx < BM * (D / 8); idx += THREADS) {
-    const int r = idx / (D / 8), c = idx % (D / 8);
-    const int tok = r / a.hpt, hh = h0 + r % a.hpt;
-    uint4 value = make_uint4(0u, 0u, 0u, 0u);
-    if (tok < ntok && hh < a.group)
-      value = *reinterpret_cast<const uint4*>(a.q + (size_t)(first_token + tok) * a.q_stride +
-                                              (size_t)(kvh * a.group + hh) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_s + (c >> 3) * SUB_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = value;
-  }
   for (int idx = tid; idx < STAGES * TILE_BYTES / 16; idx += THREADS)
     reinterpret_cast<uint4*>(v_s)[idx] = make_uint4(0u, 0u, 0u, 0u);
   {
@@ -200,8 +191,28 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  const bool producer = warp > MMA_WARP && warp < PV_WARP;
+  if (!producer) {
+  // ---- everybody but the TMA warps (which go ahead with the keys and values of earlier steps):
+  // the Q tile, swizzled by hand: row r is token r / hpt, head h0 + r % hpt of the group.
+  pdl_wait();
+  pdl_trigger();
+  constexpr int STAGERS = THREADS - (PV_WARP - MMA_WARP - 1) * 32;
+  const int stager = warp <= MMA_WARP ? tid : tid - (PV_WARP - MMA_WARP - 1) * 32;
+  for (int idx = stager; idx < BM * (D / 8); idx += STAGERS) {
+    const int r = idx / (D / 8), c = idx % (D / 8);
+    const int tok = r / a.hpt, hh = h0 + r % a.hpt;
+    uint4 value = make_uint4(0u, 0u, 0u, 0u);
+    if (tok < ntok && hh < a.group)
+      value = *reinterpret_cast<const uint4*>(a.q + (size_t)(first_token + tok) * a.q_stride +
+                                              (size_t)(kvh * a.group + hh) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + (c >> 3) * SUB_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = value;
+  }
+  fence_async_smem();
+  asm volatile("bar.sync 2, %0;" ::"n"(STAGERS) : "memory");   // the Q tile is whole before a product reads it
+  }
 
-  if (warp > MMA_WARP && warp < PV_WARP) {
+  if (producer) {
     // ---- TMA producers: some warps for the keys, some for the values; a lane fetches one
     // block of 16 keys of a tile.  Keys and values have rings of their own: a key stage is free again
     // as soon as S of its tile is computed, long before the values of that tile have been used.
@@ -264,9 +275,15 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
       __syncwarp();
       return true;
     };
-    bool alive = true;
-    for (int j = 0; j < tiles && alive; ++j)
+    bool alive = true, waited = false;
+    for (int j = 0; j < tiles && alive; ++j) {
+      if (!waited && tile_of(j) * BN + BN > context) {   // a tile with keys of this step: the kernel before writes them
+        pdl_wait();
+        waited = true;
+      }
       alive = for_keys ? load(j, k_s, &k_map, &k_run_map, k_full, k_empty) : load(j, v_s, &v_map, &v_run_map, v_full, v_empty);
+    }
+    if (!waited) pdl_wait();
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
       // ---- S = Q K^T, issued as far ahead as the two S buffers allow; the other products are

@@ -142,3 +142,16 @@ def test_skinny_plan_deals_the_weight_rows_out_evenly():
     rows, k_parts, _ = skinny.plan(64, 2048, 11008, False, 148, at_once, 232448)
     assert k_parts > 1                                                              # few rows, long K: cut along K
     assert skinny.plan(64, 2048, 64, False, 148, lambda *a: 0, 232448) is None      # one block of K cannot fill a ring of two
+
+
+def test_prompt_attention_key_ranges():
+    key_ranges = TensorAttention.key_ranges
+    assert key_ranges(256, 4096, 148, 128) == 1            # a whole prompt fills the device by itself
+    assert key_ranges(32, 4096, 148, 128) == 4             # 256 tokens of the 3B shape: 32 query tiles
+    assert key_ranges(64, 4096, 148, 128) == 2             # 512 tokens
+    assert key_ranges(8, 1024, 148, 128) == 2              # tables that hold few keys: no more ranges than have four tiles
+    assert key_ranges(8, 256, 148, 128) == 1 and key_ranges(0, 4096, 148, 128) == 1
+    for ctas in range(1, 200):
+        for keys in (128, 4096, 1 << 20):
+            ranges = key_ranges(ctas, keys, 148, 128)
+            assert 1 <= ranges <= ta.MAX_KEY_RANGES and (ranges == 1 or ctas * ranges <= 148)
