@@ -550,15 +550,14 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
 using namespace cie;
 
 extern "C" int cie_attention_prefill_tc_head_dim() { return D; }
+extern "C" int cie_attention_prefill_tc_key_tile() { return BN; }
+extern "C" int cie_attention_prefill_tc_max_ranges() { return MAX_RANGES; }
 
 // Same arguments as the mma.sync prefill kernel's entry point, without a window: the caller keeps
 // windowed layers, other head sizes and pages that are no multiple of 16 tokens on that kernel.
 // splits: key ranges launched per query tile (1 .. 4); a tile uses as many as leave each min_tiles
 // key tiles.  shares: float32 [num_tiles * kv_heads * head chunks][splits][head size + 2][128];
 // tickets: one int per (query tile, kv head, head chunk), zero before the first launch.
-extern "C" int cie_attention_prefill_tc_key_tile() { return BN; }
-extern "C" int cie_attention_prefill_tc_max_ranges() { return MAX_RANGES; }
-
 extern "C" int cie_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride,
                                         const void* k_pool, const void* v_pool, const int* table,
                                         int table_width, int num_pages, const int* tile_request,

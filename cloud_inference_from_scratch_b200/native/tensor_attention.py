@@ -98,11 +98,9 @@ class TensorAttention:
         self._decode_clusters.argtypes = [i, i]
         self._decode_clusters.restype = c_int
         self._cluster_room: dict[int, int] = {}
-        # the split decode kernel (no clusters; shares merged by whoever draws the last ticket): for
-        # pools TMA can read.  Its scratch is sized once for the most CTAs a launch with more than
-        # one CTA per unit can have: four per SM.
-        # where clusters of one request leave their shares (at most one CTA an SM takes part), and
-        # the tickets that tell the last one; the kernel leaves the tickets at zero
+        # the cluster decode kernel: where clusters of one request leave their shares (at most one
+        # CTA an SM takes part), and the tickets that tell the last one; the kernel leaves the
+        # tickets at zero
         torch = ops.torch
         self.sm_count = ops.torch.cuda.get_device_properties(ops.device).multi_processor_count
         self._chunk_shares = torch.zeros(self.sm_count * 16 * (head_dim + 2), dtype=torch.float32, device=ops.device)
@@ -128,6 +126,8 @@ class TensorAttention:
             self._split_plans: dict[int, tuple[dict[int, dict[int, int]], dict[int, int]]] = {}
             if not self.split_rings(1, 1):
                 raise RuntimeError(f"the split decode kernel does not fit this device at head size {head_dim}")
+            # shares that meet in global memory (several clusters, or CTAs without a cluster, on one
+            # unit) and their tickets: sized once for the most shares a launch can have
             self.split_cta_limit = 4 * self.sm_count
             self._split_shares = ops.torch.zeros(self.split_cta_limit * 16 * (head_dim + 4), dtype=ops.torch.float32,
                                                  device=ops.device)
@@ -178,7 +178,7 @@ class TensorAttention:
     def split_choices(self, rows: int) -> tuple[dict[int, dict[int, int]], dict[int, int]]:
         """What the split decode kernel can be launched with for ``rows`` head rows a unit, asked of
         the device once: cluster size -> (ring depth -> CTAs an SM holds), and cluster size -> how
-        many such clusters run at one time with the deepest ring that leaves an SM two CTAs."""
+        many such clusters run at one time with the deepest ring with which an SM still holds two CTAs."""
         rows = min(16, rows)
         if rows not in self._split_plans:
             rings = {1: self.split_rings(1, rows)}
