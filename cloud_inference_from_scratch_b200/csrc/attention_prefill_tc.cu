@@ -177,8 +177,6 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
     mbar_init(&pv_done[0], 1); mbar_init(&pv_done[1], 1);
     mbar_init_fence();
   }
-  if (warp == MMA_WARP) tmem_alloc<TMEM_COLS>(&tmem_slot);
-
   // Value stages start as zeros: rows that no copy fills must not hold NaN or Inf bits.
   for (int idx = tid; idx < STAGES * TILE_BYTES / 16; idx += THREADS)
     reinterpret_cast<uint4*>(v_s)[idx] = make_uint4(0u, 0u, 0u, 0u);
@@ -187,16 +185,17 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
     for (int idx = tid; idx < needed; idx += THREADS) pages_s[idx] = table_row[idx];
   }
   fence_async_smem();
-  tc_fence_before();
   __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
+  uint32_t tmem = 0;
   const bool producer = warp > MMA_WARP && warp < PV_WARP;
   if (!producer) {
   // ---- everybody but the TMA warps (which go ahead with the keys and values of earlier steps):
   // the Q tile, swizzled by hand: row r is token r / hpt, head h0 + r % hpt of the group.
+  // Tensor memory is asked for after the wait only: a CTA of an earlier kernel that is still to
+  // allocate its own on this SM must never find it taken by a CTA that waits for that kernel.
   pdl_wait();
   pdl_trigger();
+  if (warp == MMA_WARP) tmem_alloc<TMEM_COLS>(&tmem_slot);
   constexpr int STAGERS = THREADS - (PV_WARP - MMA_WARP - 1) * 32;
   const int stager = warp <= MMA_WARP ? tid : tid - (PV_WARP - MMA_WARP - 1) * 32;
   for (int idx = stager; idx < BM * (D / 8); idx += STAGERS) {
@@ -209,7 +208,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(const __grid_con
     *reinterpret_cast<uint4*>(q_s + (c >> 3) * SUB_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = value;
   }
   fence_async_smem();
+  tc_fence_before();
   asm volatile("bar.sync 2, %0;" ::"n"(STAGERS) : "memory");   // the Q tile is whole before a product reads it
+  tc_fence_after();
+  tmem = tmem_slot;
   }
 
   if (producer) {

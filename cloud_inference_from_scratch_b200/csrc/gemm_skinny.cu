@@ -13,8 +13,8 @@
 //
 // Warp 0 copies (TMA, 128-byte swizzle) into a ring of stages of [tokens 128 x 64][weights rows x
 // 64]; it asks for the weights of the first stages BEFORE `griddepcontrol.wait`, since weights do
-// not depend on the kernel before this one.  Warp 1 multiplies (one thread; accumulators in tensor
-// memory), tcgen05.commit hands stages back.  Warps 2..5 read the accumulators with tcgen05.ld and
+// not depend on the kernel before this one (tensor memory is allocated after the wait).  Warp 1
+// multiplies (one thread; accumulators in tensor memory), tcgen05.commit hands stages back.  Warps 2..5 read the accumulators with tcgen05.ld and
 // finish: bias, bfloat16 or float32 rows, or SiLU(gate) * up for gate/up rows interleaved in
 // blocks of 16.
 //
@@ -40,7 +40,6 @@ constexpr int UMMA_K = 16;
 constexpr int X_TILE_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
 constexpr int MAX_STAGES = 12;
-constexpr int MAX_K_PARTS = 8;
 constexpr int SMEM_LIMIT = 232448;   // most dynamic shared memory of a CTA on sm_100
 
 constexpr int kOutBF16 = 0, kOutF32 = 1, kOutSiluMul = 3;
@@ -178,11 +177,20 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_skinny_kernel(const __grid_co
     mbar_init(&acc_bar, 1);
     mbar_init_fence();
   }
-  if (warp == 1) tmem_alloc_cols(&tmem_base_s, tmem_cols);
-  tc_fence_before();
   __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_base_s;
+  // Tensor memory is asked for after `griddepcontrol.wait` only: a CTA of an earlier kernel that is
+  // still to allocate its own on this SM must never find it taken by a CTA that waits for that
+  // kernel.  Warps 1..5 (the product and the epilogue) meet once it is there.
+  uint32_t tmem_base = 0;
+  if (warp >= 1) {
+    pdl_wait();
+    pdl_trigger();
+    if (warp == 1) tmem_alloc_cols(&tmem_base_s, tmem_cols);
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(THREADS - 32) : "memory");
+    tc_fence_after();
+    tmem_base = tmem_base_s;
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -241,8 +249,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_skinny_kernel(const __grid_co
   float* sums = reinterpret_cast<float*>(tiles);
   bool ready = true;
   if (warp >= 2) {
-    pdl_wait();   // the kernel before may still read what this one writes
-    pdl_trigger();
     ready = mbar_wait(&acc_bar, 0, a.err);
     tc_fence_after();
     const int quarter = warp & 3;
