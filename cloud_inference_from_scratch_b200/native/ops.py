@@ -361,7 +361,7 @@ class Ops:
         self._flush()
         if self.skinny_products == "all" and self.code == BF16 and x.dtype == self.torch.bfloat16:
             skinny = self._skinny_gemm()
-            if skinny.supports(x, weight, m, n, k, False):
+            if skinny.supports(x, weight, m, n, k, False, out):
                 skinny.launch(x, weight, bias, out, 1 if out.dtype == self.torch.float32 else 0)
                 return out
         if self._tensor_gemm is not None and self._tensor_gemm.run(x, weight, bias, out):
@@ -470,7 +470,7 @@ class Ops:
             x = x.materialize()
         if self.skinny_products and self.code == BF16 and weight.block == 16 and x.dtype == self.torch.bfloat16:
             skinny = self._skinny_gemm()
-            if skinny.supports(x, weight.weight, m, 2 * inter, k, True):
+            if skinny.supports(x, weight.weight, m, 2 * inter, k, True, hidden_out):
                 self._flush()
                 skinny.launch(x, weight.weight, None, hidden_out, 3)
                 return hidden_out

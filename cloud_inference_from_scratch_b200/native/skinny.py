@@ -97,11 +97,13 @@ class SkinnyGemm:
                                     self.smem_limit)
         return self._plans[key]
 
-    def supports(self, x: Any, weight: Any, m: int, n: int, k: int, silu: bool) -> bool:
+    def supports(self, x: Any, weight: Any, m: int, n: int, k: int, silu: bool, out: Any = None) -> bool:
         if not MIN_ROWS <= m <= MAX_ROWS or k % 8 or k < 8:
             return False
-        if x.data_ptr() % 16 or weight.data_ptr() % 16 or not x.is_contiguous():
+        if x.data_ptr() % 16 or weight.data_ptr() % 16 or not x.is_contiguous() or not weight.is_contiguous():
             return False
+        if out is not None and (out.data_ptr() % 16 or not out.is_contiguous()):
+            return False   # the epilogues write whole rows of [M, N] (or [M, N / 2]) in 8- and 16-byte pieces
         if silu and n % 32:
             return False
         return (FORCE_PLAN or self.plan(m, n, k, silu)) is not None
